@@ -1,0 +1,232 @@
+"""CPU restatement of the reference's pair-representation ops.
+
+TEST INFRASTRUCTURE ONLY (see ``oracle/__init__.py``).  Every function is a
+plain, un-fused torch transcription of the *algorithm* of one reference module
+and takes that module's ``state_dict`` (same key names) as ``w``.  Arithmetic
+runs in the dtype of the inputs (pass fp32 or fp64 tensors); nothing here is
+tuned for speed.
+
+Paths cited are relative to the reference project root.
+"""
+from __future__ import annotations
+
+import math
+
+import torch
+import torch.nn.functional as F
+from torch import Tensor
+
+LN_EPS = 1e-5  # nn.LayerNorm default; src/bioemu2/biomoa/ops/triangle_multiplication.py:71
+
+
+def layer_norm(x: Tensor, weight: Tensor | None, bias: Tensor | None, eps: float = LN_EPS) -> Tensor:
+    """Biased-variance LayerNorm over the last axis (torch.nn.LayerNorm semantics)."""
+    mu = x.mean(dim=-1, keepdim=True)
+    var = ((x - mu) ** 2).mean(dim=-1, keepdim=True)
+    y = (x - mu) / torch.sqrt(var + eps)
+    if weight is not None:
+        y = y * weight
+    if bias is not None:
+        y = y + bias
+    return y
+
+
+def linear(x: Tensor, weight: Tensor, bias: Tensor | None = None) -> Tensor:
+    y = x @ weight.T
+    return y if bias is None else y + bias
+
+
+def triangle_multiplication(x: Tensor, mask: Tensor, w: dict, mode: str) -> Tensor:
+    """``TriangleMultiplicationFull.forward``.
+
+    src/bioemu2/biomoa/ops/triangle_multiplication.py:86-99 (weights :62-76).
+    No residual: the caller adds it (src/bioemu2/biomoa/modules/pairmixer.py:447-452).
+    """
+    assert mode in ("outgoing", "incoming")
+    h = layer_norm(x, w["norm_in.weight"], w["norm_in.bias"])
+    proj = linear(h, w["p_in.weight"]) * torch.sigmoid(linear(h, w["g_in.weight"]))
+    proj = torch.where(mask.bool().unsqueeze(-1), proj, torch.zeros_like(proj))
+    a, b = proj.chunk(2, dim=-1)
+    if mode == "outgoing":
+        t = torch.einsum("bikd,bjkd->bijd", a, b)
+    else:
+        t = torch.einsum("bkid,bkjd->bijd", a, b)
+    t = layer_norm(t, w["norm_out.weight"], w["norm_out.bias"])
+    return linear(t, w["p_out.weight"]) * torch.sigmoid(linear(h, w["g_out.weight"]))
+
+
+def transition(x: Tensor, w: dict) -> Tensor:
+    """``Transition.forward``: ``fc3(silu(fc1(LN(x))) * fc2(LN(x)))``.
+
+    src/bioemu2/biomoa/ops/transition.py:52-76.  The LayerNorm is applied only
+    when the state dict carries ``norm.*`` keys (``use_norm=True``, :44-45).
+    """
+    if "norm.weight" in w:
+        x = layer_norm(x, w["norm.weight"], w["norm.bias"])
+    return linear(F.silu(linear(x, w["fc1.weight"])) * linear(x, w["fc2.weight"]), w["fc3.weight"])
+
+
+def attention_pair_bias(
+    s: Tensor,
+    z: Tensor,
+    mask: Tensor,
+    w: dict,
+    num_heads: int,
+    multiplicity: int = 1,
+    inf: float = 1e6,
+) -> Tensor:
+    """``AttentionPairBias.forward`` (un-tiled branch).
+
+    src/bioemu2/biomoa/ops/attention_pair_bias.py:128-192,224-225.  The key
+    mask *replaces* masked logits by ``-inf`` (finite 1e6, :183-190); the pair
+    bias ``proj_z(norm_z(z))`` is shared by the ``multiplicity`` copies (:172-179).
+    """
+    BM, N, c_s = s.shape
+    B = z.shape[0]
+    assert BM == B * multiplicity
+    H = num_heads
+    dh = c_s // H
+    if "norm_s.weight" in w:
+        s = layer_norm(s, w["norm_s.weight"], w["norm_s.bias"])
+    qkv = linear(s, w["proj_qkv.weight"])
+    q, k, v = qkv.chunk(3, dim=-1)
+    q = (q + w["proj_q_bias"]).view(BM, N, H, dh)
+    k = k.view(BM, N, H, dh)
+    v = v.view(BM, N, H, dh)
+    g = torch.sigmoid(linear(s, w["proj_g.weight"]))
+    zb = linear(layer_norm(z, w["norm_z.weight"], w.get("norm_z.bias")), w["proj_z.weight"])
+    zb = zb.permute(0, 3, 1, 2)  # [B, H, N, N]
+    attn = torch.einsum("bihd,bjhd->bhij", q, k) / math.sqrt(dh)
+    attn = attn.view(B, multiplicity, H, N, N) + zb.unsqueeze(1)
+    key_mask = mask.bool().view(B, 1, 1, 1, N)
+    attn = torch.where(key_mask, attn, torch.full_like(attn, -inf))
+    attn = attn.softmax(dim=-1).view(BM, H, N, N)
+    o = torch.einsum("bhij,bjhd->bihd", attn, v).reshape(BM, N, c_s)
+    return linear(g * o, w["proj_o.weight"])
+
+
+def outer_product_mean(m: Tensor, mask: Tensor, w: dict) -> Tensor:
+    """``OuterProductMeanVanilla.forward``.
+
+    src/bioemu2/biomoa/ops/outer_product_mean.py:45-75.  ``mask`` is ``[B,S,N]``
+    (rows averaged over, :66-67) or ``[B,N]`` (divisor 1, :68-69).
+    """
+    mask = mask.bool()
+    c_hidden = w["proj_ab.weight"].shape[0] // 2
+    mp = linear(layer_norm(m, w["norm.weight"], w["norm.bias"]), w["proj_ab.weight"])
+    mp = torch.where(mask.unsqueeze(-1), mp, torch.zeros_like(mp))
+    a, b = mp.chunk(2, dim=-1)
+    if mask.ndim == 3:
+        num_valid = mask.any(dim=-1).sum(dim=1).clamp(min=1).to(m.dtype)
+    else:
+        num_valid = torch.ones(m.shape[0], dtype=m.dtype)
+    z = torch.einsum("bsic,bsjd->bijcd", a, b)
+    z = z.reshape(*z.shape[:3], c_hidden * c_hidden) / num_valid[:, None, None, None]
+    return linear(z, w["proj_o.weight"], w["proj_o.bias"])
+
+
+def _sub(w: dict, prefix: str) -> dict:
+    p = prefix + "."
+    return {k[len(p):]: v for k, v in w.items() if k.startswith(p)}
+
+
+def pairmixer_layer(z: Tensor, pair_mask: Tensor, w: dict) -> Tensor:
+    """``PairMixerLayer.forward`` in eval mode (dropout is the identity).
+
+    src/bioemu2/biomoa/modules/pairmixer.py:430-456; ``s`` passes through
+    unchanged and is therefore not an argument here.
+    """
+    z = z + triangle_multiplication(z, pair_mask, _sub(w, "tri_mul_out"), "outgoing")
+    z = z + triangle_multiplication(z, pair_mask, _sub(w, "tri_mul_in"), "incoming")
+    z = z + transition(z, _sub(w, "transition_z"))
+    return z
+
+
+def pairmixer_module(z: Tensor, pair_mask: Tensor, w: dict, num_blocks: int) -> Tensor:
+    """``PairMixerModule.forward``: src/bioemu2/biomoa/modules/pairmixer.py:368-370."""
+    for i in range(num_blocks):
+        z = pairmixer_layer(z, pair_mask, _sub(w, f"layers.{i}"))
+    return z
+
+
+def triangle_attention(x: Tensor, mask: Tensor, w: dict, num_heads: int, ending: bool, inf: float = 1e6) -> Tensor:
+    """Triangle self-attention around the starting (or ending) node.
+
+    NOT IN THE REFERENCE -- parity unpinned.  The reference removed this op
+    (src/bioemu2/biomoa/modules/pairmixer.py:459-462), so this is the published
+    AlphaFold-2 algorithm (Jumper et al. 2021, suppl. alg. 13/14) written with
+    the reference's pair-bias-attention conventions: bias-free projections, LN
+    eps 1e-5, finite ``inf`` replacing masked logits, and a gating projection
+    with a bias (initialised to 1 by the module).
+
+    ``x[B,N,N,D]``, ``mask[B,N,N]``.  Starting node: row ``i`` attends from
+    ``j`` to ``k`` with logits ``q[i,j]·k[i,k]/sqrt(dh) + bias[j,k]`` and keys
+    masked by ``mask[i,k]``.  Ending node is the same on the transposed pair
+    tensor.
+    """
+    if ending:
+        x = x.transpose(1, 2)
+        mask = mask.transpose(1, 2)
+    B, N, _, D = x.shape
+    H = num_heads
+    h = layer_norm(x, w["layer_norm.weight"], w["layer_norm.bias"])
+    dh = w["linear_q.weight"].shape[0] // H
+    q = linear(h, w["linear_q.weight"]).view(B, N, N, H, dh)
+    k = linear(h, w["linear_k.weight"]).view(B, N, N, H, dh)
+    v = linear(h, w["linear_v.weight"]).view(B, N, N, H, dh)
+    tri_bias = linear(h, w["linear_b.weight"]).permute(0, 3, 1, 2)  # [B,H,j,k]
+    g = torch.sigmoid(linear(h, w["linear_g.weight"], w["linear_g.bias"]))
+    logits = torch.einsum("bijhd,bikhd->bihjk", q, k) / math.sqrt(dh)
+    logits = logits + tri_bias.unsqueeze(1)
+    key_mask = mask.bool().view(B, N, 1, 1, N)
+    logits = torch.where(key_mask, logits, torch.full_like(logits, -inf))
+    p = logits.softmax(dim=-1)
+    o = torch.einsum("bihjk,bikhd->bijhd", p, v).reshape(B, N, N, H * dh)
+    out = linear(g * o, w["linear_o.weight"])
+    if ending:
+        out = out.transpose(1, 2)
+    return out
+
+
+def pairformer_block(s: Tensor, z: Tensor, token_mask: Tensor, w: dict, *, tri_heads: int = 4, apb_heads: int = 16):
+    """The composite block the benchmark configs describe.
+
+    Pair track: triangle multiplication out/in, triangle attention start/end,
+    pair transition; single track: pair-bias attention and a transition, each
+    with a residual.  The reference's own block stops after the pair
+    transition (src/bioemu2/biomoa/modules/pairmixer.py:430-456); the attention
+    parts are assembled from ``AttentionPairBias`` and the unpinned triangle
+    attention above.
+    """
+    pair_mask = token_mask[:, :, None] & token_mask[:, None, :]
+    z = z + triangle_multiplication(z, pair_mask, _sub(w, "tri_mul_out"), "outgoing")
+    z = z + triangle_multiplication(z, pair_mask, _sub(w, "tri_mul_in"), "incoming")
+    z = z + triangle_attention(z, pair_mask, _sub(w, "tri_att_start"), tri_heads, ending=False)
+    z = z + triangle_attention(z, pair_mask, _sub(w, "tri_att_end"), tri_heads, ending=True)
+    z = z + transition(z, _sub(w, "transition_z"))
+    s = s + attention_pair_bias(s, z, token_mask, _sub(w, "attention"), apb_heads)
+    s = s + transition(s, _sub(w, "transition_s"))
+    return s, z
+
+
+def conditioned_transformer_layer(
+    x: Tensor, pairs: Tensor, c: Tensor, mask: Tensor, w: dict, num_heads: int,
+    multiplicity: int = 1, lns_scale: float = 1.0,
+) -> Tensor:
+    """``ConditionedTransformerLayer.forward`` (full-attention token block).
+
+    src/bioemu2/biomoa/modules/transformer.py:317-353 with ``ada_ln`` :26-41:
+    ``x += gamma1 * APB(lns*((1+alpha1)*LN(x)+beta1)); x += gamma2 * T(lns*(...))``.
+    State-dict keys: ``cond.0.{weight,bias}`` (LayerNorm), ``cond.2.{weight,bias}``
+    (Linear), ``attention.pair_bias_attn.*``, ``transition.*``.
+    """
+    cc = layer_norm(c, w["cond.0.weight"], w["cond.0.bias"])
+    cc = linear(F.silu(cc), w["cond.2.weight"], w["cond.2.bias"])
+    a1, b1, g1, a2, b2, g2 = cc.chunk(6, dim=-1)
+    h = attention_pair_bias(
+        lns_scale * (layer_norm(x, None, None) * (1 + a1) + b1), pairs, mask,
+        _sub(w, "attention.pair_bias_attn"), num_heads, multiplicity,
+    )
+    x = x + g1 * h
+    h = transition(lns_scale * (layer_norm(x, None, None) * (1 + a2) + b2), _sub(w, "transition"))
+    return x + g2 * h

@@ -1,0 +1,80 @@
+"""Generate ``golden_fp32.pt`` by running the REFERENCE's own torch modules.
+
+Run in a container that has the reference checkout (it is imported in place
+through ``oracle.reference_shim``; nothing is copied):
+
+    python tests/golden/make_golden.py
+
+For each case in ``cases.py`` the reference module is constructed, the seeded
+weights are loaded through ``load_state_dict`` (strict), and the fp32 forward
+output is stored together with a checksum of the inputs.
+"""
+from __future__ import annotations
+
+import os
+import sys
+
+import torch
+
+ROOT = os.path.dirname(os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+sys.path.insert(0, ROOT)
+sys.path.insert(0, os.path.dirname(os.path.abspath(__file__)))
+
+import cases as C  # noqa: E402
+from oracle import reference_shim  # noqa: E402
+
+
+def run_reference(case: dict) -> torch.Tensor:
+    R = reference_shim.modules()
+    kind = case["kind"]
+    w = case["w"]
+    with torch.no_grad():
+        if kind == "trimul":
+            cls = R.TriangleMultiplicationOutgoing if case["mode"] == "outgoing" else R.TriangleMultiplicationIncoming
+            mod = cls(dim=case["x"].shape[-1]).eval()
+            mod.load_state_dict(w, strict=True)
+            return mod(case["x"], case["mask"])
+        if kind == "transition":
+            mod = R.Transition(case["x"].shape[-1], case["hidden"], use_norm=case["use_norm"]).eval()
+            mod.load_state_dict(w, strict=True)
+            return mod(case["x"])
+        if kind == "apb":
+            mod = R.AttentionPairBias(case["s"].shape[-1], case["z"].shape[-1], case["heads"],
+                                      initial_norm=case["initial_norm"]).eval()
+            mod.load_state_dict(w, strict=True)
+            return mod(case["s"], case["z"], case["mask"], multiplicity=case["M"])
+        if kind == "opm":
+            mod = R.OuterProductMeanVanilla(case["m"].shape[-1], case["c_hidden"], case["c_out"]).eval()
+            mod.load_state_dict(w, strict=True)
+            return mod(case["m"], case["mask"])
+        if kind == "pairmixer":
+            mod = R.PairMixerLayer(384, case["z"].shape[-1], trimul_variant="full").eval()
+            mod.load_state_dict(w, strict=True)
+            s = torch.zeros(1, case["z"].shape[1], 384)
+            return mod(s, case["z"], case["pair_mask"])[1]
+        if kind == "cond_layer":
+            from bioemu2.biomoa.modules.transformer import ConditionedTransformerLayer
+
+            mod = ConditionedTransformerLayer(
+                dim=case["x"].shape[-1], dim_pairwise=case["z"].shape[-1], dim_cond=case["c"].shape[-1],
+                heads=case["heads"], transition_hidden=case["hidden"], lns_scale=case["lns_scale"],
+            ).eval()
+            mod.load_state_dict(w, strict=True)
+            return mod(case["x"], case["z"], case["c"], case["mask"], multiplicity=case["M"])
+    raise KeyError(kind)
+
+
+def main() -> None:
+    torch.set_num_threads(2)  # fixed reduction order, as the reference's tests/conftest.py:5-10
+    out = {}
+    for name, make in C.CASES.items():
+        case = make()
+        y = run_reference(case)
+        out[name] = {"output": y.float().contiguous(), "input_checksum": C.checksum(C.case_tensors(case))}
+        print(f"{name:28s} out {tuple(y.shape)} absmax {float(y.abs().max()):.4f}")
+    torch.save(out, C.GOLDEN_PATH)
+    print("wrote", C.GOLDEN_PATH, os.path.getsize(C.GOLDEN_PATH), "bytes")
+
+
+if __name__ == "__main__":
+    main()
