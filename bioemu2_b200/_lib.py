@@ -1,0 +1,82 @@
+"""ctypes binding of ``libb200pair.so`` (the C ABI declared in ``include/b200pair.h``).
+
+There is no fallback: if the library has not been built, importing this module raises.
+"""
+from __future__ import annotations
+
+import ctypes
+import os
+from ctypes import POINTER, Structure, c_char_p, c_float, c_int, c_int64, c_size_t, c_uint8, c_void_p
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+LIB_PATH = os.path.join(HERE, "libb200pair.so")
+
+OK = 0
+ERR_INVALID_ARGUMENT = 1
+ERR_CUDA = 2
+ERR_UNSUPPORTED_DEVICE = 3
+ERR_WORKSPACE = 4
+ERR_DEVICE_WAIT = 5
+
+DTYPE_BF16 = 0
+DTYPE_F32 = 1
+
+
+class TriMulWeights(Structure):
+    _fields_ = [
+        ("w_in", c_void_p),
+        ("w_out", c_void_p),
+        ("ln_in_w", c_void_p),
+        ("ln_in_b", c_void_p),
+        ("ln_out_w", c_void_p),
+        ("ln_out_b", c_void_p),
+    ]
+
+
+# name -> (restype, argtypes); mirrors include/b200pair.h one to one
+SIGNATURES = {
+    "b200_version": (c_int, []),
+    "b200_last_error": (c_char_p, []),
+    "b200_check_device": (c_int, []),
+    "b200_device_status": (c_int, [POINTER(c_int)]),
+    "b200_layernorm_fwd": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_int, c_float, c_void_p]),
+    "b200_bmm_nt_bf16": (c_int, [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int64, c_int64,
+                                 c_int64, c_int64, c_int64, c_int64, c_float, c_void_p]),
+    "b200_trimul_workspace_bytes": (c_size_t, [c_int]),
+    "b200_trimul_fwd": (c_int, [c_void_p, c_void_p, c_void_p, POINTER(TriMulWeights), c_int, c_int, c_int, c_int,
+                                c_int, c_void_p, c_size_t, c_void_p]),
+    "b200_transition_fwd": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_int,
+                                    c_int, c_int, c_void_p]),
+}
+
+if not os.path.exists(LIB_PATH):
+    raise ImportError(
+        f"{LIB_PATH} is missing: the CUDA library has not been built "
+        "(run `python -m bioemu2_b200.build`). There is no CPU or PyTorch fallback."
+    )
+
+lib = ctypes.CDLL(LIB_PATH)
+for _name, (_res, _args) in SIGNATURES.items():
+    _fn = getattr(lib, _name)
+    _fn.restype = _res
+    _fn.argtypes = _args
+
+
+def last_error() -> str:
+    return (lib.b200_last_error() or b"").decode()
+
+
+def check(status: int) -> None:
+    """Turn a status code into the exception the reference modules would raise."""
+    if status == OK:
+        return
+    msg = last_error()
+    if status in (ERR_INVALID_ARGUMENT, ERR_WORKSPACE):
+        raise ValueError(f"b200pair: {msg}")
+    raise RuntimeError(f"b200pair (status {status}): {msg}")
+
+
+def device_status() -> int:
+    out = c_int(0)
+    check(lib.b200_device_status(ctypes.byref(out)))
+    return out.value

@@ -1,0 +1,169 @@
+// Batched C[b] = scale * A[b] * B[b]^T with both operands K-major bf16, fp32
+// accumulation in tensor memory and bf16 output.
+//
+// This is the per-channel contraction of triangle multiplication
+// (t[d][i][j] = sum_k a[d][i][k] * b[d][j][k]) and the MSA-depth contraction of
+// the outer product mean.  Persistent kernel, one CTA per SM:
+//   warp 0      TMA producer   (A and B K-slabs of 64 through a shared-memory ring)
+//   warp 1      MMA issuer     (tcgen05.mma 128 x BN x 16, two accumulator buffers in TMEM)
+//   warps 2..5  epilogue       (TMEM -> registers -> bf16 -> global)
+#pragma once
+#include "umma.cuh"
+
+namespace b200 {
+
+struct BmmParams {
+  __nv_bfloat16* C;
+  long long c_batch_stride;  // elements
+  int ldc;                   // elements
+  int m_valid, n_valid;      // rows / columns of C that exist (n_valid % 8 == 0)
+  int tiles_m, tiles_n, batch;
+  int k_blocks;              // K / 64, rounded up (TMA zero-fills the tail)
+  float scale;
+};
+
+template <int BN>
+struct BmmCfg {
+  static constexpr int BM = 128;
+  static constexpr int BK = 64;
+  static constexpr int STAGES = (BN == 256) ? 4 : 6;
+  static constexpr uint32_t A_BYTES = BM * BK * 2;
+  static constexpr uint32_t B_BYTES = BN * BK * 2;
+  static constexpr uint32_t STAGE_BYTES = A_BYTES + B_BYTES;
+  static constexpr uint32_t BAR_OFFSET = STAGES * STAGE_BYTES;
+  static constexpr uint32_t SMEM_BYTES = BAR_OFFSET + 256 + 1024;  // + barriers + alignment slack
+  static constexpr int THREADS = 192;
+};
+
+template <int BN>
+__global__ void __launch_bounds__(192, 1)
+bmm_nt_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB, BmmParams p) {
+  using Cfg = BmmCfg<BN>;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint64_t* full = reinterpret_cast<uint64_t*>(smem + Cfg::BAR_OFFSET);
+  uint64_t* empty = full + Cfg::STAGES;
+  uint64_t* acc_full = empty + Cfg::STAGES;
+  uint64_t* acc_empty = acc_full + 2;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_empty + 2);
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const int tiles_per_batch = p.tiles_m * p.tiles_n;
+  const int total_tiles = tiles_per_batch * p.batch;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < Cfg::STAGES; ++s) {
+      mbar_init(&full[s], 1);
+      mbar_init(&empty[s], 1);
+    }
+    for (int a = 0; a < 2; ++a) {
+      mbar_init(&acc_full[a], 1);
+      mbar_init(&acc_empty[a], 128);
+    }
+    fence_mbar_init();
+    prefetch_tmap(&tmA);
+    prefetch_tmap(&tmB);
+  }
+  if (warp == 1) tmem_alloc(tmem_slot, 512);
+  tc_fence_before_sync();
+  __syncthreads();
+  tc_fence_after_sync();
+  const uint32_t tmem_base = *tmem_slot;
+
+  if (warp == 0) {
+    if (lane == 0) {
+      int stage = 0;
+      uint32_t phase = 0;
+      for (int tile = blockIdx.x; tile < total_tiles; tile += gridDim.x) {
+        const int b = tile / tiles_per_batch;
+        const int rem = tile - b * tiles_per_batch;
+        const int tm = rem / p.tiles_n;
+        const int tn = rem - tm * p.tiles_n;
+        for (int kb = 0; kb < p.k_blocks; ++kb) {
+          mbar_wait(&empty[stage], phase ^ 1, 1);
+          uint8_t* sa = smem + stage * Cfg::STAGE_BYTES;
+          mbar_arrive_expect_tx(&full[stage], Cfg::STAGE_BYTES);
+          tma_load_3d(sa, &tmA, &full[stage], kb * 64, tm * 128, b);
+          tma_load_3d(sa + Cfg::A_BYTES, &tmB, &full[stage], kb * 64, tn * BN, b);
+          if (++stage == Cfg::STAGES) {
+            stage = 0;
+            phase ^= 1;
+          }
+        }
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0) {
+      constexpr uint32_t idesc = make_idesc_bf16(128, BN);
+      int stage = 0;
+      uint32_t phase = 0;
+      int it = 0;
+      for (int tile = blockIdx.x; tile < total_tiles; tile += gridDim.x, ++it) {
+        const int acc = it & 1;
+        mbar_wait(&acc_empty[acc], ((it >> 1) & 1) ^ 1, 2);
+        tc_fence_after_sync();
+        const uint32_t d_tmem = tmem_base + acc * BN;
+        for (int kb = 0; kb < p.k_blocks; ++kb) {
+          mbar_wait(&full[stage], phase, 3);
+          tc_fence_after_sync();
+          const uint32_t sa = smem_u32(smem + stage * Cfg::STAGE_BYTES);
+          const uint32_t sb = sa + Cfg::A_BYTES;
+#pragma unroll
+          for (int k = 0; k < 4; ++k) {
+            umma_bf16_ss(d_tmem, make_desc_k_sw128(sa + k * 32), make_desc_k_sw128(sb + k * 32), idesc,
+                         (kb | k) != 0);
+          }
+          umma_commit(&empty[stage]);
+          if (++stage == Cfg::STAGES) {
+            stage = 0;
+            phase ^= 1;
+          }
+        }
+        umma_commit(&acc_full[acc]);
+      }
+    }
+  } else {
+    const int quarter = warp & 3;  // TMEM lanes this warp may read: 32*quarter .. +31
+    int it = 0;
+    for (int tile = blockIdx.x; tile < total_tiles; tile += gridDim.x, ++it) {
+      const int b = tile / tiles_per_batch;
+      const int rem = tile - b * tiles_per_batch;
+      const int tm = rem / p.tiles_n;
+      const int tn = rem - tm * p.tiles_n;
+      const int acc = it & 1;
+      mbar_wait(&acc_full[acc], (it >> 1) & 1, 4);
+      tc_fence_after_sync();
+      const int row = tm * 128 + quarter * 32 + lane;
+      __nv_bfloat16* crow = p.C + (long long)b * p.c_batch_stride + (long long)row * p.ldc + tn * BN;
+#pragma unroll 1
+      for (int c = 0; c < BN / 32; ++c) {
+        uint32_t v[32];
+        tmem_ld_32x32(tmem_addr(tmem_base, quarter * 32, acc * BN + c * 32), v);
+        tmem_ld_wait();
+        if (row < p.m_valid) {
+#pragma unroll
+          for (int g = 0; g < 4; ++g) {
+            const int col = tn * BN + c * 32 + g * 8;
+            if (col < p.n_valid) {
+              uint4 o;
+              o.x = pack_bf16x2(__uint_as_float(v[g * 8 + 0]) * p.scale, __uint_as_float(v[g * 8 + 1]) * p.scale);
+              o.y = pack_bf16x2(__uint_as_float(v[g * 8 + 2]) * p.scale, __uint_as_float(v[g * 8 + 3]) * p.scale);
+              o.z = pack_bf16x2(__uint_as_float(v[g * 8 + 4]) * p.scale, __uint_as_float(v[g * 8 + 5]) * p.scale);
+              o.w = pack_bf16x2(__uint_as_float(v[g * 8 + 6]) * p.scale, __uint_as_float(v[g * 8 + 7]) * p.scale);
+              *reinterpret_cast<uint4*>(crow + c * 32 + g * 8) = o;
+            }
+          }
+        }
+      }
+      tc_fence_before_sync();
+      mbar_arrive(&acc_empty[acc]);
+    }
+  }
+
+  tc_fence_before_sync();
+  __syncthreads();
+  if (warp == 1) tmem_dealloc(tmem_base, 512);
+}
+
+}  // namespace b200

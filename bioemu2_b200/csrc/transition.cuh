@@ -1,0 +1,257 @@
+// Pair transition: out = fc3( silu(fc1(h)) * fc2(h) ) [+ x],  h = LN(x) (or x), dim 128 -> hidden 512 -> 128.
+//
+// One persistent CTA per SM walks tiles of 128 pair rows.  The hidden axis is processed in 8 chunks of
+// 64: GEMM1 writes [fc1 chunk | fc2 chunk] (128 x 128) to one of two TMEM buffers, a warpgroup turns it
+// into the bf16 SwiGLU product in shared memory (K-major operand), GEMM2 accumulates it against the
+// matching 64-wide slice of fc3 into the output accumulator (two of them, so the final store of a tile
+// overlaps the next tile's GEMMs).  The hidden activations never leave the SM.
+//
+//   warps 0-3   SwiGLU epilogue of even chunks + final store of even tiles
+//   warps 4-7   SwiGLU epilogue of odd chunks  + final store of odd tiles
+//   warps 8-15  producers: load rows, LayerNorm, write the GEMM1 A operand
+//   warp  16    MMA issuer
+//   warp  17    TMA loader for the weight chunks
+#pragma once
+#include "row_tile.cuh"
+
+namespace b200 {
+
+struct TransitionParams {
+  const void* x;           // [rows][128] fp32 or bf16
+  void* out;               // [rows][128] same dtype, may alias x
+  const float* ln_w;       // nullptr with use_norm == 0
+  const float* ln_b;
+  long long rows;
+  int num_tiles;
+  int use_norm;
+  int add_residual;
+  float eps;
+};
+
+namespace transition {
+constexpr int CHUNKS = 8;  // hidden 512 = 8 x 64
+constexpr uint32_t X_OFF = 0;                            // 2 stages x 32 KB (A of GEMM1)
+constexpr uint32_t W1_OFF = X_OFF + 2 * kOperandTile;    // 2 stages x 32 KB ([fc1|fc2] chunk, 128 rows x 128 K)
+constexpr uint32_t W3_OFF = W1_OFF + 2 * kOperandTile;   // 2 stages x 16 KB (fc3 slice, 128 rows x 64 K)
+constexpr uint32_t H_OFF = W3_OFF + 2 * kOperandHalf;    // 2 buffers x 16 KB (A of GEMM2, 128 rows x 64 K)
+constexpr uint32_t BAR_OFF = H_OFF + 2 * kOperandHalf;
+constexpr uint32_t SMEM_BYTES = BAR_OFF + 256 + 1024;
+constexpr int THREADS = 576;
+}  // namespace transition
+
+template <bool F32>
+__global__ void __launch_bounds__(576, 1)
+transition_kernel(const __grid_constant__ CUtensorMap tmW1, const __grid_constant__ CUtensorMap tmW3,
+                  TransitionParams p) {
+  using namespace transition;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + BAR_OFF);
+  uint64_t* x_full = bars;            // [2] count 128
+  uint64_t* x_empty = bars + 2;       // [2] count 1 (commit)
+  uint64_t* w1_full = bars + 4;       // [2] TMA
+  uint64_t* w1_empty = bars + 6;      // [2] commit
+  uint64_t* w3_full = bars + 8;       // [2] TMA
+  uint64_t* w3_empty = bars + 10;     // [2] commit
+  uint64_t* d1_full = bars + 12;      // [2] commit
+  uint64_t* d1_empty = bars + 14;     // [2] count 128
+  uint64_t* h_full = bars + 16;       // [2] count 128
+  uint64_t* h_empty = bars + 18;      // [2] commit
+  uint64_t* out_full = bars + 20;     // [2] commit
+  uint64_t* out_empty = bars + 22;    // [2] count 128
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 24);
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+
+  if (threadIdx.x == 0) {
+    for (int i = 0; i < 2; ++i) {
+      mbar_init(&x_full[i], 256);
+      mbar_init(&x_empty[i], 1);
+      mbar_init(&w1_full[i], 1);
+      mbar_init(&w1_empty[i], 1);
+      mbar_init(&w3_full[i], 1);
+      mbar_init(&w3_empty[i], 1);
+      mbar_init(&d1_full[i], 1);
+      mbar_init(&d1_empty[i], 128);
+      mbar_init(&h_full[i], 128);
+      mbar_init(&h_empty[i], 1);
+      mbar_init(&out_full[i], 1);
+      mbar_init(&out_empty[i], 128);
+    }
+    fence_mbar_init();
+    prefetch_tmap(&tmW1);
+    prefetch_tmap(&tmW3);
+  }
+  if (warp == 16) tmem_alloc(tmem_slot, 512);
+  tc_fence_before_sync();
+  __syncthreads();
+  tc_fence_after_sync();
+  const uint32_t tmem_base = *tmem_slot;
+  // TMEM columns: D1[b] at b*128 (fc1 chunk 0..63, fc2 chunk 64..127); OUT[o] at 256 + o*128.
+
+  int my_tiles = 0;
+  for (int tile = blockIdx.x; tile < p.num_tiles; tile += gridDim.x) ++my_tiles;
+  const int total_chunks = my_tiles * CHUNKS;
+  // A global chunk counter g = it*8 + c drives every ring of depth 2: stage g&1, use index g>>1.
+
+  if (warp == 17) {
+    // ------------------------------------------------------------------ weight loader (TMA)
+    if (lane == 0) {
+      for (int g = 0; g < total_chunks; ++g) {
+        const int c = g & 7, s = g & 1;
+        mbar_wait(&w1_empty[s], ((g >> 1) & 1) ^ 1, 30);
+        mbar_arrive_expect_tx(&w1_full[s], kOperandTile);
+        tma_load_2d(smem + W1_OFF + s * kOperandTile, &tmW1, &w1_full[s], 0, c * 128);
+        tma_load_2d(smem + W1_OFF + s * kOperandTile + kOperandHalf, &tmW1, &w1_full[s], 64, c * 128);
+        mbar_wait(&w3_empty[s], ((g >> 1) & 1) ^ 1, 31);
+        mbar_arrive_expect_tx(&w3_full[s], kOperandHalf);
+        tma_load_2d(smem + W3_OFF + s * kOperandHalf, &tmW3, &w3_full[s], c * 64, 0);
+      }
+    }
+  } else if (warp == 16) {
+    // ------------------------------------------------------------------ MMA issuer
+    if (lane == 0) {
+      constexpr uint32_t idesc = make_idesc_bf16(128, 128);
+      auto gemm2 = [&](int g) {  // consumes H[g&1] and the fc3 slice of chunk g
+        const int c = g & 7, b = g & 1, o = (g >> 3) & 1;
+        mbar_wait(&h_full[b], (g >> 1) & 1, 32);
+        mbar_wait(&w3_full[b], (g >> 1) & 1, 33);
+        if (c == 0) mbar_wait(&out_empty[o], (((g >> 3) >> 1) & 1) ^ 1, 34);
+        tc_fence_after_sync();
+        const uint32_t h_s = smem_u32(smem + H_OFF + b * kOperandHalf);
+        const uint32_t w3_s = smem_u32(smem + W3_OFF + b * kOperandHalf);
+#pragma unroll
+        for (int k = 0; k < 4; ++k)
+          umma_bf16_ss(tmem_base + 256 + o * 128, make_desc_k_sw128(h_s + k * 32), make_desc_k_sw128(w3_s + k * 32),
+                       idesc, (c | k) != 0);
+        umma_commit(&h_empty[b]);
+        umma_commit(&w3_empty[b]);
+        if (c == 7) umma_commit(&out_full[o]);
+      };
+      for (int g = 0; g < total_chunks; ++g) {
+        const int c = g & 7, b = g & 1, it = g >> 3, xs = it & 1;
+        if (c == 0) mbar_wait(&x_full[xs], (it >> 1) & 1, 35);
+        mbar_wait(&w1_full[b], (g >> 1) & 1, 36);
+        mbar_wait(&d1_empty[b], ((g >> 1) & 1) ^ 1, 37);
+        tc_fence_after_sync();
+        umma_k128(tmem_base + b * 128, smem_u32(smem + X_OFF + xs * kOperandTile),
+                  smem_u32(smem + W1_OFF + b * kOperandTile), idesc, false);
+        umma_commit(&w1_empty[b]);
+        umma_commit(&d1_full[b]);
+        if (c == 7) umma_commit(&x_empty[xs]);
+        if (g > 0) gemm2(g - 1);
+      }
+      if (total_chunks > 0) gemm2(total_chunks - 1);
+    }
+  } else if (warp >= 8) {
+    // ------------------------------------------------------------------ producers
+    const int pt = threadIdx.x - 256;  // 0..255
+    float gamma[8], beta[8];
+    load_gamma_beta(p.ln_w, p.ln_b, pt, gamma, beta);
+    RowTile<256> regs;
+    auto load_tile = [&](int tile) {
+      const long long row0 = (long long)tile * 128;
+      auto rp = [&](int r) -> const void* {
+        return (row0 + r) < p.rows ? static_cast<const uint8_t*>(p.x) + (row0 + r) * kD * zbytes<F32>() : nullptr;
+      };
+      if (p.use_norm)
+        regs.template load<F32, true>(pt, rp, gamma, beta, p.eps);
+      else
+        regs.template load<F32, false>(pt, rp, gamma, beta, p.eps);
+    };
+    int it = 0;
+    int tile = blockIdx.x;
+    if (tile < p.num_tiles) load_tile(tile);
+    for (; tile < p.num_tiles; tile += gridDim.x, ++it) {
+      const int s = it & 1;
+      mbar_wait(&x_empty[s], ((it >> 1) & 1) ^ 1, 38);
+      regs.store_operand(pt, smem + X_OFF + s * kOperandTile);
+      fence_proxy_async_smem();
+      mbar_arrive(&x_full[s]);
+      const int next = tile + gridDim.x;
+      if (next < p.num_tiles) load_tile(next);
+    }
+  } else {
+    // ------------------------------------------------------------------ SwiGLU + output epilogues
+    const int grp = warp >> 2;             // 0: even chunks / even tiles, 1: odd
+    const int quarter = warp & 3;
+    const int r = quarter * 32 + lane;     // pair row of the tile == TMEM lane
+    int it = 0;
+    for (int tile = blockIdx.x; tile < p.num_tiles; tile += gridDim.x, ++it) {
+      for (int c = grp; c < CHUNKS; c += 2) {
+        const int g = it * CHUNKS + c;
+        const int b = g & 1;  // == grp
+        mbar_wait(&d1_full[b], (g >> 1) & 1, 39);
+        tc_fence_after_sync();
+        mbar_wait(&h_empty[b], ((g >> 1) & 1) ^ 1, 40);
+        uint8_t* hrow = smem + H_OFF + b * kOperandHalf;
+#pragma unroll 1
+        for (int hh = 0; hh < 2; ++hh) {
+          uint32_t av[32], bv[32];
+          tmem_ld_32x32(tmem_addr(tmem_base, quarter * 32, b * 128 + hh * 32), av);
+          tmem_ld_32x32(tmem_addr(tmem_base, quarter * 32, b * 128 + 64 + hh * 32), bv);
+          tmem_ld_wait();
+#pragma unroll
+          for (int q = 0; q < 4; ++q) {
+            uint32_t o[4];
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+              const int j0 = q * 8 + e * 2;
+              const float a0 = __uint_as_float(av[j0]), a1 = __uint_as_float(av[j0 + 1]);
+              const float h0 = a0 * sigmoid_fast(a0) * __uint_as_float(bv[j0]);
+              const float h1 = a1 * sigmoid_fast(a1) * __uint_as_float(bv[j0 + 1]);
+              o[e] = pack_bf16x2(h0, h1);
+            }
+            *reinterpret_cast<uint4*>(hrow + sw128_offset(r, hh * 4 + q)) = make_uint4(o[0], o[1], o[2], o[3]);
+          }
+        }
+        tc_fence_before_sync();
+        fence_proxy_async_smem();
+        mbar_arrive(&d1_empty[b]);
+        mbar_arrive(&h_full[b]);
+      }
+      if ((it & 1) == grp) {
+        const int o = it & 1;
+        mbar_wait(&out_full[o], (it >> 1) & 1, 41);
+        tc_fence_after_sync();
+        const long long row = (long long)tile * 128 + r;
+        const bool valid = row < p.rows;
+        const uint8_t* xrow = static_cast<const uint8_t*>(p.x) + row * kD * zbytes<F32>();
+        uint8_t* orow = static_cast<uint8_t*>(p.out) + row * kD * zbytes<F32>();
+#pragma unroll 1
+        for (int c = 0; c < 4; ++c) {
+          uint32_t v[32];
+          tmem_ld_32x32(tmem_addr(tmem_base, quarter * 32, 256 + o * 128 + c * 32), v);
+          tmem_ld_wait();
+          if (valid) {
+#pragma unroll
+            for (int q = 0; q < 4; ++q) {
+              float zr[8];
+              if (p.add_residual) {
+                load8<F32>(xrow, c * 32 + q * 8, zr);
+              } else {
+#pragma unroll
+                for (int e = 0; e < 8; ++e) zr[e] = 0.f;
+              }
+#pragma unroll
+              for (int e = 0; e < 8; ++e) zr[e] += __uint_as_float(v[q * 8 + e]);
+              store8<F32>(orow, c * 32 + q * 8, zr);
+            }
+          }
+        }
+        tc_fence_before_sync();
+        mbar_arrive(&out_empty[o]);
+      }
+    }
+  }
+
+  tc_fence_before_sync();
+  __syncthreads();
+  if (warp == 16) {
+    __syncwarp();
+    tmem_dealloc(tmem_base, 512);
+  }
+}
+
+}  // namespace b200

@@ -1,0 +1,420 @@
+// Triangle multiplication, the two kernels either side of the per-channel
+// contraction (which is bmm_nt_kernel):
+//
+//   trimul_in_kernel   h = LN_in(z);  ab = mask * p_in(h) * sigmoid(g_in(h))
+//                      written channel-major, a[d][line][pos] / b[d][line][pos] (bf16, pitch Np),
+//                      so that the contraction reads K-major rows.  The product is computed
+//                      transposed -- weights are the M operand, the pair tile the N operand -- so
+//                      a TMEM lane is an output channel and each thread stores contiguous pairs.
+//   trimul_out_kernel  out = p_out(LN_out(t)) * sigmoid(g_out(LN_in(z))) [+ z]
+//                      reading t channel-major and writing the pair-major result.
+//
+// "line/pos": outgoing contracts the column index, a[d][i][k] = ab[i,k,d]; incoming contracts the
+// row index, a[d][i][k] = ab[k,i,d].  A tile is 128 consecutive `pos` on one `line`.
+#pragma once
+#include "row_tile.cuh"
+
+namespace b200 {
+
+struct TriMulInParams {
+  const void* z;           // [N][N][128] z stream (fp32 or bf16)
+  const uint8_t* mask;     // [N][N], non-zero = valid
+  const float* ln_w;
+  const float* ln_b;
+  __nv_bfloat16* a_out;    // [128][Np][Np]
+  __nv_bfloat16* b_out;
+  int N, Np;
+  int incoming;
+  int num_tiles;           // N * Np/128
+  float eps;
+};
+
+namespace trimul_in {
+constexpr uint32_t W_OFF = 0;                       // 4 M-tiles x 32 KB
+constexpr uint32_t X_OFF = 4 * kOperandTile;        // 2 stages x 32 KB
+constexpr uint32_t MASK_OFF = X_OFF + 2 * kOperandTile;  // 4 stages x 128 B
+constexpr uint32_t BAR_OFF = MASK_OFF + 4 * 128;
+constexpr uint32_t SMEM_BYTES = BAR_OFF + 128 + 1024;
+constexpr int THREADS = 416;  // warps 0-3 epilogue, 4-11 producers, 12 control
+}  // namespace trimul_in
+
+template <bool F32>
+__global__ void __launch_bounds__(416, 1)
+trimul_in_kernel(const __grid_constant__ CUtensorMap tmW, TriMulInParams p) {
+  using namespace trimul_in;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint64_t* w_full = reinterpret_cast<uint64_t*>(smem + BAR_OFF);
+  uint64_t* x_full = w_full + 1;     // [2]
+  uint64_t* x_empty = x_full + 2;    // [2]
+  uint64_t* acc_full = x_empty + 2;  // [2]  a-half, b-half
+  uint64_t* acc_empty = acc_full + 2;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_empty + 2);
+  uint8_t* mask_s = smem + MASK_OFF;
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const int tiles_per_line = p.Np >> 7;
+
+  if (threadIdx.x == 0) {
+    mbar_init(w_full, 1);
+    for (int i = 0; i < 2; ++i) {
+      mbar_init(&x_full[i], 256);
+      mbar_init(&x_empty[i], 1);
+      mbar_init(&acc_full[i], 1);
+      mbar_init(&acc_empty[i], 128);
+    }
+    fence_mbar_init();
+    prefetch_tmap(&tmW);
+  }
+  if (warp == 12) tmem_alloc(tmem_slot, 512);
+  tc_fence_before_sync();
+  __syncthreads();
+  tc_fence_after_sync();
+  const uint32_t tmem_base = *tmem_slot;
+
+  if (warp == 12) {
+    // ------------------------------------------------------------------ control
+    if (lane == 0) {
+      mbar_arrive_expect_tx(w_full, 4 * kOperandTile);
+      for (int mt = 0; mt < 4; ++mt)
+        for (int h = 0; h < 2; ++h)
+          tma_load_2d(smem + W_OFF + mt * kOperandTile + h * kOperandHalf, &tmW, w_full, h * 64, mt * 128);
+      mbar_wait(w_full, 0, 10);
+      constexpr uint32_t idesc = make_idesc_bf16(128, 128);
+      const uint32_t w_s = smem_u32(smem + W_OFF);
+      int it = 0;
+      for (int tile = blockIdx.x; tile < p.num_tiles; tile += gridDim.x, ++it) {
+        const int s = it & 1;
+        mbar_wait(&x_full[s], (it >> 1) & 1, 11);
+        tc_fence_after_sync();
+        const uint32_t x_s = smem_u32(smem + X_OFF + s * kOperandTile);
+        for (int half = 0; half < 2; ++half) {
+          mbar_wait(&acc_empty[half], (it & 1) ^ 1, 12);
+          tc_fence_after_sync();
+          for (int m2 = 0; m2 < 2; ++m2) {
+            const int mt = half * 2 + m2;
+            umma_k128(tmem_base + mt * 128, w_s + mt * kOperandTile, x_s, idesc, false);
+          }
+          umma_commit(&acc_full[half]);
+        }
+        umma_commit(&x_empty[s]);
+      }
+    }
+  } else if (warp >= 4) {
+    // ------------------------------------------------------------------ producers
+    const int pt = threadIdx.x - 128;  // 0..255
+    float gamma[8], beta[8];
+    load_gamma_beta(p.ln_w, p.ln_b, pt, gamma, beta);
+    const long long pos_stride = (p.incoming ? (long long)p.N * kD : kD) * (long long)zbytes<F32>();
+    const long long line_stride = (p.incoming ? kD : (long long)p.N * kD) * (long long)zbytes<F32>();
+    const long long mpos_stride = p.incoming ? p.N : 1;
+    const long long mline_stride = p.incoming ? 1 : p.N;
+    RowTile<256> regs;
+    uint8_t mreg = 0;
+    auto load_tile = [&](int tile) {
+      const int line = tile / tiles_per_line;
+      const int pos0 = (tile - line * tiles_per_line) << 7;
+      const uint8_t* base = static_cast<const uint8_t*>(p.z) + line * line_stride;
+      regs.template load<F32, true>(
+          pt,
+          [&](int r) -> const void* {
+            const int pos = pos0 + r;
+            return pos < p.N ? base + pos * pos_stride : nullptr;
+          },
+          gamma, beta, p.eps);
+      if (pt < 128) {
+        const int pos = pos0 + pt;
+        mreg = (pos < p.N) ? p.mask[line * mline_stride + pos * mpos_stride] : 0;
+      }
+    };
+    int it = 0;
+    int tile = blockIdx.x;
+    if (tile < p.num_tiles) load_tile(tile);
+    for (; tile < p.num_tiles; tile += gridDim.x, ++it) {
+      const int s = it & 1;
+      mbar_wait(&x_empty[s], ((it >> 1) & 1) ^ 1, 13);
+      regs.store_operand(pt, smem + X_OFF + s * kOperandTile);
+      if (pt < 128) mask_s[(it & 3) * 128 + pt] = mreg;
+      fence_proxy_async_smem();
+      mbar_arrive(&x_full[s]);
+      const int next = tile + gridDim.x;
+      if (next < p.num_tiles) load_tile(next);
+    }
+  } else {
+    // ------------------------------------------------------------------ epilogue
+    const int d = warp * 32 + lane;  // channel inside the half == TMEM lane
+    int it = 0;
+    for (int tile = blockIdx.x; tile < p.num_tiles; tile += gridDim.x, ++it) {
+      const int line = tile / tiles_per_line;
+      const int pos0 = (tile - line * tiles_per_line) << 7;
+      const uint32_t* msk = reinterpret_cast<const uint32_t*>(mask_s + (it & 3) * 128);
+      for (int half = 0; half < 2; ++half) {
+        mbar_wait(&acc_full[half], it & 1, 14);
+        tc_fence_after_sync();
+        __nv_bfloat16* dst = (half ? p.b_out : p.a_out) + ((long long)d * p.Np + line) * p.Np + pos0;
+#pragma unroll 1
+        for (int c = 0; c < 4; ++c) {
+          uint32_t pv[32], gv[32];
+          tmem_ld_32x32(tmem_addr(tmem_base, warp * 32, (half * 2) * 128 + c * 32), pv);
+          tmem_ld_32x32(tmem_addr(tmem_base, warp * 32, (half * 2 + 1) * 128 + c * 32), gv);
+          tmem_ld_wait();
+          uint32_t packed[16];
+#pragma unroll
+          for (int j = 0; j < 32; j += 2) {
+            const uint32_t m4 = msk[(c * 32 + j) >> 2];
+            const bool m0 = (m4 >> (((j)&3) * 8)) & 0xff;
+            const bool m1 = (m4 >> (((j + 1) & 3) * 8)) & 0xff;
+            const float v0 = m0 ? __uint_as_float(pv[j]) * sigmoid_fast(__uint_as_float(gv[j])) : 0.f;
+            const float v1 = m1 ? __uint_as_float(pv[j + 1]) * sigmoid_fast(__uint_as_float(gv[j + 1])) : 0.f;
+            packed[j >> 1] = pack_bf16x2(v0, v1);
+          }
+#pragma unroll
+          for (int g = 0; g < 4; ++g)
+            *reinterpret_cast<uint4*>(dst + c * 32 + g * 8) =
+                make_uint4(packed[g * 4], packed[g * 4 + 1], packed[g * 4 + 2], packed[g * 4 + 3]);
+        }
+        tc_fence_before_sync();
+        mbar_arrive(&acc_empty[half]);
+      }
+    }
+  }
+
+  tc_fence_before_sync();
+  __syncthreads();
+  if (warp == 12) {
+    __syncwarp();
+    tmem_dealloc(tmem_base, 512);
+  }
+}
+
+// ---------------------------------------------------------------------------------------------
+
+struct TriMulOutParams {
+  const void* z;           // [N][N][128]  z stream: input of the op (gate and, optionally, residual)
+  void* out;               // [N][N][128]  same dtype as z, may alias it
+  const float* ln_in_w;
+  const float* ln_in_b;
+  const float* ln_out_w;
+  const float* ln_out_b;
+  int N, Np;
+  int num_tiles;           // N * Np/128
+  int add_residual;
+  float eps;
+};
+
+namespace trimul_out {
+constexpr uint32_t W_OFF = 0;                          // p_out, g_out: 2 x 32 KB
+constexpr uint32_t T_OFF = 2 * kOperandTile;           // raw t tiles [128 d][128 j], 2 stages
+constexpr uint32_t A1_OFF = T_OFF + 2 * kOperandTile;  // LN_out(t) operand
+constexpr uint32_t A2_OFF = A1_OFF + kOperandTile;     // LN_in(z) operand
+constexpr uint32_t LN_OFF = A2_OFF + kOperandTile;     // gamma_out[128], beta_out[128] fp32
+constexpr uint32_t BAR_OFF = LN_OFF + 1024;
+constexpr uint32_t SMEM_BYTES = BAR_OFF + 128 + 1024;
+constexpr int THREADS = 544;  // warps 0-3 epilogue, 4-7 t transformers, 8-15 z producers, 16 control
+}  // namespace trimul_out
+
+template <bool F32>
+__global__ void __launch_bounds__(544, 1)
+trimul_out_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUtensorMap tmT,
+                  TriMulOutParams p) {
+  using namespace trimul_out;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint64_t* w_full = reinterpret_cast<uint64_t*>(smem + BAR_OFF);
+  uint64_t* t_full = w_full + 1;     // [2] TMA landed a raw t tile
+  uint64_t* t_empty = t_full + 2;    // [2] transformers are done with it
+  uint64_t* a1_full = t_empty + 2;   // LN_out(t) operand written
+  uint64_t* a2_full = a1_full + 1;   // LN_in(z) operand written
+  uint64_t* a_empty = a2_full + 1;   // both operands consumed by the MMAs
+  uint64_t* acc_full = a_empty + 1;  // [2]
+  uint64_t* acc_empty = acc_full + 2;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_empty + 2);
+  float* ln_s = reinterpret_cast<float*>(smem + LN_OFF);
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const int tiles_per_line = p.Np >> 7;
+
+  if (threadIdx.x == 0) {
+    mbar_init(w_full, 1);
+    for (int i = 0; i < 2; ++i) {
+      mbar_init(&t_full[i], 1);
+      mbar_init(&t_empty[i], 128);
+      mbar_init(&acc_full[i], 1);
+      mbar_init(&acc_empty[i], 128);
+    }
+    mbar_init(a1_full, 128);
+    mbar_init(a2_full, 256);
+    mbar_init(a_empty, 1);
+    fence_mbar_init();
+    prefetch_tmap(&tmW);
+    prefetch_tmap(&tmT);
+  }
+  if (threadIdx.x < 128) {
+    ln_s[threadIdx.x] = p.ln_out_w[threadIdx.x];
+    ln_s[128 + threadIdx.x] = p.ln_out_b[threadIdx.x];
+  }
+  if (warp == 16) tmem_alloc(tmem_slot, 512);
+  tc_fence_before_sync();
+  __syncthreads();
+  tc_fence_after_sync();
+  const uint32_t tmem_base = *tmem_slot;
+
+  if (warp == 16) {
+    // ------------------------------------------------------------------ control: TMA + MMA
+    if (lane == 0) {
+      mbar_arrive_expect_tx(w_full, 2 * kOperandTile);
+      for (int mt = 0; mt < 2; ++mt)
+        for (int h = 0; h < 2; ++h)
+          tma_load_2d(smem + W_OFF + mt * kOperandTile + h * kOperandHalf, &tmW, w_full, h * 64, mt * 128);
+      auto issue_t = [&](int tile, int s) {
+        const int line = tile / tiles_per_line;
+        const int pos0 = (tile - line * tiles_per_line) << 7;
+        mbar_arrive_expect_tx(&t_full[s], kOperandTile);
+        tma_load_3d(smem + T_OFF + s * kOperandTile, &tmT, &t_full[s], pos0, line, 0);
+      };
+      // prologue: first two t tiles in flight
+      int tile = blockIdx.x;
+      if (tile < p.num_tiles) issue_t(tile, 0);
+      if (tile + (int)gridDim.x < p.num_tiles) issue_t(tile + gridDim.x, 1);
+      mbar_wait(w_full, 0, 20);
+      constexpr uint32_t idesc = make_idesc_bf16(128, 128);
+      const uint32_t w_s = smem_u32(smem + W_OFF);
+      const uint32_t a1_s = smem_u32(smem + A1_OFF);
+      const uint32_t a2_s = smem_u32(smem + A2_OFF);
+      int it = 0;
+      for (; tile < p.num_tiles; tile += gridDim.x, ++it) {
+        const int acc = it & 1;
+        mbar_wait(&acc_empty[acc], ((it >> 1) & 1) ^ 1, 21);
+        mbar_wait(a1_full, it & 1, 22);
+        mbar_wait(a2_full, it & 1, 23);
+        tc_fence_after_sync();
+        umma_k128(tmem_base + acc * 256, a1_s, w_s, idesc, false);                       // p_out(LN_out(t))
+        umma_k128(tmem_base + acc * 256 + 128, a2_s, w_s + kOperandTile, idesc, false);  // g_out(LN_in(z))
+        umma_commit(a_empty);
+        umma_commit(&acc_full[acc]);
+        // refill the raw-t stage this tile used, once the transformers have released it
+        const int next2 = tile + 2 * gridDim.x;
+        if (next2 < p.num_tiles) {
+          mbar_wait(&t_empty[it & 1], (it >> 1) & 1, 24);
+          issue_t(next2, it & 1);
+        }
+      }
+    }
+  } else if (warp >= 4 && warp < 8) {
+    // ------------------------------------------------------------------ t transformers
+    // thread j owns pair column j of the raw tile [d][j]; LayerNorm over d, written as row j of A1.
+    const int j = threadIdx.x - 128;
+    int it = 0;
+    for (int tile = blockIdx.x; tile < p.num_tiles; tile += gridDim.x, ++it) {
+      const int s = it & 1;
+      mbar_wait(&t_full[s], (it >> 1) & 1, 25);
+      const __nv_bfloat16* traw = reinterpret_cast<const __nv_bfloat16*>(smem + T_OFF + s * kOperandTile) + j;
+      const float shift = __bfloat162float(traw[0]);
+      float sum = 0.f, sq = 0.f;
+#pragma unroll 8
+      for (int d = 0; d < kD; ++d) {
+        const float x = __bfloat162float(traw[d * 128]) - shift;
+        sum += x;
+        sq = fmaf(x, x, sq);
+      }
+      const float mean_s = sum * (1.0f / kD);
+      const float var = fmaxf(sq * (1.0f / kD) - mean_s * mean_s, 0.f);
+      const float rstd = rsqrtf(var + p.eps);
+      const float mean = mean_s + shift;
+      mbar_wait(a_empty, (it & 1) ^ 1, 26);
+      uint8_t* a1 = smem + A1_OFF;
+#pragma unroll 2
+      for (int c = 0; c < 16; ++c) {
+        float y[8];
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+          const int d = c * 8 + i;
+          y[i] = fmaf((__bfloat162float(traw[d * 128]) - mean) * rstd, ln_s[d], ln_s[128 + d]);
+        }
+        uint4 o = make_uint4(pack_bf16x2(y[0], y[1]), pack_bf16x2(y[2], y[3]), pack_bf16x2(y[4], y[5]),
+                             pack_bf16x2(y[6], y[7]));
+        *reinterpret_cast<uint4*>(a1 + (c >> 3) * kOperandHalf + sw128_offset(j, c & 7)) = o;
+      }
+      fence_proxy_async_smem();
+      mbar_arrive(a1_full);
+      mbar_arrive(&t_empty[s]);
+    }
+  } else if (warp >= 8) {
+    // ------------------------------------------------------------------ z producers: LN_in(z) -> A2
+    const int pt = threadIdx.x - 256;  // 0..255
+    float gamma[8], beta[8];
+    load_gamma_beta(p.ln_in_w, p.ln_in_b, pt, gamma, beta);
+    RowTile<256> regs;
+    auto load_tile = [&](int tile) {
+      const int line = tile / tiles_per_line;
+      const int pos0 = (tile - line * tiles_per_line) << 7;
+      const uint8_t* base = static_cast<const uint8_t*>(p.z) + ((long long)line * p.N + pos0) * kD * zbytes<F32>();
+      regs.template load<F32, true>(
+          pt,
+          [&](int r) -> const void* { return (pos0 + r) < p.N ? base + (long long)r * kD * zbytes<F32>() : nullptr; },
+          gamma, beta, p.eps);
+    };
+    int it = 0;
+    int tile = blockIdx.x;
+    if (tile < p.num_tiles) load_tile(tile);
+    for (; tile < p.num_tiles; tile += gridDim.x, ++it) {
+      mbar_wait(a_empty, (it & 1) ^ 1, 27);
+      regs.store_operand(pt, smem + A2_OFF);
+      fence_proxy_async_smem();
+      mbar_arrive(a2_full);
+      const int next = tile + gridDim.x;
+      if (next < p.num_tiles) load_tile(next);
+    }
+  } else {
+    // ------------------------------------------------------------------ epilogue
+    const int r = warp * 32 + lane;  // pair row of the tile == TMEM lane
+    int it = 0;
+    for (int tile = blockIdx.x; tile < p.num_tiles; tile += gridDim.x, ++it) {
+      const int line = tile / tiles_per_line;
+      const int pos0 = (tile - line * tiles_per_line) << 7;
+      const int acc = it & 1;
+      const bool valid = (pos0 + r) < p.N;
+      const long long off = ((long long)line * p.N + pos0 + r) * kD * zbytes<F32>();
+      const uint8_t* zrow = static_cast<const uint8_t*>(p.z) + off;
+      uint8_t* orow = static_cast<uint8_t*>(p.out) + off;
+      mbar_wait(&acc_full[acc], (it >> 1) & 1, 28);
+      tc_fence_after_sync();
+#pragma unroll 1
+      for (int c = 0; c < 4; ++c) {
+        uint32_t pv[32], gv[32];
+        tmem_ld_32x32(tmem_addr(tmem_base, warp * 32, acc * 256 + c * 32), pv);
+        tmem_ld_32x32(tmem_addr(tmem_base, warp * 32, acc * 256 + 128 + c * 32), gv);
+        tmem_ld_wait();
+        if (valid) {
+#pragma unroll
+          for (int g = 0; g < 4; ++g) {
+            float zr[8];
+            if (p.add_residual) {
+              load8<F32>(zrow, c * 32 + g * 8, zr);
+            } else {
+#pragma unroll
+              for (int e = 0; e < 8; ++e) zr[e] = 0.f;
+            }
+#pragma unroll
+            for (int e = 0; e < 8; ++e)
+              zr[e] = fmaf(__uint_as_float(pv[g * 8 + e]), sigmoid_fast(__uint_as_float(gv[g * 8 + e])), zr[e]);
+            store8<F32>(orow, c * 32 + g * 8, zr);
+          }
+        }
+      }
+      tc_fence_before_sync();
+      mbar_arrive(&acc_empty[acc]);
+    }
+  }
+
+  tc_fence_before_sync();
+  __syncthreads();
+  if (warp == 16) {
+    __syncwarp();
+    tmem_dealloc(tmem_base, 512);
+  }
+}
+
+}  // namespace b200

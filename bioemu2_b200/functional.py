@@ -1,0 +1,167 @@
+"""Tensor-level entry points: torch tensors in, the C ABI underneath.
+
+Every function runs on the current CUDA stream, allocates only through torch's caching allocator
+(outputs and the shared scratch buffer) and raises ``ValueError`` for bad shapes, as the reference's
+modules do, before anything is launched.
+"""
+from __future__ import annotations
+
+import ctypes
+
+import torch
+from torch import Tensor
+
+from . import _lib
+from ._lib import lib
+
+_WORKSPACES: dict[tuple[int, int], Tensor] = {}
+
+
+def _stream() -> int:
+    return torch.cuda.current_stream().cuda_stream
+
+
+def workspace(nbytes: int, device: torch.device) -> Tensor:
+    """Scratch buffer shared by all ops on (device, stream); grown on demand, 1024-byte aligned."""
+    key = (device.index if device.index is not None else torch.cuda.current_device(), _stream())
+    buf = _WORKSPACES.get(key)
+    if buf is None or buf.numel() < nbytes + 1024:
+        buf = torch.empty(nbytes + 1024, dtype=torch.uint8, device=device)
+        _WORKSPACES[key] = buf
+    off = (-buf.data_ptr()) % 1024
+    return buf[off:off + nbytes]
+
+
+def release_workspaces() -> None:
+    _WORKSPACES.clear()
+
+
+def _zdtype(t: Tensor) -> int:
+    if t.dtype == torch.float32:
+        return _lib.DTYPE_F32
+    if t.dtype == torch.bfloat16:
+        return _lib.DTYPE_BF16
+    raise ValueError(f"pair tensor must be float32 or bfloat16, got {t.dtype}")
+
+
+def mask_u8(mask: Tensor) -> Tensor:
+    """Masks travel as one byte per entry, non-zero = valid (bool tensors are reinterpreted, not copied)."""
+    if mask.dtype == torch.uint8:
+        return mask.contiguous()
+    if mask.dtype == torch.bool:
+        return mask.contiguous().view(torch.uint8)
+    return (mask != 0).to(torch.uint8).contiguous()
+
+
+def _require_cuda(*tensors: Tensor) -> None:
+    for t in tensors:
+        if not t.is_cuda:
+            raise RuntimeError("bioemu2_b200 runs on CUDA tensors only (there is no CPU path)")
+
+
+def layernorm(x: Tensor, weight: Tensor | None, bias: Tensor | None, eps: float = 1e-5) -> Tensor:
+    _require_cuda(x)
+    if x.dtype != torch.bfloat16:
+        raise ValueError("layernorm expects bfloat16 rows")
+    x = x.contiguous()
+    cols = x.shape[-1]
+    y = torch.empty_like(x)
+    w = weight.float().contiguous() if weight is not None else None
+    b = bias.float().contiguous() if bias is not None else None
+    _lib.check(lib.b200_layernorm_fwd(x.data_ptr(), y.data_ptr(), w.data_ptr() if w is not None else None,
+                                      b.data_ptr() if b is not None else None, x.numel() // cols, cols, eps,
+                                      _stream()))
+    return y
+
+
+def bmm_nt(a: Tensor, b: Tensor, scale: float = 1.0) -> Tensor:
+    """c[n] = scale * a[n] @ b[n].T for bf16 a[batch, M, K], b[batch, N, K]."""
+    _require_cuda(a, b)
+    if a.dtype != torch.bfloat16 or b.dtype != torch.bfloat16:
+        raise ValueError("bmm_nt expects bfloat16 operands")
+    if a.ndim != 3 or b.ndim != 3 or a.shape[0] != b.shape[0] or a.shape[2] != b.shape[2]:
+        raise ValueError(f"bmm_nt shapes {tuple(a.shape)} x {tuple(b.shape)}")
+    a, b = a.contiguous(), b.contiguous()
+    batch, M, K = a.shape
+    N = b.shape[1]
+    c = torch.empty(batch, M, N, dtype=torch.bfloat16, device=a.device)
+    _lib.check(lib.b200_bmm_nt_bf16(a.data_ptr(), b.data_ptr(), c.data_ptr(), batch, M, N, K, K, K, N, M * K, N * K,
+                                    M * N, scale, _stream()))
+    return c
+
+
+class TriMulPacked:
+    """Device copies of the triangle-multiplication weights in the layouts ``b200_trimul_fwd`` expects."""
+
+    def __init__(self, norm_in_w, norm_in_b, p_in, g_in, norm_out_w, norm_out_b, p_out, g_out):
+        D = p_out.shape[0]
+        if D != 128 or tuple(p_in.shape) != (256, 128):
+            raise ValueError("the triangle-multiplication kernels are built for dim=128")
+        bf = torch.bfloat16
+        self.w_in = torch.cat([p_in[:D], g_in[:D], p_in[D:], g_in[D:]], dim=0).to(bf).contiguous()
+        self.w_out = torch.cat([p_out, g_out], dim=0).to(bf).contiguous()
+        self.ln = [t.detach().float().contiguous() for t in (norm_in_w, norm_in_b, norm_out_w, norm_out_b)]
+        self.struct = _lib.TriMulWeights(self.w_in.data_ptr(), self.w_out.data_ptr(), *[t.data_ptr() for t in self.ln])
+
+
+def trimul(x: Tensor, mask: Tensor, w: TriMulPacked, incoming: bool, add_residual: bool = False,
+           out: Tensor | None = None) -> Tensor:
+    """Triangle multiplication of ``x[B,N,N,128]`` (fp32 or bf16); ``out`` may be ``x`` itself."""
+    _require_cuda(x, mask)
+    if x.ndim != 4 or x.shape[1] != x.shape[2] or x.shape[3] != 128:
+        raise ValueError(f"expected x[B,N,N,128], got {tuple(x.shape)}")
+    if tuple(mask.shape) != tuple(x.shape[:3]):
+        raise ValueError(f"mask shape {tuple(mask.shape)} does not match x {tuple(x.shape)}")
+    zd = _zdtype(x)
+    if not x.is_contiguous():
+        if out is x:
+            raise ValueError("in-place update needs a contiguous pair tensor")
+        x = x.contiguous()
+    if out is None:
+        out = torch.empty_like(x)
+    elif out.dtype != x.dtype or out.shape != x.shape or not out.is_contiguous():
+        raise ValueError("out must match x in shape and dtype and be contiguous")
+    m8 = mask_u8(mask)
+    B, N = x.shape[0], x.shape[1]
+    nbytes = lib.b200_trimul_workspace_bytes(N)
+    ws = workspace(nbytes, x.device)
+    _lib.check(lib.b200_trimul_fwd(x.data_ptr(), m8.data_ptr(), out.data_ptr(), ctypes.byref(w.struct), B, N,
+                                   1 if incoming else 0, 1 if add_residual else 0, zd, ws.data_ptr(), nbytes,
+                                   _stream()))
+    return out
+
+
+class TransitionPacked:
+    """Weights of a 128 -> 512 -> 128 SwiGLU transition in the layout ``b200_transition_fwd`` expects."""
+
+    def __init__(self, norm_w, norm_b, fc1, fc2, fc3):
+        if tuple(fc1.shape) != (512, 128) or tuple(fc3.shape) != (128, 512):
+            raise ValueError("the fused pair-transition kernel is built for dim=128, hidden=512")
+        bf = torch.bfloat16
+        w13 = torch.cat([fc1.reshape(8, 64, 128), fc2.reshape(8, 64, 128)], dim=1)  # [8][128][128]
+        self.w13 = w13.reshape(1024, 128).to(bf).contiguous()
+        self.w3 = fc3.to(bf).contiguous()
+        self.norm_w = norm_w.detach().float().contiguous() if norm_w is not None else None
+        self.norm_b = norm_b.detach().float().contiguous() if norm_b is not None else None
+
+
+def transition(x: Tensor, w: TransitionPacked, add_residual: bool = False, out: Tensor | None = None) -> Tensor:
+    _require_cuda(x)
+    if x.shape[-1] != 128:
+        raise ValueError(f"expected x[..., 128], got {tuple(x.shape)}")
+    zd = _zdtype(x)
+    if not x.is_contiguous():
+        if out is x:
+            raise ValueError("in-place update needs a contiguous tensor")
+        x = x.contiguous()
+    if out is None:
+        out = torch.empty_like(x)
+    elif out.dtype != x.dtype or out.shape != x.shape or not out.is_contiguous():
+        raise ValueError("out must match x in shape and dtype and be contiguous")
+    rows = x.numel() // 128
+    use_norm = w.norm_w is not None
+    _lib.check(lib.b200_transition_fwd(x.data_ptr(), out.data_ptr(), w.w13.data_ptr(), w.w3.data_ptr(),
+                                       w.norm_w.data_ptr() if use_norm else None,
+                                       w.norm_b.data_ptr() if use_norm else None, rows, 1 if use_norm else 0,
+                                       1 if add_residual else 0, zd, _stream()))
+    return out

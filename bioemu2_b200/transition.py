@@ -1,0 +1,42 @@
+"""SwiGLU transition with the reference's contract (src/bioemu2/biomoa/ops/transition.py:17-91).
+
+``fc3(silu(fc1(norm(x))) * fc2(norm(x)))``.  ``chunk_size`` exists in the reference to bound the
+memory of the hidden activations; the fused kernel never materialises them, so it is accepted and
+ignored.  The fused kernel covers the pair transition (dim 128, hidden 512).
+"""
+from __future__ import annotations
+
+import torch.nn as nn
+from torch import Tensor
+
+from . import functional as F
+from .triangle_multiplication import PackedWeightsMixin
+
+
+class Transition(PackedWeightsMixin, nn.Module):
+    def __init__(self, dim: int, hidden: int, out_dim: int | None = None, use_norm: bool = True,
+                 chunk_size: int | None = None) -> None:
+        super().__init__()
+        out_dim = out_dim or dim
+        self.use_norm = use_norm
+        self.chunk_size = chunk_size
+        if use_norm:
+            self.norm = nn.LayerNorm(dim, eps=1e-5)
+        self.fc1 = nn.Linear(dim, hidden, bias=False)
+        self.fc2 = nn.Linear(dim, hidden, bias=False)
+        self.fc3 = nn.Linear(hidden, out_dim, bias=False)
+        self.hidden = hidden
+        if (dim, hidden, out_dim) != (128, 512, 128):
+            raise ValueError("bioemu2_b200.Transition currently covers dim=128, hidden=512 (the pair transition)")
+
+    def _build_packed(self):
+        return F.TransitionPacked(self.norm.weight if self.use_norm else None,
+                                  self.norm.bias if self.use_norm else None,
+                                  self.fc1.weight, self.fc2.weight, self.fc3.weight)
+
+    def forward(self, x: Tensor) -> Tensor:
+        return F.transition(x, self.packed())
+
+    def forward_residual_(self, x: Tensor) -> Tensor:
+        """``x += forward(x)`` in place, fused into the kernel's final store; returns ``x``."""
+        return F.transition(x, self.packed(), add_residual=True, out=x)

@@ -1,0 +1,126 @@
+/*
+ * b200pair -- C ABI of the B200 (sm_100a) kernels for the pair-representation hot path.
+ *
+ * The reference project is pure PyTorch: its seam for this path is the nn.Module contract of the ops
+ * (there is no FFI to mirror), so each entry point below names the reference module method whose
+ * arithmetic it replaces.  Conventions shared by all entry points:
+ *
+ *   - every pointer is a DEVICE pointer borrowed for the duration of the call, unless it says "host";
+ *   - work is enqueued on `stream` (a cudaStream_t passed as void*); nothing synchronises;
+ *   - nothing is allocated: scratch comes from the caller (`*_workspace_bytes` says how much);
+ *   - activations are bf16, LayerNorm parameters fp32, projection weights bf16 in the packed layouts
+ *     described per function (the Python modules in bioemu2_b200/ build them from the reference's
+ *     state_dict tensors);
+ *   - the return value is a status code (B200_OK == 0); b200_last_error() gives the message of the
+ *     calling thread's last failure.  No exception crosses the boundary.
+ *   - kernels bound every wait; if one runs out the kernel finishes with wrong data and
+ *     b200_device_status() reports it.
+ */
+#ifndef B200PAIR_H_
+#define B200PAIR_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define B200_OK 0
+#define B200_ERR_INVALID_ARGUMENT 1
+#define B200_ERR_CUDA 2
+#define B200_ERR_UNSUPPORTED_DEVICE 3
+#define B200_ERR_WORKSPACE 4
+#define B200_ERR_DEVICE_WAIT 5
+
+typedef void* b200_stream_t; /* cudaStream_t */
+
+/* Element type of the pair tensor ("z stream") an entry point reads and writes.  The reference keeps the
+ * pair tensor in fp32 even under bf16 autocast (the residual adds promote), so fp32 is the trunk's type;
+ * bf16 serves callers that hold a bf16 pair tensor.  Arithmetic is the same for both: bf16 tensor-core
+ * operands, fp32 accumulation, fp32 LayerNorm / gating / residual. */
+#define B200_DTYPE_BF16 0
+#define B200_DTYPE_F32 1
+
+/* Library version (major*100 + minor). */
+int b200_version(void);
+
+/* Message of the calling thread's most recent failure ("" if none). */
+const char* b200_last_error(void);
+
+/* Checks that the current device is compute capability 10.x.  Every compute entry point calls it. */
+int b200_check_device(void);
+
+/* Synchronises the device, then reads and clears the device status word into *status (host pointer).
+ * 0 = every kernel wait completed; otherwise low byte 1 = a bounded wait ran out, bits 8.. = its site. */
+int b200_device_status(int* status);
+
+/* ---------------------------------------------------------------------------------------------------
+ * Row LayerNorm: y[r,:] = (x[r,:] - mean) * rsqrt(var + eps) * w + b over `cols` (multiple of 8, <= 1024).
+ * Replaces torch.nn.LayerNorm as used by norm_in / norm_s / norm_z
+ * (src/bioemu2/biomoa/ops/triangle_multiplication.py:71, attention_pair_bias.py:85,90).
+ * w or b may be NULL (no scale / no shift).
+ * ------------------------------------------------------------------------------------------------- */
+int b200_layernorm_fwd(const void* x, void* y, const float* w, const float* b, int64_t rows, int cols, float eps,
+                       b200_stream_t stream);
+
+/* ---------------------------------------------------------------------------------------------------
+ * Batched C[b] = scale * A[b] * B[b]^T, bf16 in / bf16 out, fp32 accumulation on the tensor cores.
+ * A: [batch][M][K] (row pitch lda elements), B: [batch][N][K] (pitch ldb), C: [batch][M][N] (pitch ldc).
+ * Pitches and batch strides are in elements and must be multiples of 8; N multiple of 8.
+ * Replaces the per-channel einsum of TriangleMultiplicationFull.forward
+ * (src/bioemu2/biomoa/ops/triangle_multiplication.py:94-98) and the MSA-depth contraction of
+ * OuterProductMeanVanilla.forward (src/bioemu2/biomoa/ops/outer_product_mean.py:71).
+ * ------------------------------------------------------------------------------------------------- */
+int b200_bmm_nt_bf16(const void* A, const void* B, void* C, int batch, int M, int N, int K, int64_t lda,
+                     int64_t ldb, int64_t ldc, int64_t a_batch_stride, int64_t b_batch_stride,
+                     int64_t c_batch_stride, float scale, b200_stream_t stream);
+
+/* ---------------------------------------------------------------------------------------------------
+ * Triangle multiplication, TriangleMultiplicationFull.forward
+ * (src/bioemu2/biomoa/ops/triangle_multiplication.py:86-99; weights :62-76), c_z = 128.
+ *
+ *   w_in   bf16 [512][128]: rows 0..127 = p_in.weight[0:128], 128..255 = g_in.weight[0:128],
+ *                           256..383 = p_in.weight[128:256], 384..511 = g_in.weight[128:256]
+ *   w_out  bf16 [256][128]: rows 0..127 = p_out.weight, 128..255 = g_out.weight
+ *   ln_*   fp32 [128]
+ *
+ * z, out: [B][N][N][128] of `z_dtype`; mask: uint8 [B][N][N] (non-zero = valid).  `out` may alias `z`.
+ * incoming: 0 = outgoing ("bikd,bjkd->bijd"), 1 = incoming ("bkid,bkjd->bijd").
+ * add_residual: 0 returns the update as the reference op does; 1 returns z + update, which is what
+ * PairMixerLayer.forward does with it (src/bioemu2/biomoa/modules/pairmixer.py:447-452).
+ * Workspace: b200_trimul_workspace_bytes(N) bytes, 1024-byte aligned.
+ * ------------------------------------------------------------------------------------------------- */
+typedef struct {
+  const void* w_in;
+  const void* w_out;
+  const float* ln_in_w;
+  const float* ln_in_b;
+  const float* ln_out_w;
+  const float* ln_out_b;
+} b200_trimul_weights;
+
+size_t b200_trimul_workspace_bytes(int N);
+
+int b200_trimul_fwd(const void* z, const uint8_t* mask, void* out, const b200_trimul_weights* w, int B, int N,
+                    int incoming, int add_residual, int z_dtype, void* workspace, size_t workspace_bytes,
+                    b200_stream_t stream);
+
+/* ---------------------------------------------------------------------------------------------------
+ * Pair transition, Transition.forward (src/bioemu2/biomoa/ops/transition.py:52-76) for dim 128, hidden 512:
+ * out = fc3(silu(fc1(h)) * fc2(h)) [+ x], h = LayerNorm(x) when use_norm else x.
+ *
+ *   w13  bf16 [1024][128]: for hidden chunk c = 0..7, rows c*128 + 0..63 = fc1.weight[c*64 + 0..63],
+ *                          rows c*128 + 64..127 = fc2.weight[c*64 + 0..63]
+ *   w3   bf16 [128][512] = fc3.weight
+ *
+ * x, out: [rows][128] of `x_dtype`; `out` may alias `x`.
+ * ------------------------------------------------------------------------------------------------- */
+int b200_transition_fwd(const void* x, void* out, const void* w13, const void* w3, const float* ln_w,
+                        const float* ln_b, int64_t rows, int use_norm, int add_residual, int x_dtype,
+                        b200_stream_t stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* B200PAIR_H_ */

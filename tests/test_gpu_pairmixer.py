@@ -1,0 +1,54 @@
+"""PairMixer layer / module on the GPU against the golden vectors and the CPU oracle."""
+import os
+import sys
+
+import pytest
+import torch
+
+sys.path.insert(0, os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden"))
+import cases as C  # noqa: E402
+import helpers as H  # noqa: E402
+from gpu_util import assert_close  # noqa: E402
+from oracle import pair_ops as O  # noqa: E402
+
+pytestmark = pytest.mark.gpu
+
+
+def test_pairmixer_layer_golden():
+    import bioemu2_b200 as b
+
+    golden = torch.load(C.GOLDEN_PATH)
+    case = C.CASES["pairmixer_layer"]()
+    layer = b.PairMixerLayer(384, 128).eval()
+    layer.load_state_dict(case["w"], strict=True)
+    layer.cuda()
+    z = case["z"].cuda()
+    z_before = z.clone()
+    s = torch.zeros(1, z.shape[1], 384, device="cuda")
+    with torch.no_grad():
+        s_out, z_out = layer(s, z, case["pair_mask"].cuda())
+    assert s_out is s
+    assert torch.equal(z, z_before), "forward must not modify its input"
+    valid = case["pair_mask"][0]
+    assert_close("pairmixer_layer_golden", z_out[0][valid.cuda()], golden["pairmixer_layer"]["output"][0][valid])
+
+
+def test_pairmixer_module_4_blocks_vs_oracle():
+    import bioemu2_b200 as b
+
+    N, L = 72, 4
+    g = torch.Generator().manual_seed(31)
+    w = {}
+    for i in range(L):
+        w.update(H.prefixed(f"layers.{i}", H.pairmixer_layer_weights(g, 128, perturbed=False)))
+    z = torch.randn(1, N, N, 128, generator=g)
+    tok = torch.ones(1, N, dtype=torch.bool)
+    tok[0, N - 7:] = False
+    pm = tok[:, :, None] & tok[:, None, :]
+    ref = O.pairmixer_module(z, pm, w, L)
+    mod = b.PairMixerModule(384, 128, L).eval()
+    mod.load_state_dict(w, strict=True)
+    mod.cuda()
+    with torch.no_grad():
+        _, out = mod(torch.zeros(1, N, 384, device="cuda"), z.cuda(), pm.cuda())
+    assert_close("pairmixer_module_4", out[0][pm[0].cuda()], ref[0][pm[0]])
