@@ -2,6 +2,12 @@
 ``nn.Module`` contracts.  Importing the package loads the CUDA library; without it the import fails."""
 from . import _lib  # noqa: F401  (fails loudly when the library is not built)
 from . import functional
+from .attention_pair_bias import AttentionPairBias
+from .outer_product_mean import (
+    OuterProductMean,
+    OuterProductMeanTritonMemorySaving,
+    OuterProductMeanVanilla,
+)
 from .pairmixer import PairMixerLayer, PairMixerModule
 from .transition import Transition
 from .triangle_multiplication import (
@@ -12,6 +18,10 @@ from .triangle_multiplication import (
 
 __all__ = [
     "functional",
+    "AttentionPairBias",
+    "OuterProductMean",
+    "OuterProductMeanTritonMemorySaving",
+    "OuterProductMeanVanilla",
     "PairMixerLayer",
     "PairMixerModule",
     "Transition",

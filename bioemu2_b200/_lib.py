@@ -33,6 +33,15 @@ class TriMulWeights(Structure):
     ]
 
 
+class OpmWeights(Structure):
+    _fields_ = [("w_ab", c_void_p), ("w_o", c_void_p), ("ln_w", c_void_p), ("ln_b", c_void_p), ("bias_o", c_void_p)]
+
+
+class ApbWeights(Structure):
+    _fields_ = [("w_qkg", c_void_p), ("b_qkg", c_void_p), ("w_v", c_void_p), ("w_z", c_void_p), ("ln_z_w", c_void_p),
+                ("ln_z_b", c_void_p), ("ln_s_w", c_void_p), ("ln_s_b", c_void_p), ("w_o", c_void_p)]
+
+
 # name -> (restype, argtypes); mirrors include/b200pair.h one to one
 SIGNATURES = {
     "b200_version": (c_int, []),
@@ -47,6 +56,12 @@ SIGNATURES = {
                                 c_int, c_void_p, c_size_t, c_void_p]),
     "b200_transition_fwd": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_int,
                                     c_int, c_int, c_void_p]),
+    "b200_opm_workspace_bytes": (c_size_t, [c_int, c_int]),
+    "b200_opm_fwd": (c_int, [c_void_p, c_void_p, c_int, c_void_p, POINTER(OpmWeights), c_int, c_int, c_int, c_int,
+                             c_int, c_void_p, c_size_t, c_void_p]),
+    "b200_apb_workspace_bytes": (c_size_t, [c_int, c_int, c_int, c_int, c_int]),
+    "b200_apb_fwd": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, POINTER(ApbWeights), c_int, c_int, c_int, c_int,
+                             c_int, c_int, c_int, c_void_p, c_size_t, c_void_p]),
 }
 
 if not os.path.exists(LIB_PATH):

@@ -8,18 +8,24 @@
 //   warp 1      MMA issuer     (tcgen05.mma 128 x BN x 16, two accumulator buffers in TMEM)
 //   warps 2..5  epilogue       (TMEM -> registers -> bf16 -> global)
 #pragma once
-#include "umma.cuh"
+#include "row_tile.cuh"
 
 namespace b200 {
 
 struct BmmParams {
-  __nv_bfloat16* C;
+  void* C;                   // bf16, or fp32 when out_f32
   long long c_batch_stride;  // elements
   int ldc;                   // elements
   int m_valid, n_valid;      // rows / columns of C that exist (n_valid % 8 == 0)
   int tiles_m, tiles_n, batch;
   int k_blocks;              // K / 64, rounded up (TMA zero-fills the tail)
   float scale;
+  const float* scale_ptr;    // optional per-batch device scalar multiplied into scale
+  const float* bias;         // optional per-column bias added after scaling
+  int out_f32;
+  // Outer-product store: with opm_ntok > 0, C row r = (i, c) and column q = (j, d) (c, d < 32) go to
+  // C[((i * opm_ntok + j) * 32 + c) * 32 + d]: every pair (i, j) gets its 32x32 outer product contiguous.
+  int opm_ntok;
 };
 
 template <int BN>
@@ -135,23 +141,36 @@ bmm_nt_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ C
       mbar_wait(&acc_full[acc], (it >> 1) & 1, 4);
       tc_fence_after_sync();
       const int row = tm * 128 + quarter * 32 + lane;
-      __nv_bfloat16* crow = p.C + (long long)b * p.c_batch_stride + (long long)row * p.ldc + tn * BN;
+      const float scale = p.scale_ptr ? p.scale * p.scale_ptr[b] : p.scale;
+      const size_t esz = p.out_f32 ? 4 : 2;
+      uint8_t* cbase = static_cast<uint8_t*>(p.C) + (long long)b * p.c_batch_stride * esz;
 #pragma unroll 1
       for (int c = 0; c < BN / 32; ++c) {
         uint32_t v[32];
         tmem_ld_32x32(tmem_addr(tmem_base, quarter * 32, acc * BN + c * 32), v);
         tmem_ld_wait();
         if (row < p.m_valid) {
+          const int col0 = tn * BN + c * 32;
+          long long off0;  // element offset of (row, col0)
+          if (p.opm_ntok > 0)
+            off0 = (((long long)(row >> 5) * p.opm_ntok + (col0 >> 5)) * 32 + (row & 31)) * 32;
+          else
+            off0 = (long long)row * p.ldc + col0;
 #pragma unroll
           for (int g = 0; g < 4; ++g) {
-            const int col = tn * BN + c * 32 + g * 8;
+            const int col = col0 + g * 8;
             if (col < p.n_valid) {
-              uint4 o;
-              o.x = pack_bf16x2(__uint_as_float(v[g * 8 + 0]) * p.scale, __uint_as_float(v[g * 8 + 1]) * p.scale);
-              o.y = pack_bf16x2(__uint_as_float(v[g * 8 + 2]) * p.scale, __uint_as_float(v[g * 8 + 3]) * p.scale);
-              o.z = pack_bf16x2(__uint_as_float(v[g * 8 + 4]) * p.scale, __uint_as_float(v[g * 8 + 5]) * p.scale);
-              o.w = pack_bf16x2(__uint_as_float(v[g * 8 + 6]) * p.scale, __uint_as_float(v[g * 8 + 7]) * p.scale);
-              *reinterpret_cast<uint4*>(crow + c * 32 + g * 8) = o;
+              float x[8];
+#pragma unroll
+              for (int e = 0; e < 8; ++e) x[e] = __uint_as_float(v[g * 8 + e]) * scale;
+              if (p.bias) {
+#pragma unroll
+                for (int e = 0; e < 8; ++e) x[e] += p.bias[col + e];
+              }
+              if (p.out_f32)
+                store8<true>(cbase + (off0 + g * 8) * 4, 0, x);
+              else
+                store8<false>(cbase + (off0 + g * 8) * 2, 0, x);
             }
           }
         }
@@ -163,7 +182,10 @@ bmm_nt_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ C
 
   tc_fence_before_sync();
   __syncthreads();
-  if (warp == 1) tmem_dealloc(tmem_base, 512);
+  if (warp == 1) {
+    __syncwarp();
+    tmem_dealloc(tmem_base, 512);
+  }
 }
 
 }  // namespace b200

@@ -1,6 +1,6 @@
 // HBM-bound row kernels: 128-bit loads and stores, one warp per row, fp32 statistics.
 #pragma once
-#include "umma.cuh"
+#include "row_tile.cuh"
 
 namespace b200 {
 
@@ -10,26 +10,42 @@ __device__ __forceinline__ float warp_sum(float x) {
   return x;
 }
 
-// y[r,:] = LN(x[r,:]) * w + b for bf16 rows of `cols` <= 1024 channels (multiple of 8).
+// y[r,:] = LN(x[r,:]) * w + b for rows of `cols` <= 1024 channels (multiple of 8); x fp32 or bf16, y bf16.
+// With normalize == 0 the rows are only converted to bf16.
+template <bool F32IN>
 __global__ void __launch_bounds__(256)
-layernorm_rows_kernel(const __nv_bfloat16* __restrict__ x, __nv_bfloat16* __restrict__ y,
+layernorm_rows_kernel(const void* __restrict__ x, __nv_bfloat16* __restrict__ y,
                       const float* __restrict__ w, const float* __restrict__ b, long long rows, int cols,
-                      float eps) {
+                      float eps, int normalize) {
   const int lane = threadIdx.x & 31;
   const int nvec = cols >> 3;
   const long long warp_global = (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
   const long long warp_stride = (long long)gridDim.x * (blockDim.x >> 5);
   const float inv = 1.0f / float(cols);
   for (long long r = warp_global; r < rows; r += warp_stride) {
-    const uint4* xr = reinterpret_cast<const uint4*>(x + r * cols);
+    const uint8_t* xr = static_cast<const uint8_t*>(x) + r * cols * (long long)(F32IN ? 4 : 2);
     uint4 v[4];
     float s = 0.f;
 #pragma unroll
     for (int i = 0; i < 4; ++i) {
       const int vi = lane + i * 32;
-      v[i] = (vi < nvec) ? __ldg(xr + vi) : make_uint4(0, 0, 0, 0);
-      s += bf16lo(v[i].x) + bf16hi(v[i].x) + bf16lo(v[i].y) + bf16hi(v[i].y) + bf16lo(v[i].z) + bf16hi(v[i].z) +
-           bf16lo(v[i].w) + bf16hi(v[i].w);
+      if (vi < nvec) {
+        float f[8];
+        load8<F32IN>(xr, vi * 8, f);
+        v[i] = make_uint4(pack_bf16x2(f[0], f[1]), pack_bf16x2(f[2], f[3]), pack_bf16x2(f[4], f[5]),
+                          pack_bf16x2(f[6], f[7]));
+#pragma unroll
+        for (int e = 0; e < 8; ++e) s += f[e];
+      } else {
+        v[i] = make_uint4(0, 0, 0, 0);
+      }
+    }
+    if (!normalize) {
+      uint4* yr0 = reinterpret_cast<uint4*>(y + r * cols);
+#pragma unroll
+      for (int i = 0; i < 4; ++i)
+        if (lane + i * 32 < nvec) yr0[lane + i * 32] = v[i];
+      continue;
     }
     const float mean = warp_sum(s) * inv;
     float ss = 0.f;

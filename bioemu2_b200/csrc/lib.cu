@@ -10,6 +10,8 @@
 #include "trimul.cuh"
 #include "transition.cuh"
 #include "elementwise.cuh"
+#include "opm.cuh"
+#include "attention.cuh"
 
 namespace b200 {
 
@@ -19,35 +21,50 @@ static int set_smem(Kernel k, uint32_t bytes) {
   return 0;
 }
 
-static int launch_bmm(const void* A, const void* B, void* C, int batch, int M, int N, int K, int64_t lda,
-                      int64_t ldb, int64_t ldc, int64_t sa, int64_t sb, int64_t sc, float scale,
-                      cudaStream_t stream) {
-  const int BN = (N % 256 == 0 || N > 1024) ? 256 : 128;
+struct BmmLaunch {
+  const void* A;
+  const void* B;
+  void* C;
+  int batch, M, N, K;
+  int64_t lda, ldb, ldc, sa, sb, sc;  // elements
+  float scale = 1.0f;
+  const float* scale_ptr = nullptr;
+  const float* bias = nullptr;
+  int out_f32 = 0;
+  int opm_ntok = 0;
+};
+
+static int launch_bmm(const BmmLaunch& a, cudaStream_t stream) {
+  const int BN = (a.N % 256 == 0 || a.N > 1024) ? 256 : 128;
   CUtensorMap tmA, tmB;
   {
-    const uint64_t dims[3] = {uint64_t(K), uint64_t(M), uint64_t(batch)};
-    const uint64_t str[2] = {uint64_t(lda) * 2, uint64_t(sa) * 2};
+    const uint64_t dims[3] = {uint64_t(a.K), uint64_t(a.M), uint64_t(a.batch)};
+    const uint64_t str[2] = {uint64_t(a.lda) * 2, uint64_t(a.sa > 0 ? a.sa : a.lda * a.M) * 2};
     const uint32_t box[3] = {64, 128, 1};
-    if (int e = make_tmap_bf16(&tmA, A, 3, dims, str, box, CU_TENSOR_MAP_SWIZZLE_128B)) return e;
+    if (int e = make_tmap_bf16(&tmA, a.A, 3, dims, str, box, CU_TENSOR_MAP_SWIZZLE_128B)) return e;
   }
   {
-    const uint64_t dims[3] = {uint64_t(K), uint64_t(N), uint64_t(batch)};
-    const uint64_t str[2] = {uint64_t(ldb) * 2, uint64_t(sb) * 2};
+    const uint64_t dims[3] = {uint64_t(a.K), uint64_t(a.N), uint64_t(a.batch)};
+    const uint64_t str[2] = {uint64_t(a.ldb) * 2, uint64_t(a.sb > 0 ? a.sb : a.ldb * a.N) * 2};
     const uint32_t box[3] = {64, uint32_t(BN), 1};
-    if (int e = make_tmap_bf16(&tmB, B, 3, dims, str, box, CU_TENSOR_MAP_SWIZZLE_128B)) return e;
+    if (int e = make_tmap_bf16(&tmB, a.B, 3, dims, str, box, CU_TENSOR_MAP_SWIZZLE_128B)) return e;
   }
   BmmParams p;
-  p.C = static_cast<__nv_bfloat16*>(C);
-  p.c_batch_stride = sc;
-  p.ldc = int(ldc);
-  p.m_valid = M;
-  p.n_valid = N;
-  p.tiles_m = (M + 127) / 128;
-  p.tiles_n = (N + BN - 1) / BN;
-  p.batch = batch;
-  p.k_blocks = (K + 63) / 64;
-  p.scale = scale;
-  const int total = p.tiles_m * p.tiles_n * batch;
+  p.C = a.C;
+  p.c_batch_stride = a.sc;
+  p.ldc = int(a.ldc);
+  p.m_valid = a.M;
+  p.n_valid = a.N;
+  p.tiles_m = (a.M + 127) / 128;
+  p.tiles_n = (a.N + BN - 1) / BN;
+  p.batch = a.batch;
+  p.k_blocks = (a.K + 63) / 64;
+  p.scale = a.scale;
+  p.scale_ptr = a.scale_ptr;
+  p.bias = a.bias;
+  p.out_f32 = a.out_f32;
+  p.opm_ntok = a.opm_ntok;
+  const int total = p.tiles_m * p.tiles_n * a.batch;
   const int grid = total < sm_count() ? total : sm_count();
   if (BN == 256) {
     if (int e = set_smem(bmm_nt_kernel<256>, BmmCfg<256>::SMEM_BYTES)) return e;
@@ -56,6 +73,103 @@ static int launch_bmm(const void* A, const void* B, void* C, int batch, int M, i
     if (int e = set_smem(bmm_nt_kernel<128>, BmmCfg<128>::SMEM_BYTES)) return e;
     bmm_nt_kernel<128><<<grid, 192, BmmCfg<128>::SMEM_BYTES, stream>>>(tmA, tmB, p);
   }
+  B200_CUDA(cudaGetLastError());
+  return 0;
+}
+
+static int launch_rows_to_bf16(const void* x, bool f32, __nv_bfloat16* y, const float* w, const float* b,
+                               int64_t rows, int cols, bool normalize, cudaStream_t stream) {
+  const int warps = 8;
+  int64_t blocks = (rows + warps - 1) / warps;
+  const int64_t cap = int64_t(sm_count()) * 16;
+  if (blocks > cap) blocks = cap;
+  if (blocks < 1) blocks = 1;
+  if (f32)
+    layernorm_rows_kernel<true><<<int(blocks), warps * 32, 0, stream>>>(x, y, w, b, rows, cols, 1e-5f, normalize);
+  else
+    layernorm_rows_kernel<false><<<int(blocks), warps * 32, 0, stream>>>(x, y, w, b, rows, cols, 1e-5f, normalize);
+  B200_CUDA(cudaGetLastError());
+  return 0;
+}
+
+// Describes where the attention core finds its operands (all bf16, device memory).
+struct FlashLaunch {
+  const void* qk;        // rows of `qk_width` columns; Q heads at q_col0 + h*DH, K heads at k_col0 + h*DH
+  int64_t qk_width;      // elements per row
+  int64_t qk_b_stride;   // elements between batch items
+  const void* vT;        // [Bt][H*DH][v_pitch]
+  int64_t v_pitch;
+  const void* bias;      // [groups*H][N][bias_pitch]
+  int64_t bias_pitch;
+  int bias_groups;
+  FlashParams p;
+};
+
+template <int DH>
+static int launch_flash_t(const FlashLaunch& a, cudaStream_t stream) {
+  using Cfg = FlashCfg<DH>;
+  const FlashParams& p0 = a.p;
+  CUtensorMap tmQ, tmV, tmB;
+  {
+    const uint64_t dims[3] = {uint64_t(a.qk_width), uint64_t(p0.N), uint64_t(p0.Bt)};
+    const uint64_t str[2] = {uint64_t(a.qk_width) * 2, uint64_t(a.qk_b_stride) * 2};
+    const uint32_t box[3] = {uint32_t(DH), 128, 1};
+    if (int e = make_tmap_bf16(&tmQ, a.qk, 3, dims, str, box,
+                               DH == 32 ? CU_TENSOR_MAP_SWIZZLE_64B : CU_TENSOR_MAP_SWIZZLE_128B))
+      return e;
+  }
+  {
+    const uint64_t dims[3] = {uint64_t(p0.N), uint64_t(p0.H) * DH, uint64_t(p0.Bt)};
+    const uint64_t str[2] = {uint64_t(a.v_pitch) * 2, uint64_t(a.v_pitch) * p0.H * DH * 2};
+    const uint32_t box[3] = {64, uint32_t(DH), 1};
+    if (int e = make_tmap_bf16(&tmV, a.vT, 3, dims, str, box, CU_TENSOR_MAP_SWIZZLE_128B)) return e;
+  }
+  {
+    const uint64_t dims[3] = {uint64_t(p0.N), uint64_t(p0.N), uint64_t(a.bias_groups) * p0.H};
+    const uint64_t str[2] = {uint64_t(a.bias_pitch) * 2, uint64_t(a.bias_pitch) * p0.N * 2};
+    const uint32_t box[3] = {64, 128, 1};
+    if (int e = make_tmap_bf16(&tmB, a.bias, 3, dims, str, box, CU_TENSOR_MAP_SWIZZLE_128B)) return e;
+  }
+  FlashParams p = p0;
+  p.nqt = (p.N + 127) / 128;
+  p.nkt = (p.N + 127) / 128;
+  p.total_work = p.Bt * p.H * p.nqt;
+  if (int e = set_smem(flash_core_kernel<DH>, Cfg::SMEM_BYTES)) return e;
+  const int grid = p.total_work < sm_count() ? p.total_work : sm_count();
+  flash_core_kernel<DH><<<grid, Cfg::THREADS, Cfg::SMEM_BYTES, stream>>>(tmQ, tmQ, tmV, tmB, p);
+  B200_CUDA(cudaGetLastError());
+  return 0;
+}
+
+static int launch_flash(const FlashLaunch& a, int DH, cudaStream_t stream) {
+  return DH == 32 ? launch_flash_t<32>(a, stream) : launch_flash_t<64>(a, stream);
+}
+
+static int launch_pair_bias(const void* z, bool f32, const float* ln_w, const float* ln_b, const void* w_z,
+                            __nv_bfloat16* zb, int N, int Nk, int H, cudaStream_t stream) {
+  CUtensorMap tmW;
+  const uint64_t dims[2] = {128, 16};
+  const uint64_t str[1] = {256};
+  const uint32_t box[2] = {64, 16};
+  if (int e = make_tmap_bf16(&tmW, w_z, 2, dims, str, box, CU_TENSOR_MAP_SWIZZLE_128B)) return e;
+  if (int e = set_smem(pair_bias_kernel<true>, pair_bias::SMEM_BYTES)) return e;
+  if (int e = set_smem(pair_bias_kernel<false>, pair_bias::SMEM_BYTES)) return e;
+  PairBiasParams p;
+  p.z = z;
+  p.ln_w = ln_w;
+  p.ln_b = ln_b;
+  p.zb = zb;
+  p.N = N;
+  p.Nk = Nk;
+  p.H = H;
+  p.num_tiles = N * ((N + 127) / 128);
+  p.scale = 1.4426950408889634f;
+  p.eps = 1e-5f;
+  const int grid = p.num_tiles < sm_count() ? p.num_tiles : sm_count();
+  if (f32)
+    pair_bias_kernel<true><<<grid, pair_bias::THREADS, pair_bias::SMEM_BYTES, stream>>>(tmW, p);
+  else
+    pair_bias_kernel<false><<<grid, pair_bias::THREADS, pair_bias::SMEM_BYTES, stream>>>(tmW, p);
   B200_CUDA(cudaGetLastError());
   return 0;
 }
@@ -109,8 +223,8 @@ int b200_layernorm_fwd(const void* x, void* y, const float* w, const float* b, i
   int64_t blocks = (rows + warps - 1) / warps;
   const int64_t cap = int64_t(sm_count()) * 16;
   if (blocks > cap) blocks = cap;
-  layernorm_rows_kernel<<<int(blocks), warps * 32, 0, static_cast<cudaStream_t>(stream)>>>(
-      static_cast<const __nv_bfloat16*>(x), static_cast<__nv_bfloat16*>(y), w, b, rows, cols, eps);
+  layernorm_rows_kernel<false><<<int(blocks), warps * 32, 0, static_cast<cudaStream_t>(stream)>>>(
+      x, static_cast<__nv_bfloat16*>(y), w, b, rows, cols, eps, 1);
   B200_CUDA(cudaGetLastError());
   return B200_OK;
 }
@@ -124,9 +238,12 @@ int b200_bmm_nt_bf16(const void* A, const void* B, void* C, int batch, int M, in
   B200_CHECK_ARG(N % 8 == 0, "N=%d must be a multiple of 8", N);
   B200_CHECK_ARG(lda % 8 == 0 && ldb % 8 == 0 && ldc % 8 == 0, "row pitches must be multiples of 8 elements");
   B200_CHECK_ARG(sa % 8 == 0 && sb % 8 == 0 && sc % 8 == 0, "batch strides must be multiples of 8 elements");
+  B200_CHECK_ARG(batch == 1 || (sa > 0 && sb > 0), "batch strides must be positive");
   B200_CHECK_ARG(lda >= K && ldb >= K && ldc >= N, "row pitch smaller than the row");
   B200_CHECK_ARG(aligned(A, 16) && aligned(B, 16) && aligned(C, 16), "A/B/C must be 16-byte aligned");
-  return launch_bmm(A, B, C, batch, M, N, K, lda, ldb, ldc, sa, sb, sc, scale, static_cast<cudaStream_t>(stream));
+  BmmLaunch a{A, B, C, batch, M, N, K, lda, ldb, ldc, sa, sb, sc};
+  a.scale = scale;
+  return launch_bmm(a, static_cast<cudaStream_t>(stream));
 }
 
 static inline int padded_n(int N) { return (N + 127) / 128 * 128; }
@@ -208,9 +325,11 @@ int b200_trimul_fwd(const void* z, const uint8_t* mask, void* out, const b200_tr
       trimul_in_kernel<false><<<grid, trimul_in::THREADS, trimul_in::SMEM_BYTES, stream>>>(tmWin, pi);
     B200_CUDA(cudaGetLastError());
 
-    if (int e = launch_bmm(a_buf, b_buf, t_buf, kD, Np, Np, Np, Np, Np, Np, int64_t(Np) * Np, int64_t(Np) * Np,
-                           int64_t(Np) * Np, 1.0f, stream))
-      return e;
+    {
+      const int64_t plane_el = int64_t(Np) * Np;
+      BmmLaunch a{a_buf, b_buf, t_buf, kD, Np, Np, Np, Np, Np, Np, plane_el, plane_el, plane_el};
+      if (int e = launch_bmm(a, stream)) return e;
+    }
 
     TriMulOutParams po;
     po.z = zb;
@@ -276,6 +395,231 @@ int b200_transition_fwd(const void* x, void* out, const void* w13, const void* w
   else
     transition_kernel<false><<<grid, transition::THREADS, transition::SMEM_BYTES, stream>>>(tmW1, tmW3, p);
   B200_CUDA(cudaGetLastError());
+  return B200_OK;
+}
+
+// ------------------------------------------------------------------------------------------------ OPM
+static void opm_plan(int S, int N, int* Sp, int* CI, size_t* ab_bytes, size_t* outer_bytes) {
+  *Sp = (S + 7) / 8 * 8;
+  const size_t per_tok = size_t(N) * 1024 * 2;               // bytes of outer products for one token row
+  size_t ci = (size_t(1) << 30) / per_tok;                    // keep the chunk near 1 GiB
+  ci = ci / 4 * 4;
+  if (ci < 4) ci = 4;
+  const size_t n4 = size_t(N + 3) / 4 * 4;
+  if (ci > n4) ci = n4;
+  *CI = int(ci);
+  *ab_bytes = (size_t(N) * 32 * size_t(*Sp) * 2 + 1023) / 1024 * 1024;
+  *outer_bytes = (ci * per_tok + 1023) / 1024 * 1024;
+}
+
+size_t b200_opm_workspace_bytes(int S, int N) {
+  if (S <= 0 || N <= 0) return 0;
+  int Sp, CI;
+  size_t ab, outer;
+  opm_plan(S, N, &Sp, &CI, &ab, &outer);
+  return 2 * ab + outer + 1024;
+}
+
+int b200_opm_fwd(const void* m, const uint8_t* mask, int mask_ndim, void* out, const b200_opm_weights* w, int B,
+                 int S, int N, int m_dtype, int out_dtype, void* workspace, size_t workspace_bytes,
+                 b200_stream_t stream_) {
+  if (int e = b200_check_device()) return e;
+  cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+  B200_CHECK_ARG(m && mask && out && w, "m/mask/out/w is NULL");
+  B200_CHECK_ARG(w->w_ab && w->w_o && w->ln_w && w->ln_b && w->bias_o, "a weight pointer is NULL");
+  B200_CHECK_ARG(B > 0 && S > 0 && N > 0, "B=%d, S=%d, N=%d must be positive", B, S, N);
+  B200_CHECK_ARG(mask_ndim == 3 || (mask_ndim == 2 && B == 1), "mask must be [B,S,N], or [B,N] with B == 1");
+  B200_CHECK_ARG((m_dtype | 1) == 1 && (out_dtype | 1) == 1, "unknown dtype");
+  B200_CHECK_ARG(aligned(m, 32) && aligned(out, 32) && aligned(w->w_ab, 16) && aligned(w->w_o, 16),
+                 "m/out must be 32-byte aligned, weights 16-byte aligned");
+  const size_t need = b200_opm_workspace_bytes(S, N);
+  if (!workspace || workspace_bytes < need || !aligned(workspace, 1024))
+    return fail(B200_ERR_WORKSPACE, "workspace must be 1024-byte aligned and hold %zu bytes (got %zu)", need,
+                workspace_bytes);
+  int Sp, CI;
+  size_t ab_bytes, outer_bytes;
+  opm_plan(S, N, &Sp, &CI, &ab_bytes, &outer_bytes);
+  uint8_t* ws = static_cast<uint8_t*>(workspace);
+  __nv_bfloat16* aT = reinterpret_cast<__nv_bfloat16*>(ws);
+  __nv_bfloat16* bT = reinterpret_cast<__nv_bfloat16*>(ws + ab_bytes);
+  __nv_bfloat16* outer = reinterpret_cast<__nv_bfloat16*>(ws + 2 * ab_bytes);
+  float* inv = reinterpret_cast<float*>(ws + 2 * ab_bytes + outer_bytes);
+
+  CUtensorMap tmW;
+  {
+    const uint64_t dims[2] = {64, 64};
+    const uint64_t str[1] = {128};
+    const uint32_t box[2] = {64, 64};
+    if (int e = make_tmap_bf16(&tmW, w->w_ab, 2, dims, str, box, CU_TENSOR_MAP_SWIZZLE_128B)) return e;
+  }
+  if (int e = set_smem(opm_proj_kernel<true>, opm_proj::SMEM_BYTES)) return e;
+  if (int e = set_smem(opm_proj_kernel<false>, opm_proj::SMEM_BYTES)) return e;
+  const size_t m_esz = m_dtype == B200_DTYPE_F32 ? 4 : 2;
+  const size_t o_esz = out_dtype == B200_DTYPE_F32 ? 4 : 2;
+
+  for (int bi = 0; bi < B; ++bi) {
+    OpmProjParams pp;
+    pp.m = static_cast<const uint8_t*>(m) + size_t(bi) * S * N * 64 * m_esz;
+    pp.mask = mask + (mask_ndim == 3 ? size_t(bi) * S * N : 0);
+    pp.mask_s_stride = mask_ndim == 3 ? N : 0;
+    pp.ln_w = w->ln_w;
+    pp.ln_b = w->ln_b;
+    pp.aT = aT;
+    pp.bT = bT;
+    pp.S = S;
+    pp.N = N;
+    pp.Sp = Sp;
+    pp.num_tiles = N * ((S + 127) / 128);
+    pp.eps = 1e-5f;
+    const int grid = pp.num_tiles < sm_count() ? pp.num_tiles : sm_count();
+    if (m_dtype == B200_DTYPE_F32)
+      opm_proj_kernel<true><<<grid, opm_proj::THREADS, opm_proj::SMEM_BYTES, stream>>>(tmW, pp);
+    else
+      opm_proj_kernel<false><<<grid, opm_proj::THREADS, opm_proj::SMEM_BYTES, stream>>>(tmW, pp);
+    B200_CUDA(cudaGetLastError());
+    const float* scale_ptr = nullptr;
+    if (mask_ndim == 3) {
+      opm_inv_row_count_kernel<<<1, 1024, 0, stream>>>(pp.mask, S, N, inv);
+      B200_CUDA(cudaGetLastError());
+      scale_ptr = inv;
+    }
+    for (int i0 = 0; i0 < N; i0 += CI) {
+      const int ci = (N - i0) < CI ? (N - i0) : CI;
+      {
+        BmmLaunch a{aT + size_t(i0) * 32 * Sp, bT, outer, 1, ci * 32, N * 32, S, Sp, Sp, 0, 0, 0, 0};
+        a.scale_ptr = scale_ptr;
+        a.opm_ntok = N;
+        if (int e = launch_bmm(a, stream)) return e;
+      }
+      {
+        void* dst = static_cast<uint8_t*>(out) + (size_t(bi) * N * N + size_t(i0) * N) * 128 * o_esz;
+        BmmLaunch a{outer, w->w_o, dst, 1, ci * N, 128, 1024, 1024, 1024, 128, 0, 0, 0};
+        a.bias = w->bias_o;
+        a.out_f32 = out_dtype == B200_DTYPE_F32;
+        if (int e = launch_bmm(a, stream)) return e;
+      }
+    }
+  }
+  return B200_OK;
+}
+
+// ------------------------------------------------------------------------------------------------ APB
+struct ApbPlan {
+  int dh, DH, W1, Nk;
+  size_t off_sln, off_qkg, off_vT, off_zb, off_og, total;
+};
+
+static bool apb_plan(int B, int M, int N, int c_s, int H, ApbPlan* pl) {
+  if (H <= 0 || H > 16 || c_s % H != 0) return false;
+  pl->dh = c_s / H;
+  if (pl->dh % 8 != 0 || pl->dh > 64 || c_s % 8 != 0) return false;
+  pl->DH = pl->dh <= 32 ? 32 : 64;
+  pl->W1 = 2 * H * pl->DH + c_s;
+  pl->Nk = (N + 7) / 8 * 8;
+  const size_t rows = size_t(B) * M * N;
+  auto up = [](size_t x) { return (x + 1023) / 1024 * 1024; };
+  size_t o = 0;
+  pl->off_sln = o; o += up(rows * c_s * 2);
+  pl->off_qkg = o; o += up(rows * pl->W1 * 2);
+  pl->off_vT = o;  o += up(size_t(B) * M * H * pl->DH * pl->Nk * 2);
+  pl->off_zb = o;  o += up(size_t(B) * H * N * pl->Nk * 2);
+  pl->off_og = o;  o += up(rows * c_s * 2);
+  pl->total = o;
+  return true;
+}
+
+size_t b200_apb_workspace_bytes(int B, int M, int N, int c_s, int H) {
+  ApbPlan pl;
+  if (B <= 0 || M <= 0 || N <= 0 || !apb_plan(B, M, N, c_s, H, &pl)) return 0;
+  return pl.total;
+}
+
+int b200_apb_fwd(const void* s, const void* z, const uint8_t* mask, void* out, const b200_apb_weights* w, int B,
+                 int M, int N, int c_s, int H, int s_dtype, int z_dtype, void* workspace, size_t workspace_bytes,
+                 b200_stream_t stream_) {
+  if (int e = b200_check_device()) return e;
+  cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+  B200_CHECK_ARG(s && z && mask && out && w, "s/z/mask/out/w is NULL");
+  B200_CHECK_ARG(w->w_qkg && w->b_qkg && w->w_v && w->w_z && w->ln_z_w && w->w_o, "a weight pointer is NULL");
+  B200_CHECK_ARG(B > 0 && M > 0 && N > 0, "B=%d, M=%d, N=%d must be positive", B, M, N);
+  B200_CHECK_ARG((s_dtype | 1) == 1 && (z_dtype | 1) == 1, "unknown dtype");
+  ApbPlan pl;
+  B200_CHECK_ARG(apb_plan(B, M, N, c_s, H, &pl),
+                 "unsupported c_s=%d, H=%d: need H <= 16, head dim a multiple of 8 and <= 64", c_s, H);
+  B200_CHECK_ARG(aligned(s, 32) && aligned(z, 32) && aligned(out, 32), "s/z/out must be 32-byte aligned");
+  if (!workspace || workspace_bytes < pl.total || !aligned(workspace, 1024))
+    return fail(B200_ERR_WORKSPACE, "workspace must be 1024-byte aligned and hold %zu bytes (got %zu)", pl.total,
+                workspace_bytes);
+  uint8_t* ws = static_cast<uint8_t*>(workspace);
+  __nv_bfloat16* s_ln = reinterpret_cast<__nv_bfloat16*>(ws + pl.off_sln);
+  __nv_bfloat16* qkg = reinterpret_cast<__nv_bfloat16*>(ws + pl.off_qkg);
+  __nv_bfloat16* vT = reinterpret_cast<__nv_bfloat16*>(ws + pl.off_vT);
+  __nv_bfloat16* zb = reinterpret_cast<__nv_bfloat16*>(ws + pl.off_zb);
+  __nv_bfloat16* og = reinterpret_cast<__nv_bfloat16*>(ws + pl.off_og);
+  const int BM = B * M;
+  const int64_t rows = int64_t(BM) * N;
+  const int HD = H * pl.DH;
+
+  // 1. LayerNorm (or plain conversion) of the single track
+  if (int e = launch_rows_to_bf16(s, s_dtype == B200_DTYPE_F32, s_ln, w->ln_s_w, w->ln_s_b, rows, c_s,
+                                  w->ln_s_w != nullptr, stream))
+    return e;
+  // 2. q | k | g projection (heads padded to DH, q pre-scaled) and V^T per batch item
+  {
+    BmmLaunch a{s_ln, w->w_qkg, qkg, 1, int(rows), pl.W1, c_s, c_s, c_s, pl.W1, 0, 0, 0};
+    a.bias = w->b_qkg;
+    if (int e = launch_bmm(a, stream)) return e;
+  }
+  for (int b = 0; b < BM; ++b) {
+    BmmLaunch a{w->w_v, s_ln + size_t(b) * N * c_s, vT + size_t(b) * HD * pl.Nk, 1, HD, N, c_s, c_s, c_s, pl.Nk, 0, 0, 0};
+    if (int e = launch_bmm(a, stream)) return e;
+  }
+  // 3. pair bias, one pass over z per batch element
+  const size_t z_esz = z_dtype == B200_DTYPE_F32 ? 4 : 2;
+  for (int b = 0; b < B; ++b) {
+    if (int e = launch_pair_bias(static_cast<const uint8_t*>(z) + size_t(b) * N * N * kD * z_esz,
+                                 z_dtype == B200_DTYPE_F32, w->ln_z_w, w->ln_z_b, w->w_z,
+                                 zb + size_t(b) * H * N * pl.Nk, N, pl.Nk, H, stream))
+      return e;
+  }
+  // 4. attention core
+  {
+    FlashLaunch a;
+    a.qk = qkg;
+    a.qk_width = pl.W1;
+    a.qk_b_stride = int64_t(N) * pl.W1;
+    a.vT = vT;
+    a.v_pitch = pl.Nk;
+    a.bias = zb;
+    a.bias_pitch = pl.Nk;
+    a.bias_groups = B;
+    FlashParams& p = a.p;
+    p.mask = mask;
+    p.mask_div = M;
+    p.bias_div = M;
+    p.gate = qkg;
+    p.gate_b_stride = int64_t(N) * pl.W1;
+    p.gate_pitch = pl.W1;
+    p.gate_col0 = 2 * HD;
+    p.out = og;
+    p.out_b_stride = int64_t(N) * c_s;
+    p.out_pitch = c_s;
+    p.out_col0 = 0;
+    p.dh_out = pl.dh;
+    p.N = N;
+    p.H = H;
+    p.Bt = BM;
+    p.q_col0 = 0;
+    p.k_col0 = HD;
+    p.v_row0 = 0;
+    if (int e = launch_flash(a, pl.DH, stream)) return e;
+  }
+  // 5. output projection
+  {
+    BmmLaunch a{og, w->w_o, out, 1, int(rows), c_s, c_s, c_s, c_s, c_s, 0, 0, 0};
+    a.out_f32 = s_dtype == B200_DTYPE_F32;
+    if (int e = launch_bmm(a, stream)) return e;
+  }
   return B200_OK;
 }
 

@@ -165,3 +165,108 @@ def transition(x: Tensor, w: TransitionPacked, add_residual: bool = False, out: 
                                        w.norm_b.data_ptr() if use_norm else None, rows, 1 if use_norm else 0,
                                        1 if add_residual else 0, zd, _stream()))
     return out
+
+
+class OpmPacked:
+    """Weights of the outer product mean (c_in 64, c_hidden 32, c_out 128) for ``b200_opm_fwd``."""
+
+    def __init__(self, norm_w, norm_b, proj_ab, proj_o_w, proj_o_b):
+        if tuple(proj_ab.shape) != (64, 64) or tuple(proj_o_w.shape) != (128, 1024):
+            raise ValueError("the outer-product-mean kernels are built for c_in=64, c_hidden=32, c_out=128")
+        bf = torch.bfloat16
+        self.w_ab = proj_ab.to(bf).contiguous()
+        self.w_o = proj_o_w.to(bf).contiguous()
+        self.f32 = [t.detach().float().contiguous() for t in (norm_w, norm_b, proj_o_b)]
+        self.struct = _lib.OpmWeights(self.w_ab.data_ptr(), self.w_o.data_ptr(), self.f32[0].data_ptr(),
+                                      self.f32[1].data_ptr(), self.f32[2].data_ptr())
+
+
+def outer_product_mean(m: Tensor, mask: Tensor, w: OpmPacked) -> Tensor:
+    """``m[B,S,N,64]`` (fp32 or bf16), ``mask[B,S,N]`` or ``[B,N]`` -> ``[B,N,N,128]`` in ``m.dtype``."""
+    _require_cuda(m, mask)
+    if m.ndim != 4 or m.shape[-1] != 64:
+        raise ValueError(f"expected m[B,S,N,64], got {tuple(m.shape)}")
+    B, S, N, _ = m.shape
+    if mask.ndim == 3:
+        if tuple(mask.shape) != (B, S, N):
+            raise ValueError(f"mask shape {tuple(mask.shape)} does not match m {tuple(m.shape)}")
+    elif mask.ndim == 2:
+        if tuple(mask.shape) != (B, N) or B != 1:
+            raise ValueError("a [B,N] mask needs B == 1 (the only shape that broadcasts in the reference)")
+    else:
+        raise ValueError("mask must be [B,S,N] or [B,N]")
+    zd = _zdtype(m)
+    m = m.contiguous()
+    out = torch.empty(B, N, N, 128, dtype=m.dtype, device=m.device)
+    m8 = mask_u8(mask)
+    nbytes = lib.b200_opm_workspace_bytes(S, N)
+    ws = workspace(nbytes, m.device)
+    _lib.check(lib.b200_opm_fwd(m.data_ptr(), m8.data_ptr(), mask.ndim, out.data_ptr(), ctypes.byref(w.struct), B, S, N,
+                                zd, zd, ws.data_ptr(), nbytes, _stream()))
+    return out
+
+
+LOG2E = 1.4426950408889634
+
+
+def _pad_heads(wt: Tensor, H: int, dh: int, DH: int) -> Tensor:
+    """[H*dh, ...] -> [H*DH, ...] with zero rows appended to every head."""
+    rest = wt.shape[1:]
+    out = wt.new_zeros((H, DH) + tuple(rest))
+    out[:, :dh] = wt.reshape((H, dh) + tuple(rest))
+    return out.reshape((H * DH,) + tuple(rest))
+
+
+class ApbPacked:
+    """Weights of single-track pair-bias attention in the layouts ``b200_apb_fwd`` expects."""
+
+    def __init__(self, c_s, c_z, H, proj_qkv, proj_q_bias, proj_g, norm_z_w, norm_z_b, proj_z, proj_o,
+                 norm_s_w=None, norm_s_b=None):
+        if c_z != 128:
+            raise ValueError("pair-bias attention is built for c_z=128")
+        dh = c_s // H
+        if c_s % H or dh % 8 or dh > 64 or H > 16:
+            raise ValueError("pair-bias attention needs H <= 16 and a head dim that is a multiple of 8 and <= 64")
+        DH = 32 if dh <= 32 else 64
+        self.c_s, self.H = c_s, H
+        bf = torch.bfloat16
+        wq, wk, wv = proj_qkv.detach().float().chunk(3, dim=0)
+        qscale = LOG2E / (dh ** 0.5)
+        self.w_qkg = torch.cat([_pad_heads(wq * qscale, H, dh, DH), _pad_heads(wk, H, dh, DH),
+                                proj_g.detach().float()], dim=0).to(bf).contiguous()
+        b = torch.zeros(2 * H * DH + c_s, dtype=torch.float32, device=proj_qkv.device)
+        b[: H * DH] = _pad_heads(proj_q_bias.detach().float() * qscale, H, dh, DH)
+        self.b_qkg = b
+        self.w_v = _pad_heads(wv, H, dh, DH).to(bf).contiguous()
+        wz = torch.zeros(16, 128, dtype=torch.float32, device=proj_z.device)
+        wz[:H] = proj_z.detach().float()
+        self.w_z = wz.to(bf).contiguous()
+        self.ln_z_w = norm_z_w.detach().float().contiguous()
+        self.ln_z_b = norm_z_b.detach().float().contiguous() if norm_z_b is not None else None
+        self.ln_s_w = norm_s_w.detach().float().contiguous() if norm_s_w is not None else None
+        self.ln_s_b = norm_s_b.detach().float().contiguous() if norm_s_b is not None else None
+        self.w_o = proj_o.detach().to(bf).contiguous()
+        ptr = lambda t: t.data_ptr() if t is not None else None  # noqa: E731
+        self.struct = _lib.ApbWeights(ptr(self.w_qkg), ptr(self.b_qkg), ptr(self.w_v), ptr(self.w_z), ptr(self.ln_z_w),
+                                      ptr(self.ln_z_b), ptr(self.ln_s_w), ptr(self.ln_s_b), ptr(self.w_o))
+
+
+def attention_pair_bias(s: Tensor, z: Tensor, mask: Tensor, w: ApbPacked, multiplicity: int = 1) -> Tensor:
+    """``s[B*M,N,c_s]``, ``z[B,N,N,128]``, ``mask[B,N]`` -> ``[B*M,N,c_s]`` in ``s.dtype``."""
+    _require_cuda(s, z, mask)
+    if s.ndim != 3 or z.ndim != 4 or mask.ndim != 2:
+        raise ValueError(f"{tuple(s.shape)}, {tuple(z.shape)}, {tuple(mask.shape)}")
+    B, N = z.shape[0], z.shape[1]
+    if s.shape[0] != B * multiplicity or s.shape[1] != N or s.shape[2] != w.c_s:
+        raise ValueError(f"{tuple(s.shape)}, {tuple(z.shape)}, multiplicity={multiplicity}")
+    if tuple(z.shape) != (B, N, N, 128) or tuple(mask.shape) != (B, N):
+        raise ValueError(f"z {tuple(z.shape)} / mask {tuple(mask.shape)} do not match s {tuple(s.shape)}")
+    sd, zd = _zdtype(s), _zdtype(z)
+    s, z = s.contiguous(), z.contiguous()
+    out = torch.empty_like(s)
+    m8 = mask_u8(mask)
+    nbytes = lib.b200_apb_workspace_bytes(B, multiplicity, N, w.c_s, w.H)
+    ws = workspace(nbytes, s.device)
+    _lib.check(lib.b200_apb_fwd(s.data_ptr(), z.data_ptr(), m8.data_ptr(), out.data_ptr(), ctypes.byref(w.struct), B,
+                                multiplicity, N, w.c_s, w.H, sd, zd, ws.data_ptr(), nbytes, _stream()))
+    return out

@@ -120,6 +120,74 @@ int b200_transition_fwd(const void* x, void* out, const void* w13, const void* w
                         const float* ln_b, int64_t rows, int use_norm, int add_residual, int x_dtype,
                         b200_stream_t stream);
 
+/* ---------------------------------------------------------------------------------------------------
+ * Outer product mean, OuterProductMeanVanilla.forward (src/bioemu2/biomoa/ops/outer_product_mean.py:45-75)
+ * for c_in = 64, c_hidden = 32, c_out = 128:
+ *   m' = mask * proj_ab(LN(m));  a, b = halves of m';  out[i,j,:] = proj_o(vec(sum_s a[s,i,:] (x) b[s,j,:]) / n) + bias
+ * with n = number of MSA rows holding at least one valid token (clamped to >= 1) for a [B,S,N] mask
+ * (mask_ndim 3) and n = 1 for a [B,N] mask (mask_ndim 2, B must be 1, as in the reference where only that
+ * shape broadcasts).  The S-contraction accumulates in fp32 on the tensor cores and is rounded to bf16
+ * once, before proj_o, as the reference's `z.to(m)` does under autocast.
+ *
+ *   w_ab  bf16 [64][64]    = proj_ab.weight        ln_w, ln_b  fp32 [64]
+ *   w_o   bf16 [128][1024] = proj_o.weight         bias_o      fp32 [128]
+ *
+ * m: [B][S][N][64] of m_dtype; mask: uint8; out: [B][N][N][128] of out_dtype.
+ * Workspace: b200_opm_workspace_bytes(S, N) bytes, 1024-byte aligned.
+ * ------------------------------------------------------------------------------------------------- */
+typedef struct {
+  const void* w_ab;
+  const void* w_o;
+  const float* ln_w;
+  const float* ln_b;
+  const float* bias_o;
+} b200_opm_weights;
+
+size_t b200_opm_workspace_bytes(int S, int N);
+
+int b200_opm_fwd(const void* m, const uint8_t* mask, int mask_ndim, void* out, const b200_opm_weights* w, int B,
+                 int S, int N, int m_dtype, int out_dtype, void* workspace, size_t workspace_bytes,
+                 b200_stream_t stream);
+
+/* ---------------------------------------------------------------------------------------------------
+ * Single-track attention with pair bias, AttentionPairBias.forward
+ * (src/bioemu2/biomoa/ops/attention_pair_bias.py:128-225):
+ *   s' = LN(s) (if initial_norm);  q = Wq s' + b_q, k, v;  g = sigmoid(Wg s');  bias = proj_z(LN_z(z));
+ *   o = softmax(q.k / sqrt(dh) + bias, masked keys replaced by -1e6) v;  out = Wo (g * o)
+ * with the pair bias and key mask shared by the M ("multiplicity") copies of each batch element.
+ * H <= 16 heads, head dim dh = c_s / H a multiple of 8 and <= 64; c_z = 128.  Heads are padded to
+ * DH = 32 (dh <= 32) or 64 columns inside the packed weights:
+ *
+ *   w_qkg  bf16 [2*H*DH + c_s][c_s]  rows h*DH + d (d < dh) = Wq[h*dh + d] * log2(e)/sqrt(dh), zero rows for
+ *                                    d >= dh; then the same for Wk (unscaled); then Wg
+ *   b_qkg  fp32 [2*H*DH + c_s]       proj_q_bias in the q rows with the same scaling, zero elsewhere
+ *   w_v    bf16 [H*DH][c_s]          Wv, head-padded
+ *   w_z    bf16 [16][128]            proj_z.weight, zero rows for h >= H
+ *   ln_z_w fp32 [128]; ln_z_b fp32 [128] or NULL (norm_z has no bias by default)
+ *   ln_s_w, ln_s_b fp32 [c_s], both NULL when initial_norm is False
+ *   w_o    bf16 [c_s][c_s]
+ *
+ * s, out: [B*M][N][c_s] of s_dtype; z: [B][N][N][128] of z_dtype; mask: uint8 [B][N].
+ * Workspace: b200_apb_workspace_bytes(B, M, N, c_s, H) bytes, 1024-byte aligned.
+ * ------------------------------------------------------------------------------------------------- */
+typedef struct {
+  const void* w_qkg;
+  const float* b_qkg;
+  const void* w_v;
+  const void* w_z;
+  const float* ln_z_w;
+  const float* ln_z_b;
+  const float* ln_s_w;
+  const float* ln_s_b;
+  const void* w_o;
+} b200_apb_weights;
+
+size_t b200_apb_workspace_bytes(int B, int M, int N, int c_s, int H);
+
+int b200_apb_fwd(const void* s, const void* z, const uint8_t* mask, void* out, const b200_apb_weights* w, int B,
+                 int M, int N, int c_s, int H, int s_dtype, int z_dtype, void* workspace, size_t workspace_bytes,
+                 b200_stream_t stream);
+
 #ifdef __cplusplus
 }
 #endif
