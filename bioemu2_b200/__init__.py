@@ -10,6 +10,11 @@ from .outer_product_mean import (
 )
 from .pairmixer import PairMixerLayer, PairMixerModule
 from .transition import Transition
+from .triangle_attention import (
+    TriangleAttention,
+    TriangleAttentionEndingNode,
+    TriangleAttentionStartingNode,
+)
 from .triangle_multiplication import (
     TriangleMultiplication,
     TriangleMultiplicationIncoming,
@@ -25,6 +30,9 @@ __all__ = [
     "PairMixerLayer",
     "PairMixerModule",
     "Transition",
+    "TriangleAttention",
+    "TriangleAttentionEndingNode",
+    "TriangleAttentionStartingNode",
     "TriangleMultiplication",
     "TriangleMultiplicationIncoming",
     "TriangleMultiplicationOutgoing",

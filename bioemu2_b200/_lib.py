@@ -42,6 +42,11 @@ class ApbWeights(Structure):
                 ("ln_z_b", c_void_p), ("ln_s_w", c_void_p), ("ln_s_b", c_void_p), ("w_o", c_void_p)]
 
 
+class TriAttWeights(Structure):
+    _fields_ = [("w_qkgv", c_void_p), ("g_bias", c_void_p), ("w_b", c_void_p), ("w_o", c_void_p), ("ln_w", c_void_p),
+                ("ln_b", c_void_p)]
+
+
 # name -> (restype, argtypes); mirrors include/b200pair.h one to one
 SIGNATURES = {
     "b200_version": (c_int, []),
@@ -62,6 +67,9 @@ SIGNATURES = {
     "b200_apb_workspace_bytes": (c_size_t, [c_int, c_int, c_int, c_int, c_int]),
     "b200_apb_fwd": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, POINTER(ApbWeights), c_int, c_int, c_int, c_int,
                              c_int, c_int, c_int, c_void_p, c_size_t, c_void_p]),
+    "b200_triatt_workspace_bytes": (c_size_t, [c_int]),
+    "b200_triatt_fwd": (c_int, [c_void_p, c_void_p, c_void_p, POINTER(TriAttWeights), c_int, c_int, c_int, c_int,
+                                c_int, c_void_p, c_size_t, c_void_p]),
 }
 
 if not os.path.exists(LIB_PATH):

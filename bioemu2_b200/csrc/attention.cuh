@@ -21,8 +21,9 @@
 namespace b200 {
 
 struct FlashParams {
-  const uint8_t* mask;  // [.][N] one byte per key
-  int mask_div;         // mask row of batch item b is b / mask_div
+  const uint8_t* mask;  // one byte per key: mask[(b / mask_div) * mask_row_stride + key * mask_key_stride]
+  int mask_div;
+  long long mask_row_stride, mask_key_stride;
   int bias_div;         // bias group of batch item b is b / bias_div
   const __nv_bfloat16* gate;  // raw gate logits (sigmoid applied here) or nullptr
   long long gate_b_stride;
@@ -201,7 +202,7 @@ flash_core_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
       const int bh = work / p.nqt;
       const int h = bh % p.H;
       const int b = bh / p.H;
-      const uint8_t* mrow = p.mask + (long long)(b / p.mask_div) * p.N;
+      const uint8_t* mrow = p.mask + (long long)(b / p.mask_div) * p.mask_row_stride;
       float m_run = -INFINITY, l_run = 0.f, alpha_prev = 0.f;
       float o[DH];
 #pragma unroll
@@ -213,7 +214,7 @@ flash_core_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
         // key-validity bits of this tile: bit j of word w <=> key t*128 + 32*w + j exists and is unmasked
         {
           const int key = t * 128 + r;
-          const bool ok = key < p.N && mrow[key] != 0;
+          const bool ok = key < p.N && mrow[key * p.mask_key_stride] != 0;
           const bool in = key < p.N;
           const uint32_t okb = __ballot_sync(0xffffffffu, ok);
           const uint32_t inb = __ballot_sync(0xffffffffu, in);
@@ -362,6 +363,7 @@ struct PairBiasParams {
   const float* ln_b;    // nullptr: LayerNorm without bias
   __nv_bfloat16* zb;    // [H][N][Nk]
   int N, Nk, H;
+  int transposed;       // 1: bias of the transposed pair tensor, zb[h][i][j] from z[j][i]
   int num_tiles;        // N * ceil(N/128)
   float scale;          // log2(e)
   float eps;
@@ -436,12 +438,14 @@ pair_bias_kernel(const __grid_constant__ CUtensorMap tmW, PairBiasParams p) {
     float gamma[8], beta[8];
     load_gamma_beta(p.ln_w, p.ln_b, pt, gamma, beta);
     RowTile<256> regs;
+    const long long pos_stride = (p.transposed ? (long long)p.N * kD : kD) * (long long)zbytes<F32>();
+    const long long line_stride = (p.transposed ? kD : (long long)p.N * kD) * (long long)zbytes<F32>();
     auto load_tile = [&](int tile) {
       const int i = tile / tiles_per_row;
       const int j0 = (tile - i * tiles_per_row) << 7;
-      const uint8_t* base = static_cast<const uint8_t*>(p.z) + ((long long)i * p.N + j0) * kD * zbytes<F32>();
+      const uint8_t* base = static_cast<const uint8_t*>(p.z) + i * line_stride;
       regs.template load<F32, true>(
-          pt, [&](int r) -> const void* { return (j0 + r) < p.N ? base + (long long)r * kD * zbytes<F32>() : nullptr; },
+          pt, [&](int r) -> const void* { return (j0 + r) < p.N ? base + (j0 + r) * pos_stride : nullptr; },
           gamma, beta, p.eps);
     };
     int it = 0;

@@ -26,6 +26,11 @@ struct BmmParams {
   // Outer-product store: with opm_ntok > 0, C row r = (i, c) and column q = (j, d) (c, d < 32) go to
   // C[((i * opm_ntok + j) * 32 + c) * 32 + d]: every pair (i, j) gets its 32x32 outer product contiguous.
   int opm_ntok;
+  // Residual and transposed pair store (output projection of triangle attention): with residual != nullptr
+  // the value read from it at the destination offset is added; with remap_n > 0 row r = line * remap_n + pos
+  // is stored as row pos * remap_n + line.
+  const void* residual;
+  int remap_n;
 };
 
 template <int BN>
@@ -154,6 +159,8 @@ bmm_nt_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ C
           long long off0;  // element offset of (row, col0)
           if (p.opm_ntok > 0)
             off0 = (((long long)(row >> 5) * p.opm_ntok + (col0 >> 5)) * 32 + (row & 31)) * 32;
+          else if (p.remap_n > 0)
+            off0 = ((long long)(row % p.remap_n) * p.remap_n + row / p.remap_n) * p.ldc + col0;
           else
             off0 = (long long)row * p.ldc + col0;
 #pragma unroll
@@ -166,6 +173,16 @@ bmm_nt_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ C
               if (p.bias) {
 #pragma unroll
                 for (int e = 0; e < 8; ++e) x[e] += p.bias[col + e];
+              }
+              if (p.residual) {
+                float rz[8];
+                const uint8_t* rb = static_cast<const uint8_t*>(p.residual) + (long long)b * p.c_batch_stride * esz;
+                if (p.out_f32)
+                  load8<true>(rb + (off0 + g * 8) * 4, 0, rz);
+                else
+                  load8<false>(rb + (off0 + g * 8) * 2, 0, rz);
+#pragma unroll
+                for (int e = 0; e < 8; ++e) x[e] += rz[e];
               }
               if (p.out_f32)
                 store8<true>(cbase + (off0 + g * 8) * 4, 0, x);

@@ -12,6 +12,7 @@
 #include "elementwise.cuh"
 #include "opm.cuh"
 #include "attention.cuh"
+#include "triatt.cuh"
 
 namespace b200 {
 
@@ -32,6 +33,8 @@ struct BmmLaunch {
   const float* bias = nullptr;
   int out_f32 = 0;
   int opm_ntok = 0;
+  const void* residual = nullptr;
+  int remap_n = 0;
 };
 
 static int launch_bmm(const BmmLaunch& a, cudaStream_t stream) {
@@ -64,6 +67,8 @@ static int launch_bmm(const BmmLaunch& a, cudaStream_t stream) {
   p.bias = a.bias;
   p.out_f32 = a.out_f32;
   p.opm_ntok = a.opm_ntok;
+  p.residual = a.residual;
+  p.remap_n = a.remap_n;
   const int total = p.tiles_m * p.tiles_n * a.batch;
   const int grid = total < sm_count() ? total : sm_count();
   if (BN == 256) {
@@ -146,7 +151,7 @@ static int launch_flash(const FlashLaunch& a, int DH, cudaStream_t stream) {
 }
 
 static int launch_pair_bias(const void* z, bool f32, const float* ln_w, const float* ln_b, const void* w_z,
-                            __nv_bfloat16* zb, int N, int Nk, int H, cudaStream_t stream) {
+                            __nv_bfloat16* zb, int N, int Nk, int H, cudaStream_t stream, bool transposed = false) {
   CUtensorMap tmW;
   const uint64_t dims[2] = {128, 16};
   const uint64_t str[1] = {256};
@@ -162,6 +167,7 @@ static int launch_pair_bias(const void* z, bool f32, const float* ln_w, const fl
   p.N = N;
   p.Nk = Nk;
   p.H = H;
+  p.transposed = transposed ? 1 : 0;
   p.num_tiles = N * ((N + 127) / 128);
   p.scale = 1.4426950408889634f;
   p.eps = 1e-5f;
@@ -596,6 +602,8 @@ int b200_apb_fwd(const void* s, const void* z, const uint8_t* mask, void* out, c
     FlashParams& p = a.p;
     p.mask = mask;
     p.mask_div = M;
+    p.mask_row_stride = N;
+    p.mask_key_stride = 1;
     p.bias_div = M;
     p.gate = qkg;
     p.gate_b_stride = int64_t(N) * pl.W1;
@@ -619,6 +627,130 @@ int b200_apb_fwd(const void* s, const void* z, const uint8_t* mask, void* out, c
     BmmLaunch a{og, w->w_o, out, 1, int(rows), c_s, c_s, c_s, c_s, c_s, 0, 0, 0};
     a.out_f32 = s_dtype == B200_DTYPE_F32;
     if (int e = launch_bmm(a, stream)) return e;
+  }
+  return B200_OK;
+}
+
+// ------------------------------------------------------------------------------------------------ triangle attention
+struct TriAttPlan {
+  int Nk;
+  size_t off_qkg, off_vT, off_tb, off_og, total;
+};
+
+static void triatt_plan(int N, TriAttPlan* pl) {
+  pl->Nk = (N + 7) / 8 * 8;
+  auto up = [](size_t x) { return (x + 1023) / 1024 * 1024; };
+  size_t o = 0;
+  pl->off_qkg = o; o += up(size_t(N) * N * 384 * 2);
+  pl->off_vT = o;  o += up(size_t(N) * kD * pl->Nk * 2);
+  pl->off_tb = o;  o += up(size_t(4) * N * pl->Nk * 2);
+  pl->off_og = o;  o += up(size_t(N) * N * kD * 2);
+  pl->total = o;
+}
+
+size_t b200_triatt_workspace_bytes(int N) {
+  if (N <= 0) return 0;
+  TriAttPlan pl;
+  triatt_plan(N, &pl);
+  return pl.total;
+}
+
+int b200_triatt_fwd(const void* z, const uint8_t* mask, void* out, const b200_triatt_weights* w, int B, int N,
+                    int ending, int add_residual, int z_dtype, void* workspace, size_t workspace_bytes,
+                    b200_stream_t stream_) {
+  if (int e = b200_check_device()) return e;
+  cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+  B200_CHECK_ARG(z && mask && out && w, "z/mask/out/w is NULL");
+  B200_CHECK_ARG(w->w_qkgv && w->g_bias && w->w_b && w->w_o && w->ln_w && w->ln_b, "a weight pointer is NULL");
+  B200_CHECK_ARG(B > 0 && N > 0, "B=%d, N=%d must be positive", B, N);
+  B200_CHECK_ARG((z_dtype | 1) == 1, "unknown z_dtype %d", z_dtype);
+  B200_CHECK_ARG(aligned(z, 32) && aligned(out, 32), "z/out must be 32-byte aligned");
+  TriAttPlan pl;
+  triatt_plan(N, &pl);
+  if (!workspace || workspace_bytes < pl.total || !aligned(workspace, 1024))
+    return fail(B200_ERR_WORKSPACE, "workspace must be 1024-byte aligned and hold %zu bytes (got %zu)", pl.total,
+                workspace_bytes);
+  uint8_t* ws = static_cast<uint8_t*>(workspace);
+  __nv_bfloat16* qkg = reinterpret_cast<__nv_bfloat16*>(ws + pl.off_qkg);
+  __nv_bfloat16* vT = reinterpret_cast<__nv_bfloat16*>(ws + pl.off_vT);
+  __nv_bfloat16* tb = reinterpret_cast<__nv_bfloat16*>(ws + pl.off_tb);
+  __nv_bfloat16* og = reinterpret_cast<__nv_bfloat16*>(ws + pl.off_og);
+  const bool f32 = z_dtype == B200_DTYPE_F32;
+  const size_t esz = f32 ? 4 : 2;
+
+  CUtensorMap tmW;
+  {
+    const uint64_t dims[2] = {128, 512};
+    const uint64_t str[1] = {256};
+    const uint32_t box[2] = {64, 128};
+    if (int e = make_tmap_bf16(&tmW, w->w_qkgv, 2, dims, str, box, CU_TENSOR_MAP_SWIZZLE_128B)) return e;
+  }
+  if (int e = set_smem(triatt_proj_kernel<true>, triatt_proj::SMEM_BYTES)) return e;
+  if (int e = set_smem(triatt_proj_kernel<false>, triatt_proj::SMEM_BYTES)) return e;
+
+  for (int bi = 0; bi < B; ++bi) {
+    const uint8_t* zb_ = static_cast<const uint8_t*>(z) + size_t(bi) * N * N * kD * esz;
+    uint8_t* ob = static_cast<uint8_t*>(out) + size_t(bi) * N * N * kD * esz;
+    TriAttProjParams pp;
+    pp.z = zb_;
+    pp.ln_w = w->ln_w;
+    pp.ln_b = w->ln_b;
+    pp.g_bias = w->g_bias;
+    pp.qkg = qkg;
+    pp.vT = vT;
+    pp.N = N;
+    pp.Nk = pl.Nk;
+    pp.transposed = ending ? 1 : 0;
+    pp.num_tiles = N * ((N + 127) / 128);
+    pp.eps = 1e-5f;
+    const int grid = pp.num_tiles < sm_count() ? pp.num_tiles : sm_count();
+    if (f32)
+      triatt_proj_kernel<true><<<grid, triatt_proj::THREADS, triatt_proj::SMEM_BYTES, stream>>>(tmW, pp);
+    else
+      triatt_proj_kernel<false><<<grid, triatt_proj::THREADS, triatt_proj::SMEM_BYTES, stream>>>(tmW, pp);
+    B200_CUDA(cudaGetLastError());
+    if (int e = launch_pair_bias(zb_, f32, w->ln_w, w->ln_b, w->w_b, tb, N, pl.Nk, 4, stream, ending != 0)) return e;
+    {
+      FlashLaunch a;
+      a.qk = qkg;
+      a.qk_width = 384;
+      a.qk_b_stride = int64_t(N) * 384;
+      a.vT = vT;
+      a.v_pitch = pl.Nk;
+      a.bias = tb;
+      a.bias_pitch = pl.Nk;
+      a.bias_groups = 1;
+      FlashParams& p = a.p;
+      p.mask = mask + size_t(bi) * N * N;
+      p.mask_div = 1;
+      // line l attends over keys k with mask[l][k] (starting node) or mask[k][l] (ending node)
+      p.mask_row_stride = ending ? 1 : N;
+      p.mask_key_stride = ending ? N : 1;
+      p.bias_div = N;
+      p.gate = qkg;
+      p.gate_b_stride = int64_t(N) * 384;
+      p.gate_pitch = 384;
+      p.gate_col0 = 256;
+      p.out = og;
+      p.out_b_stride = int64_t(N) * kD;
+      p.out_pitch = kD;
+      p.out_col0 = 0;
+      p.dh_out = 32;
+      p.N = N;
+      p.H = 4;
+      p.Bt = N;
+      p.q_col0 = 0;
+      p.k_col0 = 128;
+      p.v_row0 = 0;
+      if (int e = launch_flash(a, 32, stream)) return e;
+    }
+    {
+      BmmLaunch a{og, w->w_o, ob, 1, N * N, kD, kD, kD, kD, kD, 0, 0, 0};
+      a.out_f32 = f32;
+      a.residual = add_residual ? static_cast<const void*>(zb_) : nullptr;
+      a.remap_n = ending ? N : 0;
+      if (int e = launch_bmm(a, stream)) return e;
+    }
   }
   return B200_OK;
 }

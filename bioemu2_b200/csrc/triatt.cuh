@@ -1,0 +1,208 @@
+// Triangle attention, projection stage: h = LN(x);  q | k | g = h Wq^T, h Wk^T, h Wg^T + b_g  (pair-major,
+// bf16, row pitch 384) and V^T = Wv h^T (channel-major per line, bf16, pitch Nk), the layouts the flash
+// core reads.  x is the pair tensor for the starting node and its transpose for the ending node: a tile
+// is 128 consecutive `pos` on one `line`, pair (line, pos) = z[line][pos] or z[pos][line].
+//
+//   warps 0-3   epilogue: q, k (lane = pair), then g (lane = pair) and V^T (lane = channel)
+//   warps 4-11  producers: load rows, LayerNorm, write the shared operand tile (A for q/k/g, B for V^T)
+//   warp  12    control: TMA of the weights (resident), MMA issue
+// TMEM: q 0..127, k 128..255 (group A), g 256..383, V^T 384..511 (group B); each group has its own
+// full/empty barriers so the next tile's products start while the other group is being stored.
+#pragma once
+#include "row_tile.cuh"
+
+namespace b200 {
+
+struct TriAttProjParams {
+  const void* z;         // [N][N][128] fp32 or bf16
+  const float* ln_w;
+  const float* ln_b;
+  const float* g_bias;   // [128]
+  __nv_bfloat16* qkg;    // [N lines][N pos][384]
+  __nv_bfloat16* vT;     // [N lines][128][Nk]
+  int N, Nk;
+  int transposed;        // 0: starting node, 1: ending node
+  int num_tiles;         // N * ceil(N/128)
+  float eps;
+};
+
+namespace triatt_proj {
+constexpr uint32_t W_OFF = 0;                        // Wq, Wk, Wg, Wv: 4 x 32 KB
+constexpr uint32_t X_OFF = 4 * kOperandTile;         // 2 stages x 32 KB
+constexpr uint32_t GB_OFF = X_OFF + 2 * kOperandTile;  // gate bias, 512 B
+constexpr uint32_t BAR_OFF = GB_OFF + 512;
+constexpr uint32_t SMEM_BYTES = BAR_OFF + 128 + 1024;
+constexpr int THREADS = 416;
+}  // namespace triatt_proj
+
+template <bool F32>
+__global__ void __launch_bounds__(416, 1)
+triatt_proj_kernel(const __grid_constant__ CUtensorMap tmW, TriAttProjParams p) {
+  using namespace triatt_proj;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint64_t* w_full = reinterpret_cast<uint64_t*>(smem + BAR_OFF);
+  uint64_t* x_full = w_full + 1;     // [2] count 256
+  uint64_t* x_empty = x_full + 2;    // [2] commit
+  uint64_t* acc_full = x_empty + 2;  // [2] group A, group B
+  uint64_t* acc_empty = acc_full + 2;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_empty + 2);
+  float* gb_s = reinterpret_cast<float*>(smem + GB_OFF);
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const int tiles_per_line = (p.N + 127) >> 7;
+
+  if (threadIdx.x == 0) {
+    mbar_init(w_full, 1);
+    for (int i = 0; i < 2; ++i) {
+      mbar_init(&x_full[i], 256);
+      mbar_init(&x_empty[i], 1);
+      mbar_init(&acc_full[i], 1);
+      mbar_init(&acc_empty[i], 128);
+    }
+    fence_mbar_init();
+    prefetch_tmap(&tmW);
+  }
+  if (threadIdx.x < 128) gb_s[threadIdx.x] = p.g_bias[threadIdx.x];
+  if (warp == 12) tmem_alloc(tmem_slot, 512);
+  tc_fence_before_sync();
+  __syncthreads();
+  tc_fence_after_sync();
+  const uint32_t tmem_base = *tmem_slot;
+
+  if (warp == 12) {
+    if (lane == 0) {
+      mbar_arrive_expect_tx(w_full, 4 * kOperandTile);
+      for (int mt = 0; mt < 4; ++mt)
+        for (int h = 0; h < 2; ++h)
+          tma_load_2d(smem + W_OFF + mt * kOperandTile + h * kOperandHalf, &tmW, w_full, h * 64, mt * 128);
+      mbar_wait(w_full, 0, 90);
+      constexpr uint32_t idesc = make_idesc_bf16(128, 128);
+      const uint32_t w_s = smem_u32(smem + W_OFF);
+      int it = 0;
+      for (int tile = blockIdx.x; tile < p.num_tiles; tile += gridDim.x, ++it) {
+        const int s = it & 1;
+        mbar_wait(&x_full[s], (it >> 1) & 1, 91);
+        const uint32_t x_s = smem_u32(smem + X_OFF + s * kOperandTile);
+        mbar_wait(&acc_empty[0], (it & 1) ^ 1, 92);
+        tc_fence_after_sync();
+        umma_k128(tmem_base + 0, x_s, w_s + 0 * kOperandTile, idesc, false);    // q  [pair][ch]
+        umma_k128(tmem_base + 128, x_s, w_s + 1 * kOperandTile, idesc, false);  // k
+        umma_commit(&acc_full[0]);
+        mbar_wait(&acc_empty[1], (it & 1) ^ 1, 93);
+        tc_fence_after_sync();
+        umma_k128(tmem_base + 256, x_s, w_s + 2 * kOperandTile, idesc, false);  // g  [pair][ch]
+        umma_k128(tmem_base + 384, w_s + 3 * kOperandTile, x_s, idesc, false);  // V^T [ch][pair]
+        umma_commit(&acc_full[1]);
+        umma_commit(&x_empty[s]);
+      }
+    }
+  } else if (warp >= 4) {
+    const int pt = threadIdx.x - 128;
+    float gamma[8], beta[8];
+    load_gamma_beta(p.ln_w, p.ln_b, pt, gamma, beta);
+    const long long pos_stride = (p.transposed ? (long long)p.N * kD : kD) * (long long)zbytes<F32>();
+    const long long line_stride = (p.transposed ? kD : (long long)p.N * kD) * (long long)zbytes<F32>();
+    RowTile<256> regs;
+    auto load_tile = [&](int tile) {
+      const int line = tile / tiles_per_line;
+      const int pos0 = (tile - line * tiles_per_line) << 7;
+      const uint8_t* base = static_cast<const uint8_t*>(p.z) + line * line_stride;
+      regs.template load<F32, true>(
+          pt,
+          [&](int r) -> const void* {
+            const int pos = pos0 + r;
+            return pos < p.N ? base + pos * pos_stride : nullptr;
+          },
+          gamma, beta, p.eps);
+    };
+    int it = 0;
+    int tile = blockIdx.x;
+    if (tile < p.num_tiles) load_tile(tile);
+    for (; tile < p.num_tiles; tile += gridDim.x, ++it) {
+      const int s = it & 1;
+      mbar_wait(&x_empty[s], ((it >> 1) & 1) ^ 1, 94);
+      regs.store_operand(pt, smem + X_OFF + s * kOperandTile);
+      fence_proxy_async_smem();
+      mbar_arrive(&x_full[s]);
+      const int next = tile + gridDim.x;
+      if (next < p.num_tiles) load_tile(next);
+    }
+  } else {
+    const int r = warp * 32 + lane;  // TMEM lane: pair of the tile for q/k/g, channel for V^T
+    int it = 0;
+    for (int tile = blockIdx.x; tile < p.num_tiles; tile += gridDim.x, ++it) {
+      const int line = tile / tiles_per_line;
+      const int pos0 = (tile - line * tiles_per_line) << 7;
+      const bool valid = (pos0 + r) < p.N;
+      __nv_bfloat16* row = p.qkg + ((long long)line * p.N + pos0 + r) * 384;
+      // ---- group A: q, k
+      mbar_wait(&acc_full[0], it & 1, 95);
+      tc_fence_after_sync();
+#pragma unroll 1
+      for (int c = 0; c < 8; ++c) {
+        uint32_t v[32];
+        tmem_ld_32x32(tmem_addr(tmem_base, warp * 32, c * 32), v);
+        tmem_ld_wait();
+        if (valid) {
+#pragma unroll
+          for (int g = 0; g < 4; ++g)
+            *reinterpret_cast<uint4*>(row + c * 32 + g * 8) = make_uint4(
+                pack_bf16x2(__uint_as_float(v[g * 8 + 0]), __uint_as_float(v[g * 8 + 1])),
+                pack_bf16x2(__uint_as_float(v[g * 8 + 2]), __uint_as_float(v[g * 8 + 3])),
+                pack_bf16x2(__uint_as_float(v[g * 8 + 4]), __uint_as_float(v[g * 8 + 5])),
+                pack_bf16x2(__uint_as_float(v[g * 8 + 6]), __uint_as_float(v[g * 8 + 7])));
+        }
+      }
+      tc_fence_before_sync();
+      mbar_arrive(&acc_empty[0]);
+      // ---- group B: g (+ bias), V^T
+      mbar_wait(&acc_full[1], it & 1, 96);
+      tc_fence_after_sync();
+#pragma unroll 1
+      for (int c = 0; c < 4; ++c) {
+        uint32_t v[32];
+        tmem_ld_32x32(tmem_addr(tmem_base, warp * 32, 256 + c * 32), v);
+        tmem_ld_wait();
+        if (valid) {
+#pragma unroll
+          for (int g = 0; g < 4; ++g) {
+            float y[8];
+#pragma unroll
+            for (int e = 0; e < 8; ++e) y[e] = __uint_as_float(v[g * 8 + e]) + gb_s[c * 32 + g * 8 + e];
+            *reinterpret_cast<uint4*>(row + 256 + c * 32 + g * 8) = make_uint4(
+                pack_bf16x2(y[0], y[1]), pack_bf16x2(y[2], y[3]), pack_bf16x2(y[4], y[5]), pack_bf16x2(y[6], y[7]));
+          }
+        }
+      }
+      __nv_bfloat16* vrow = p.vT + ((long long)line * kD + r) * p.Nk + pos0;
+#pragma unroll 1
+      for (int c = 0; c < 4; ++c) {
+        uint32_t v[32];
+        tmem_ld_32x32(tmem_addr(tmem_base, warp * 32, 384 + c * 32), v);
+        tmem_ld_wait();
+#pragma unroll
+        for (int g = 0; g < 4; ++g) {
+          if (pos0 + c * 32 + g * 8 < p.N)
+            *reinterpret_cast<uint4*>(vrow + c * 32 + g * 8) = make_uint4(
+                pack_bf16x2(__uint_as_float(v[g * 8 + 0]), __uint_as_float(v[g * 8 + 1])),
+                pack_bf16x2(__uint_as_float(v[g * 8 + 2]), __uint_as_float(v[g * 8 + 3])),
+                pack_bf16x2(__uint_as_float(v[g * 8 + 4]), __uint_as_float(v[g * 8 + 5])),
+                pack_bf16x2(__uint_as_float(v[g * 8 + 6]), __uint_as_float(v[g * 8 + 7])));
+        }
+      }
+      tc_fence_before_sync();
+      mbar_arrive(&acc_empty[1]);
+    }
+  }
+
+  tc_fence_before_sync();
+  __syncthreads();
+  if (warp == 12) {
+    __syncwarp();
+    tmem_dealloc(tmem_base, 512);
+  }
+}
+
+}  // namespace b200

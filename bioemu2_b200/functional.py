@@ -270,3 +270,48 @@ def attention_pair_bias(s: Tensor, z: Tensor, mask: Tensor, w: ApbPacked, multip
     _lib.check(lib.b200_apb_fwd(s.data_ptr(), z.data_ptr(), m8.data_ptr(), out.data_ptr(), ctypes.byref(w.struct), B,
                                 multiplicity, N, w.c_s, w.H, sd, zd, ws.data_ptr(), nbytes, _stream()))
     return out
+
+
+class TriAttPacked:
+    """Weights of triangle attention (dim 128, 4 heads x 32) in the layouts ``b200_triatt_fwd`` expects."""
+
+    def __init__(self, ln_w, ln_b, wq, wk, wv, wb, wg, bg, wo):
+        if tuple(wq.shape) != (128, 128) or tuple(wb.shape) != (4, 128) or tuple(wo.shape) != (128, 128):
+            raise ValueError("triangle attention is built for dim=128, 4 heads of 32")
+        bf = torch.bfloat16
+        qscale = LOG2E / (32 ** 0.5)
+        self.w_qkgv = torch.cat([wq.detach().float() * qscale, wk.detach().float(), wg.detach().float(),
+                                 wv.detach().float()], dim=0).to(bf).contiguous()
+        wb16 = torch.zeros(16, 128, dtype=torch.float32, device=wb.device)
+        wb16[:4] = wb.detach().float()
+        self.w_b = wb16.to(bf).contiguous()
+        self.w_o = wo.detach().to(bf).contiguous()
+        self.f32 = [t.detach().float().contiguous() for t in (bg, ln_w, ln_b)]
+        self.struct = _lib.TriAttWeights(self.w_qkgv.data_ptr(), self.f32[0].data_ptr(), self.w_b.data_ptr(),
+                                         self.w_o.data_ptr(), self.f32[1].data_ptr(), self.f32[2].data_ptr())
+
+
+def triangle_attention(x: Tensor, mask: Tensor, w: TriAttPacked, ending: bool, add_residual: bool = False,
+                       out: Tensor | None = None) -> Tensor:
+    """Triangle attention of ``x[B,N,N,128]`` (fp32 or bf16) with ``mask[B,N,N]``; ``out`` may be ``x``."""
+    _require_cuda(x, mask)
+    if x.ndim != 4 or x.shape[1] != x.shape[2] or x.shape[3] != 128:
+        raise ValueError(f"expected x[B,N,N,128], got {tuple(x.shape)}")
+    if tuple(mask.shape) != tuple(x.shape[:3]):
+        raise ValueError(f"mask shape {tuple(mask.shape)} does not match x {tuple(x.shape)}")
+    zd = _zdtype(x)
+    if not x.is_contiguous():
+        if out is x:
+            raise ValueError("in-place update needs a contiguous pair tensor")
+        x = x.contiguous()
+    if out is None:
+        out = torch.empty_like(x)
+    elif out.dtype != x.dtype or out.shape != x.shape or not out.is_contiguous():
+        raise ValueError("out must match x in shape and dtype and be contiguous")
+    m8 = mask_u8(mask)
+    B, N = x.shape[0], x.shape[1]
+    nbytes = lib.b200_triatt_workspace_bytes(N)
+    ws = workspace(nbytes, x.device)
+    _lib.check(lib.b200_triatt_fwd(x.data_ptr(), m8.data_ptr(), out.data_ptr(), ctypes.byref(w.struct), B, N,
+                                   1 if ending else 0, 1 if add_residual else 0, zd, ws.data_ptr(), nbytes, _stream()))
+    return out

@@ -188,6 +188,37 @@ int b200_apb_fwd(const void* s, const void* z, const uint8_t* mask, void* out, c
                  int M, int N, int c_s, int H, int s_dtype, int z_dtype, void* workspace, size_t workspace_bytes,
                  b200_stream_t stream);
 
+/* ---------------------------------------------------------------------------------------------------
+ * Triangle attention around the starting (ending = 0) or ending (ending = 1) node, 4 heads x 32, c_z = 128.
+ * This op has NO counterpart in the reference (its trunk removed triangle attention,
+ * src/bioemu2/biomoa/modules/pairmixer.py:459-462); it is the AlphaFold-2 algorithm with the reference's
+ * pair-bias-attention conventions (bias-free projections except the gate, masked logits replaced by -1e6):
+ *   h = LN(x);  q, k, v = W h;  bias[j,k] = W_b h[j,k];  g = sigmoid(W_g h + b_g)
+ *   o[i,j] = softmax_k(q[i,j].k[i,k]/sqrt(32) + bias[j,k], keys masked by mask[i,k]) v[i,k];  out = W_o (g * o)
+ * with x = z (starting node) or x = z transposed in its two token axes (ending node, result transposed back).
+ *
+ *   w_qkgv bf16 [512][128]: rows 0..127 W_q * log2(e)/sqrt(32), 128..255 W_k, 256..383 W_g, 384..511 W_v
+ *   g_bias fp32 [128];  w_b bf16 [16][128] (rows 0..3 = W_b, rest zero);  w_o bf16 [128][128];  ln_w, ln_b fp32 [128]
+ *
+ * z, out: [B][N][N][128] of z_dtype; mask: uint8 [B][N][N].  With add_residual the result is z + update.
+ * `out` may alias `z`: z is fully consumed by the projection stage before the output stage writes.
+ * Workspace: b200_triatt_workspace_bytes(N) bytes, 1024-byte aligned.
+ * ------------------------------------------------------------------------------------------------- */
+typedef struct {
+  const void* w_qkgv;
+  const float* g_bias;
+  const void* w_b;
+  const void* w_o;
+  const float* ln_w;
+  const float* ln_b;
+} b200_triatt_weights;
+
+size_t b200_triatt_workspace_bytes(int N);
+
+int b200_triatt_fwd(const void* z, const uint8_t* mask, void* out, const b200_triatt_weights* w, int B, int N,
+                    int ending, int add_residual, int z_dtype, void* workspace, size_t workspace_bytes,
+                    b200_stream_t stream);
+
 #ifdef __cplusplus
 }
 #endif
