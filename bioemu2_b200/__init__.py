@@ -8,7 +8,9 @@ from .outer_product_mean import (
     OuterProductMeanTritonMemorySaving,
     OuterProductMeanVanilla,
 )
+from .pairformer import PairformerBlock, PairformerModule
 from .pairmixer import PairMixerLayer, PairMixerModule
+from .transformer import AttentionLayer, ConditionedTransformerLayer
 from .transition import Transition
 from .triangle_attention import (
     TriangleAttention,
@@ -27,6 +29,10 @@ __all__ = [
     "OuterProductMean",
     "OuterProductMeanTritonMemorySaving",
     "OuterProductMeanVanilla",
+    "AttentionLayer",
+    "ConditionedTransformerLayer",
+    "PairformerBlock",
+    "PairformerModule",
     "PairMixerLayer",
     "PairMixerModule",
     "Transition",

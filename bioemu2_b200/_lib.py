@@ -70,6 +70,14 @@ SIGNATURES = {
     "b200_triatt_workspace_bytes": (c_size_t, [c_int]),
     "b200_triatt_fwd": (c_int, [c_void_p, c_void_p, c_void_p, POINTER(TriAttWeights), c_int, c_int, c_int, c_int,
                                 c_int, c_void_p, c_size_t, c_void_p]),
+    "b200_rows_to_bf16": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_int, c_int, c_int, c_int, c_void_p]),
+    "b200_linear_bf16": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_int, c_int, c_int,
+                                 c_void_p]),
+    "b200_swiglu_fwd": (c_int, [c_void_p, c_void_p, c_int64, c_int, c_void_p]),
+    "b200_adaln_fwd": (c_int, [c_void_p, c_void_p, c_int, c_int, c_int, c_float, c_void_p, c_int64, c_int, c_int,
+                               c_void_p]),
+    "b200_gated_residual_fwd": (c_int, [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int64, c_int, c_int, c_int,
+                                        c_void_p]),
 }
 
 if not os.path.exists(LIB_PATH):

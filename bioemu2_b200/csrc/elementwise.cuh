@@ -16,7 +16,7 @@ template <bool F32IN>
 __global__ void __launch_bounds__(256)
 layernorm_rows_kernel(const void* __restrict__ x, __nv_bfloat16* __restrict__ y,
                       const float* __restrict__ w, const float* __restrict__ b, long long rows, int cols,
-                      float eps, int normalize) {
+                      float eps, int normalize, int silu) {
   const int lane = threadIdx.x & 31;
   const int nvec = cols >> 3;
   const long long warp_global = (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
@@ -80,11 +80,105 @@ layernorm_rows_kernel(const void* __restrict__ x, __nv_bfloat16* __restrict__ y,
             a += b[c0];
             c += b[c0 + 1];
           }
+          if (silu) {
+            a *= sigmoid_fast(a);
+            c *= sigmoid_fast(c);
+          }
           o[e] = pack_bf16x2(a, c);
         }
         yr[vi] = make_uint4(o[0], o[1], o[2], o[3]);
       }
     }
+  }
+}
+
+// h[r, j] = silu(h12[r, j]) * h12[r, H + j]   (bf16 in, bf16 out; H multiple of 8)
+__global__ void __launch_bounds__(256)
+swiglu_rows_kernel(const __nv_bfloat16* __restrict__ h12, __nv_bfloat16* __restrict__ h, long long rows, int H) {
+  const int nvec = H >> 3;
+  const long long total = rows * nvec;
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (long long)gridDim.x * blockDim.x) {
+    const long long r = i / nvec;
+    const int v = int(i - r * nvec);
+    float a[8], b[8];
+    load8<false>(h12 + r * 2 * H, v * 8, a);
+    load8<false>(h12 + r * 2 * H + H, v * 8, b);
+#pragma unroll
+    for (int e = 0; e < 8; ++e) a[e] = a[e] * sigmoid_fast(a[e]) * b[e];
+    store8<false>(h + r * H, v * 8, a);
+  }
+}
+
+// y[r,:] = lns * (LN(x[r,:]) * (1 + alpha[r,:]) + beta[r,:]) with alpha/beta columns of a [rows][cw] fp32 tensor
+// (adaptive LayerNorm without learned affine); x fp32 or bf16, y bf16.  One warp per row, cols <= 1024.
+template <bool F32IN>
+__global__ void __launch_bounds__(256)
+adaln_rows_kernel(const void* __restrict__ x, const float* __restrict__ cond, int cw, int alpha_col, int beta_col,
+                  float lns, __nv_bfloat16* __restrict__ y, long long rows, int cols, float eps) {
+  const int lane = threadIdx.x & 31;
+  const int nvec = cols >> 3;
+  const long long warp_global = (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  const long long warp_stride = (long long)gridDim.x * (blockDim.x >> 5);
+  const float inv = 1.0f / float(cols);
+  for (long long r = warp_global; r < rows; r += warp_stride) {
+    const uint8_t* xr = static_cast<const uint8_t*>(x) + r * cols * (long long)(F32IN ? 4 : 2);
+    float f[4][8];
+    float s = 0.f;
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const int vi = lane + i * 32;
+      if (vi < nvec) {
+        load8<F32IN>(xr, vi * 8, f[i]);
+#pragma unroll
+        for (int e = 0; e < 8; ++e) s += f[i][e];
+      }
+    }
+    const float mean = warp_sum(s) * inv;
+    float ss = 0.f;
+#pragma unroll
+    for (int i = 0; i < 4; ++i)
+      if (lane + i * 32 < nvec) {
+#pragma unroll
+        for (int e = 0; e < 8; ++e) {
+          f[i][e] -= mean;
+          ss = fmaf(f[i][e], f[i][e], ss);
+        }
+      }
+    const float rstd = rsqrtf(warp_sum(ss) * inv + eps);
+    const float* cr = cond + r * cw;
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const int vi = lane + i * 32;
+      if (vi < nvec) {
+        float al[8], be[8];
+        load8<true>(cr + alpha_col, vi * 8, al);
+        load8<true>(cr + beta_col, vi * 8, be);
+#pragma unroll
+        for (int e = 0; e < 8; ++e) f[i][e] = lns * fmaf(f[i][e] * rstd, 1.0f + al[e], be[e]);
+        store8<false>(y + r * cols, vi * 8, f[i]);
+      }
+    }
+  }
+}
+
+// x[r,:] += gamma[r,:] * h[r,:]  (gamma: columns of a [rows][cw] fp32 tensor; x and h fp32 or bf16)
+template <bool XF32, bool HF32>
+__global__ void __launch_bounds__(256)
+gated_residual_rows_kernel(void* __restrict__ x, const void* __restrict__ h, const float* __restrict__ cond, int cw,
+                           int gamma_col, long long rows, int cols) {
+  const int nvec = cols >> 3;
+  const long long total = rows * nvec;
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (long long)gridDim.x * blockDim.x) {
+    const long long r = i / nvec;
+    const int v = int(i - r * nvec);
+    float a[8], b[8], g[8];
+    uint8_t* xr = static_cast<uint8_t*>(x) + r * cols * (long long)(XF32 ? 4 : 2);
+    load8<XF32>(xr, v * 8, a);
+    load8<HF32>(static_cast<const uint8_t*>(h) + r * cols * (long long)(HF32 ? 4 : 2), v * 8, b);
+    load8<true>(cond + r * cw + gamma_col, v * 8, g);
+#pragma unroll
+    for (int e = 0; e < 8; ++e) a[e] = fmaf(g[e], b[e], a[e]);
+    store8<XF32>(xr, v * 8, a);
   }
 }
 

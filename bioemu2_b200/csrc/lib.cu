@@ -83,16 +83,16 @@ static int launch_bmm(const BmmLaunch& a, cudaStream_t stream) {
 }
 
 static int launch_rows_to_bf16(const void* x, bool f32, __nv_bfloat16* y, const float* w, const float* b,
-                               int64_t rows, int cols, bool normalize, cudaStream_t stream) {
+                               int64_t rows, int cols, bool normalize, cudaStream_t stream, bool silu = false) {
   const int warps = 8;
   int64_t blocks = (rows + warps - 1) / warps;
   const int64_t cap = int64_t(sm_count()) * 16;
   if (blocks > cap) blocks = cap;
   if (blocks < 1) blocks = 1;
   if (f32)
-    layernorm_rows_kernel<true><<<int(blocks), warps * 32, 0, stream>>>(x, y, w, b, rows, cols, 1e-5f, normalize);
+    layernorm_rows_kernel<true><<<int(blocks), warps * 32, 0, stream>>>(x, y, w, b, rows, cols, 1e-5f, normalize, silu);
   else
-    layernorm_rows_kernel<false><<<int(blocks), warps * 32, 0, stream>>>(x, y, w, b, rows, cols, 1e-5f, normalize);
+    layernorm_rows_kernel<false><<<int(blocks), warps * 32, 0, stream>>>(x, y, w, b, rows, cols, 1e-5f, normalize, silu);
   B200_CUDA(cudaGetLastError());
   return 0;
 }
@@ -230,7 +230,7 @@ int b200_layernorm_fwd(const void* x, void* y, const float* w, const float* b, i
   const int64_t cap = int64_t(sm_count()) * 16;
   if (blocks > cap) blocks = cap;
   layernorm_rows_kernel<false><<<int(blocks), warps * 32, 0, static_cast<cudaStream_t>(stream)>>>(
-      x, static_cast<__nv_bfloat16*>(y), w, b, rows, cols, eps, 1);
+      x, static_cast<__nv_bfloat16*>(y), w, b, rows, cols, eps, 1, 0);
   B200_CUDA(cudaGetLastError());
   return B200_OK;
 }
@@ -752,6 +752,98 @@ int b200_triatt_fwd(const void* z, const uint8_t* mask, void* out, const b200_tr
       if (int e = launch_bmm(a, stream)) return e;
     }
   }
+  return B200_OK;
+}
+
+// ------------------------------------------------------------------------------------------------ single-track helpers
+static int grid_for(int64_t work_items, int per_block) {
+  int64_t blocks = (work_items + per_block - 1) / per_block;
+  const int64_t cap = int64_t(sm_count()) * 16;
+  if (blocks > cap) blocks = cap;
+  if (blocks < 1) blocks = 1;
+  return int(blocks);
+}
+
+int b200_rows_to_bf16(const void* x, void* y, const float* w, const float* b, int64_t rows, int cols, int x_dtype,
+                      int normalize, int silu, b200_stream_t stream) {
+  if (int e = b200_check_device()) return e;
+  B200_CHECK_ARG(x && y, "x/y is NULL");
+  B200_CHECK_ARG(rows >= 0 && cols > 0 && cols % 8 == 0 && cols <= 1024, "cols=%d must be a multiple of 8, <= 1024", cols);
+  B200_CHECK_ARG((x_dtype | 1) == 1, "unknown dtype");
+  B200_CHECK_ARG(aligned(x, 32) && aligned(y, 16), "x must be 32-byte aligned, y 16-byte aligned");
+  if (rows == 0) return B200_OK;
+  return launch_rows_to_bf16(x, x_dtype == B200_DTYPE_F32, static_cast<__nv_bfloat16*>(y), w, b, rows, cols,
+                             normalize != 0, static_cast<cudaStream_t>(stream), silu != 0);
+}
+
+int b200_linear_bf16(const void* x, const void* w, const float* bias, const void* residual, void* out, int64_t rows,
+                     int in_features, int out_features, int out_dtype, b200_stream_t stream) {
+  if (int e = b200_check_device()) return e;
+  B200_CHECK_ARG(x && w && out, "x/w/out is NULL");
+  B200_CHECK_ARG(rows > 0 && rows < (int64_t(1) << 31), "rows out of range");
+  B200_CHECK_ARG(in_features > 0 && in_features % 8 == 0 && out_features > 0 && out_features % 8 == 0,
+                 "in_features=%d and out_features=%d must be positive multiples of 8", in_features, out_features);
+  B200_CHECK_ARG((out_dtype | 1) == 1, "unknown dtype");
+  B200_CHECK_ARG(aligned(x, 16) && aligned(w, 16) && aligned(out, 32) && (!residual || aligned(residual, 32)),
+                 "x/w must be 16-byte aligned, out/residual 32-byte aligned");
+  BmmLaunch a{x, w, out, 1, int(rows), out_features, in_features, in_features, in_features, out_features, 0, 0, 0};
+  a.bias = bias;
+  a.residual = residual;
+  a.out_f32 = out_dtype == B200_DTYPE_F32;
+  return launch_bmm(a, static_cast<cudaStream_t>(stream));
+}
+
+int b200_swiglu_fwd(const void* h12, void* h, int64_t rows, int hidden, b200_stream_t stream) {
+  if (int e = b200_check_device()) return e;
+  B200_CHECK_ARG(h12 && h, "h12/h is NULL");
+  B200_CHECK_ARG(rows >= 0 && hidden > 0 && hidden % 8 == 0, "hidden=%d must be a positive multiple of 8", hidden);
+  B200_CHECK_ARG(aligned(h12, 16) && aligned(h, 16), "h12/h must be 16-byte aligned");
+  if (rows == 0) return B200_OK;
+  swiglu_rows_kernel<<<grid_for(rows * (hidden / 8), 256), 256, 0, static_cast<cudaStream_t>(stream)>>>(
+      static_cast<const __nv_bfloat16*>(h12), static_cast<__nv_bfloat16*>(h), rows, hidden);
+  B200_CUDA(cudaGetLastError());
+  return B200_OK;
+}
+
+int b200_adaln_fwd(const void* x, const float* cond, int cond_width, int alpha_col, int beta_col, float lns, void* y,
+                   int64_t rows, int cols, int x_dtype, b200_stream_t stream) {
+  if (int e = b200_check_device()) return e;
+  B200_CHECK_ARG(x && cond && y, "x/cond/y is NULL");
+  B200_CHECK_ARG(rows >= 0 && cols > 0 && cols % 8 == 0 && cols <= 1024, "cols=%d must be a multiple of 8, <= 1024", cols);
+  B200_CHECK_ARG(cond_width % 8 == 0 && alpha_col % 8 == 0 && beta_col % 8 == 0 && alpha_col + cols <= cond_width &&
+                     beta_col + cols <= cond_width, "bad conditioning layout");
+  B200_CHECK_ARG((x_dtype | 1) == 1, "unknown dtype");
+  B200_CHECK_ARG(aligned(x, 32) && aligned(cond, 32) && aligned(y, 16), "x/cond must be 32-byte aligned, y 16-byte");
+  if (rows == 0) return B200_OK;
+  const int grid = grid_for(rows, 8);
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  if (x_dtype == B200_DTYPE_F32)
+    adaln_rows_kernel<true><<<grid, 256, 0, st>>>(x, cond, cond_width, alpha_col, beta_col, lns,
+                                                  static_cast<__nv_bfloat16*>(y), rows, cols, 1e-5f);
+  else
+    adaln_rows_kernel<false><<<grid, 256, 0, st>>>(x, cond, cond_width, alpha_col, beta_col, lns,
+                                                   static_cast<__nv_bfloat16*>(y), rows, cols, 1e-5f);
+  B200_CUDA(cudaGetLastError());
+  return B200_OK;
+}
+
+int b200_gated_residual_fwd(void* x, const void* h, const float* cond, int cond_width, int gamma_col, int64_t rows,
+                            int cols, int x_dtype, int h_dtype, b200_stream_t stream) {
+  if (int e = b200_check_device()) return e;
+  B200_CHECK_ARG(x && h && cond, "x/h/cond is NULL");
+  B200_CHECK_ARG(rows >= 0 && cols > 0 && cols % 8 == 0, "cols=%d must be a positive multiple of 8", cols);
+  B200_CHECK_ARG(cond_width % 8 == 0 && gamma_col % 8 == 0 && gamma_col + cols <= cond_width, "bad conditioning layout");
+  B200_CHECK_ARG((x_dtype | 1) == 1 && (h_dtype | 1) == 1, "unknown dtype");
+  B200_CHECK_ARG(aligned(x, 32) && aligned(h, 32) && aligned(cond, 32), "x/h/cond must be 32-byte aligned");
+  if (rows == 0) return B200_OK;
+  const int grid = grid_for(rows * (cols / 8), 256);
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  const bool xf = x_dtype == B200_DTYPE_F32, hf = h_dtype == B200_DTYPE_F32;
+  if (xf && hf) gated_residual_rows_kernel<true, true><<<grid, 256, 0, st>>>(x, h, cond, cond_width, gamma_col, rows, cols);
+  else if (xf) gated_residual_rows_kernel<true, false><<<grid, 256, 0, st>>>(x, h, cond, cond_width, gamma_col, rows, cols);
+  else if (hf) gated_residual_rows_kernel<false, true><<<grid, 256, 0, st>>>(x, h, cond, cond_width, gamma_col, rows, cols);
+  else gated_residual_rows_kernel<false, false><<<grid, 256, 0, st>>>(x, h, cond, cond_width, gamma_col, rows, cols);
+  B200_CUDA(cudaGetLastError());
   return B200_OK;
 }
 

@@ -315,3 +315,100 @@ def triangle_attention(x: Tensor, mask: Tensor, w: TriAttPacked, ending: bool, a
     _lib.check(lib.b200_triatt_fwd(x.data_ptr(), m8.data_ptr(), out.data_ptr(), ctypes.byref(w.struct), B, N,
                                    1 if ending else 0, 1 if add_residual else 0, zd, ws.data_ptr(), nbytes, _stream()))
     return out
+
+
+# ----------------------------------------------------------------------------------- single-track building blocks
+def _ptr(t: Tensor | None):
+    return t.data_ptr() if t is not None else None
+
+
+def rows_to_bf16(x: Tensor, weight: Tensor | None = None, bias: Tensor | None = None, normalize: bool = True,
+                 silu: bool = False) -> Tensor:
+    """``[silu]([LayerNorm](x) * weight + bias)`` over the last axis as bf16 (x fp32 or bf16)."""
+    _require_cuda(x)
+    xd = _zdtype(x)
+    x = x.contiguous()
+    cols = x.shape[-1]
+    y = torch.empty(x.shape, dtype=torch.bfloat16, device=x.device)
+    w = weight.detach().float().contiguous() if weight is not None else None
+    b = bias.detach().float().contiguous() if bias is not None else None
+    _lib.check(lib.b200_rows_to_bf16(x.data_ptr(), y.data_ptr(), _ptr(w), _ptr(b), x.numel() // cols, cols, xd,
+                                     1 if normalize else 0, 1 if silu else 0, _stream()))
+    return y
+
+
+def linear_bf16(x: Tensor, w_bf16: Tensor, bias_f32: Tensor | None = None, residual: Tensor | None = None,
+                out_dtype: torch.dtype = torch.bfloat16, out: Tensor | None = None) -> Tensor:
+    """``x @ w.T [+ bias] [+ residual]`` with bf16 ``x[..., in]`` and ``w[out, in]``; ``out`` may be ``residual``."""
+    _require_cuda(x, w_bf16)
+    if x.dtype != torch.bfloat16 or w_bf16.dtype != torch.bfloat16:
+        raise ValueError("linear_bf16 expects bfloat16 x and w")
+    x = x.contiguous()
+    fin, fout = x.shape[-1], w_bf16.shape[0]
+    if w_bf16.shape[1] != fin:
+        raise ValueError(f"weight {tuple(w_bf16.shape)} does not match input width {fin}")
+    rows = x.numel() // fin
+    if out is None:
+        out = torch.empty(x.shape[:-1] + (fout,), dtype=out_dtype, device=x.device)
+    od = _zdtype(out)
+    if residual is not None and (residual.dtype != out.dtype or residual.shape != out.shape or not residual.is_contiguous()):
+        raise ValueError("residual must match the output in shape and dtype and be contiguous")
+    _lib.check(lib.b200_linear_bf16(x.data_ptr(), w_bf16.data_ptr(), _ptr(bias_f32), _ptr(residual), out.data_ptr(),
+                                    rows, fin, fout, od, _stream()))
+    return out
+
+
+def swiglu(h12: Tensor) -> Tensor:
+    """``silu(h12[..., :H]) * h12[..., H:]`` for bf16 ``h12[..., 2H]``."""
+    H = h12.shape[-1] // 2
+    h12 = h12.contiguous()
+    out = torch.empty(h12.shape[:-1] + (H,), dtype=torch.bfloat16, device=h12.device)
+    _lib.check(lib.b200_swiglu_fwd(h12.data_ptr(), out.data_ptr(), h12.numel() // (2 * H), H, _stream()))
+    return out
+
+
+def adaln(x: Tensor, cond: Tensor, alpha_col: int, beta_col: int, lns: float) -> Tensor:
+    """``lns * (LN(x) * (1 + alpha) + beta)`` as bf16; alpha/beta are column blocks of fp32 ``cond[rows, cw]``."""
+    xd = _zdtype(x)
+    x = x.contiguous()
+    cols = x.shape[-1]
+    y = torch.empty(x.shape, dtype=torch.bfloat16, device=x.device)
+    _lib.check(lib.b200_adaln_fwd(x.data_ptr(), cond.data_ptr(), cond.shape[-1], alpha_col, beta_col, float(lns),
+                                  y.data_ptr(), x.numel() // cols, cols, xd, _stream()))
+    return y
+
+
+def gated_residual_(x: Tensor, h: Tensor, cond: Tensor, gamma_col: int) -> Tensor:
+    """``x += gamma * h`` in place (gamma a column block of fp32 ``cond``); returns ``x``."""
+    if not x.is_contiguous() or not h.is_contiguous():
+        raise ValueError("gated_residual_ needs contiguous tensors")
+    cols = x.shape[-1]
+    _lib.check(lib.b200_gated_residual_fwd(x.data_ptr(), h.data_ptr(), cond.data_ptr(), cond.shape[-1], gamma_col,
+                                           x.numel() // cols, cols, _zdtype(x), _zdtype(h), _stream()))
+    return x
+
+
+class TransitionGenericPacked:
+    """Weights of a SwiGLU transition of any width (multiples of 8): ``w12 = [fc1; fc2]``, ``w3``."""
+
+    def __init__(self, norm_w, norm_b, fc1, fc2, fc3):
+        bf = torch.bfloat16
+        self.w12 = torch.cat([fc1.detach(), fc2.detach()], dim=0).to(bf).contiguous()
+        self.w3 = fc3.detach().to(bf).contiguous()
+        self.norm_w, self.norm_b = norm_w, norm_b
+        if fc1.shape[0] % 8 or fc1.shape[1] % 8 or fc3.shape[0] % 8 or fc1.shape[1] > 1024:
+            raise ValueError("transition widths must be multiples of 8 and the input width at most 1024")
+
+
+def transition_generic(x: Tensor, w: TransitionGenericPacked, add_residual: bool = False,
+                       out: Tensor | None = None) -> Tensor:
+    """Un-fused transition for the single track: LayerNorm/convert, fc1|fc2 GEMM, SwiGLU, fc3 GEMM (+ residual)."""
+    _require_cuda(x)
+    x = x.contiguous()
+    xb = x if (x.dtype == torch.bfloat16 and w.norm_w is None) else rows_to_bf16(
+        x, w.norm_w, w.norm_b, normalize=w.norm_w is not None)
+    h = swiglu(linear_bf16(xb, w.w12))
+    same_width = w.w3.shape[0] == x.shape[-1]
+    if add_residual and not same_width:
+        raise ValueError("the residual needs out_dim == dim")
+    return linear_bf16(h, w.w3, residual=x if add_residual else None, out_dtype=x.dtype, out=out)

@@ -1,0 +1,68 @@
+"""The composite Pairformer block the benchmark configurations describe, and its stack.
+
+Pair track: triangle multiplication outgoing / incoming, triangle attention starting / ending node, pair
+transition; single track: attention with pair bias (bias projected from z) and a transition; every
+sub-block is residual.  The reference's own trunk block (``PairMixerLayer``, ``bioemu2_b200.pairmixer``) is
+the first two and the fifth of these (src/bioemu2/biomoa/modules/pairmixer.py:430-456); the attention
+sub-blocks are ``AttentionPairBias`` (src/bioemu2/biomoa/ops/attention_pair_bias.py:42) and the triangle
+attention of ``bioemu2_b200.triangle_attention``, which the reference lacks.
+
+Sub-module names: ``tri_mul_out``, ``tri_mul_in``, ``tri_att_start``, ``tri_att_end``, ``transition_z``,
+``attention``, ``transition_s``.
+"""
+from __future__ import annotations
+
+import torch
+import torch.nn as nn
+from torch import Tensor
+
+from .attention_pair_bias import AttentionPairBias
+from .transition import Transition
+from .triangle_attention import TriangleAttention
+from .triangle_multiplication import TriangleMultiplication
+
+
+class PairformerBlock(nn.Module):
+    def __init__(self, token_s: int = 384, token_z: int = 128, tri_heads: int = 4, tri_head_dim: int = 32,
+                 apb_heads: int = 16) -> None:
+        super().__init__()
+        self.tri_mul_out = TriangleMultiplication(token_z, "outgoing")
+        self.tri_mul_in = TriangleMultiplication(token_z, "incoming")
+        self.tri_att_start = TriangleAttention(token_z, tri_heads, tri_head_dim, ending=False)
+        self.tri_att_end = TriangleAttention(token_z, tri_heads, tri_head_dim, ending=True)
+        self.transition_z = Transition(token_z, 4 * token_z)
+        self.attention = AttentionPairBias(token_s, token_z, apb_heads)
+        self.transition_s = Transition(token_s, 4 * token_s)
+
+    def forward_(self, s: Tensor, z: Tensor, token_mask: Tensor, pair_mask_u8: Tensor) -> tuple[Tensor, Tensor]:
+        """In-place form: updates ``s`` and ``z`` (contiguous, fp32 or bf16) and returns them."""
+        self.tri_mul_out.forward_residual_(z, pair_mask_u8)
+        self.tri_mul_in.forward_residual_(z, pair_mask_u8)
+        self.tri_att_start.forward_residual_(z, pair_mask_u8)
+        self.tri_att_end.forward_residual_(z, pair_mask_u8)
+        self.transition_z.forward_residual_(z)
+        s += self.attention(s, z, token_mask)
+        self.transition_s.forward_residual_(s)
+        return s, z
+
+    def forward(self, s: Tensor, z: Tensor, token_mask: Tensor) -> tuple[Tensor, Tensor]:
+        if self.training:
+            raise RuntimeError("bioemu2_b200 modules are inference-only: call .eval()")
+        pm = (token_mask[:, :, None] & token_mask[:, None, :]).to(torch.uint8)
+        return self.forward_(s.clone(), z.clone(), token_mask, pm)
+
+
+class PairformerModule(nn.Module):
+    def __init__(self, token_s: int = 384, token_z: int = 128, num_blocks: int = 48, **block_kwargs) -> None:
+        super().__init__()
+        self.num_blocks = num_blocks
+        self.layers = nn.ModuleList([PairformerBlock(token_s, token_z, **block_kwargs) for _ in range(num_blocks)])
+
+    def forward(self, s: Tensor, z: Tensor, token_mask: Tensor) -> tuple[Tensor, Tensor]:
+        if self.training:
+            raise RuntimeError("bioemu2_b200 modules are inference-only: call .eval()")
+        s, z = s.clone(), z.clone()
+        pm = (token_mask[:, :, None] & token_mask[:, None, :]).to(torch.uint8)
+        for layer in self.layers:
+            layer.forward_(s, z, token_mask, pm)
+        return s, z

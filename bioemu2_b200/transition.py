@@ -2,7 +2,8 @@
 
 ``fc3(silu(fc1(norm(x))) * fc2(norm(x)))``.  ``chunk_size`` exists in the reference to bound the
 memory of the hidden activations; the fused kernel never materialises them, so it is accepted and
-ignored.  The fused kernel covers the pair transition (dim 128, hidden 512).
+ignored.  The pair transition (dim 128, hidden 512) runs as one fused kernel; other widths (the single
+track: 384 -> 1536, 768 -> 4*768) run as LayerNorm, two tcgen05 GEMMs and a SwiGLU kernel.
 """
 from __future__ import annotations
 
@@ -26,17 +27,22 @@ class Transition(PackedWeightsMixin, nn.Module):
         self.fc2 = nn.Linear(dim, hidden, bias=False)
         self.fc3 = nn.Linear(hidden, out_dim, bias=False)
         self.hidden = hidden
-        if (dim, hidden, out_dim) != (128, 512, 128):
-            raise ValueError("bioemu2_b200.Transition currently covers dim=128, hidden=512 (the pair transition)")
+        self._fused = (dim, hidden, out_dim) == (128, 512, 128)
+        if not self._fused and (dim % 8 or hidden % 8 or out_dim % 8 or dim > 1024):
+            raise ValueError("bioemu2_b200.Transition needs widths that are multiples of 8 and dim <= 1024")
 
     def _build_packed(self):
-        return F.TransitionPacked(self.norm.weight if self.use_norm else None,
-                                  self.norm.bias if self.use_norm else None,
-                                  self.fc1.weight, self.fc2.weight, self.fc3.weight)
+        cls = F.TransitionPacked if self._fused else F.TransitionGenericPacked
+        return cls(self.norm.weight if self.use_norm else None, self.norm.bias if self.use_norm else None,
+                   self.fc1.weight, self.fc2.weight, self.fc3.weight)
 
     def forward(self, x: Tensor) -> Tensor:
-        return F.transition(x, self.packed())
+        if self._fused:
+            return F.transition(x, self.packed())
+        return F.transition_generic(x, self.packed())
 
     def forward_residual_(self, x: Tensor) -> Tensor:
         """``x += forward(x)`` in place, fused into the kernel's final store; returns ``x``."""
-        return F.transition(x, self.packed(), add_residual=True, out=x)
+        if self._fused:
+            return F.transition(x, self.packed(), add_residual=True, out=x)
+        return F.transition_generic(x, self.packed(), add_residual=True, out=x)

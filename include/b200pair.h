@@ -219,6 +219,29 @@ int b200_triatt_fwd(const void* z, const uint8_t* mask, void* out, const b200_tr
                     int ending, int add_residual, int z_dtype, void* workspace, size_t workspace_bytes,
                     b200_stream_t stream);
 
+/* ---------------------------------------------------------------------------------------------------
+ * Single-track building blocks (token stream [rows][cols], rows = B*M*N): the pieces of
+ * Transition.forward for widths other than 128/512 (src/bioemu2/biomoa/ops/transition.py:52-76) and of
+ * ConditionedTransformerLayer.forward (src/bioemu2/biomoa/modules/transformer.py:26-53,317-353).
+ *
+ * b200_rows_to_bf16      y = [silu]([LN](x) * w + b) as bf16; normalize = 0 only converts.  w/b may be NULL.
+ * b200_linear_bf16       out = x w^T [+ bias] [+ residual]; x bf16 [rows][in], w bf16 [out][in] (nn.Linear
+ *                        layout), out/residual [rows][out] of out_dtype (residual may alias out).
+ * b200_swiglu_fwd        h = silu(h12[:, :hidden]) * h12[:, hidden:], bf16.
+ * b200_adaln_fwd         y = lns * (LN(x) * (1 + alpha) + beta), no learned affine (ada_ln, transformer.py:26-41);
+ *                        alpha/beta are column blocks of the fp32 conditioning tensor cond[rows][cond_width].
+ * b200_gated_residual_fwd  x += gamma * h in place (ada_scale + residual, transformer.py:349,352).
+ * ------------------------------------------------------------------------------------------------- */
+int b200_rows_to_bf16(const void* x, void* y, const float* w, const float* b, int64_t rows, int cols, int x_dtype,
+                      int normalize, int silu, b200_stream_t stream);
+int b200_linear_bf16(const void* x, const void* w, const float* bias, const void* residual, void* out, int64_t rows,
+                     int in_features, int out_features, int out_dtype, b200_stream_t stream);
+int b200_swiglu_fwd(const void* h12, void* h, int64_t rows, int hidden, b200_stream_t stream);
+int b200_adaln_fwd(const void* x, const float* cond, int cond_width, int alpha_col, int beta_col, float lns, void* y,
+                   int64_t rows, int cols, int x_dtype, b200_stream_t stream);
+int b200_gated_residual_fwd(void* x, const void* h, const float* cond, int cond_width, int gamma_col, int64_t rows,
+                            int cols, int x_dtype, int h_dtype, b200_stream_t stream);
+
 #ifdef __cplusplus
 }
 #endif
