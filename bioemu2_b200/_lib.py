@@ -59,6 +59,8 @@ SIGNATURES = {
     "b200_trimul_workspace_bytes": (c_size_t, [c_int]),
     "b200_trimul_fwd": (c_int, [c_void_p, c_void_p, c_void_p, POINTER(TriMulWeights), c_int, c_int, c_int, c_int,
                                 c_int, c_void_p, c_size_t, c_void_p]),
+    "b200_trimul_fwd_static": (c_int, [c_void_p, c_void_p, c_void_p, POINTER(TriMulWeights), c_int, c_int, c_int,
+                                       c_int, c_int, c_void_p]),
     "b200_transition_fwd": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_int,
                                     c_int, c_int, c_void_p]),
     "b200_opm_workspace_bytes": (c_size_t, [c_int, c_int]),
@@ -83,7 +85,7 @@ SIGNATURES = {
 if not os.path.exists(LIB_PATH):
     raise ImportError(
         f"{LIB_PATH} is missing: the CUDA library has not been built "
-        "(run `python -m bioemu2_b200.build`). There is no CPU or PyTorch fallback."
+        "(run `python __graft_entry__.py` at the repository root). There is no CPU or PyTorch fallback."
     )
 
 lib = ctypes.CDLL(LIB_PATH)

@@ -1,4 +1,4 @@
-"""Build the CUDA library in-tree: ``python -m bioemu2_b200.build``.
+"""Build the CUDA library in-tree: ``python bioemu2_b200/build.py`` (or ``python __graft_entry__.py``).
 
 One nvcc invocation compiles ``csrc/lib.cu`` (which includes every kernel) for sm_100a into
 ``libb200pair.so`` beside this file.  nvcc cross-compiles, so no GPU is needed to build.

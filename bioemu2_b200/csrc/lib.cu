@@ -404,6 +404,36 @@ int b200_transition_fwd(const void* x, void* out, const void* w13, const void* w
   return B200_OK;
 }
 
+// ------------------------------------------------------------------------------------------------ no-allocation variant
+// Scratch for b200_trimul_fwd_static: the three channel-major planes a, b, t for N <= 256 (padded to 256),
+// plus slack so the base can be rounded up to the 1024-byte alignment the kernels' launcher asks for.
+// It lives in the library image: every GPU that loads the library holds these 48 MiB until the process exits.
+#define B200_STATIC_TRIMUL_MAX_N 256
+static __device__ __align__(256) unsigned char g_trimul_static_scratch[size_t(3) * 128 * 256 * 256 * 2 + 1024];
+
+// Device address of the scratch per device ordinal, resolved on first use with that device current.
+// (In host code the array's name is only a handle for the runtime, never a pointer a kernel may be given.)
+static void* g_trimul_static_ptr[64] = {nullptr};
+
+int b200_trimul_fwd_static(const void* z, const uint8_t* mask, void* out, const b200_trimul_weights* w, int B, int N,
+                           int incoming, int add_residual, int z_dtype, b200_stream_t stream) {
+  if (int e = b200_check_device()) return e;
+  B200_CHECK_ARG(N > 0 && N <= B200_STATIC_TRIMUL_MAX_N,
+                 "b200_trimul_fwd_static handles N <= %d (got %d); use b200_trimul_fwd with a caller workspace",
+                 B200_STATIC_TRIMUL_MAX_N, N);
+  int dev = 0;
+  B200_CUDA(cudaGetDevice(&dev));
+  B200_CHECK_ARG(dev >= 0 && dev < 64, "device ordinal %d out of range", dev);
+  if (!g_trimul_static_ptr[dev]) {
+    void* ptr = nullptr;
+    B200_CUDA(cudaGetSymbolAddress(&ptr, g_trimul_static_scratch));
+    g_trimul_static_ptr[dev] = ptr;
+  }
+  uintptr_t base = (reinterpret_cast<uintptr_t>(g_trimul_static_ptr[dev]) + 1023) & ~uintptr_t(1023);
+  return b200_trimul_fwd(z, mask, out, w, B, N, incoming, add_residual, z_dtype, reinterpret_cast<void*>(base),
+                         b200_trimul_workspace_bytes(N), stream);
+}
+
 // ------------------------------------------------------------------------------------------------ OPM
 static void opm_plan(int S, int N, int* Sp, int* CI, size_t* ab_bytes, size_t* outer_bytes) {
   *Sp = (S + 7) / 8 * 8;

@@ -107,6 +107,25 @@ int b200_trimul_fwd(const void* z, const uint8_t* mask, void* out, const b200_tr
                     b200_stream_t stream);
 
 /* ---------------------------------------------------------------------------------------------------
+ * Triangle multiplication without a caller workspace and without any allocation.
+ * (No counterpart in the reference: it exists for callers of this library that must not allocate device
+ * memory -- a serving loop whose memory is fully handed to another framework's pool, a latency-critical
+ * thread where cudaMalloc's implicit device synchronisation is not acceptable, or an embedding host that
+ * simply has no allocator to lend a workspace from.)
+ *
+ * Same arguments and results as b200_trimul_fwd, minus the workspace: the scratch is a fixed array inside the
+ * library image, 48 MiB per GPU that loads the library, held until the process exits.  Limit: N <= 256;
+ * larger N is rejected with B200_ERR_INVALID_ARGUMENT.  The call makes no cudaMalloc/cudaFree and calls no
+ * allocating library routine.  The first call on each device resolves the array's device address
+ * (cudaGetSymbolAddress with that device current); make that first call outside any stream capture.
+ * All calls on a device share the one array: calls that may overlap on the GPU (different streams) race and
+ * must be serialised by the caller.  Nothing in the array needs to start at zero -- every element that is
+ * read has been written earlier in the same call -- so it is not cleared between calls.
+ * ------------------------------------------------------------------------------------------------- */
+int b200_trimul_fwd_static(const void* z, const uint8_t* mask, void* out, const b200_trimul_weights* w, int B, int N,
+                           int incoming, int add_residual, int z_dtype, b200_stream_t stream);
+
+/* ---------------------------------------------------------------------------------------------------
  * Pair transition, Transition.forward (src/bioemu2/biomoa/ops/transition.py:52-76) for dim 128, hidden 512:
  * out = fc3(silu(fc1(h)) * fc2(h)) [+ x], h = LayerNorm(x) when use_norm else x.
  *
