@@ -9,7 +9,8 @@ import os
 from ctypes import POINTER, Structure, c_char_p, c_float, c_int, c_int64, c_size_t, c_uint8, c_void_p
 
 HERE = os.path.dirname(os.path.abspath(__file__))
-LIB_PATH = os.path.join(HERE, "libb200pair.so")
+# BIOEMU2_B200_LIB points at an alternative build of the same library (profiling or experimental builds).
+LIB_PATH = os.environ.get("BIOEMU2_B200_LIB") or os.path.join(HERE, "libb200pair.so")
 
 OK = 0
 ERR_INVALID_ARGUMENT = 1
@@ -47,6 +48,18 @@ class TriAttWeights(Structure):
                 ("ln_b", c_void_p)]
 
 
+class AttentionCoreArgs(Structure):
+    _fields_ = [
+        ("qk", c_void_p), ("qk_width", c_int64), ("qk_batch_stride", c_int64), ("q_col0", c_int), ("k_col0", c_int),
+        ("vT", c_void_p), ("v_pitch", c_int64), ("bias", c_void_p), ("bias_pitch", c_int64), ("bias_groups", c_int),
+        ("bias_div", c_int), ("mask", c_void_p), ("mask_div", c_int), ("mask_row_stride", c_int64),
+        ("mask_key_stride", c_int64), ("gate", c_void_p), ("gate_batch_stride", c_int64), ("gate_pitch", c_int),
+        ("gate_col0", c_int), ("out", c_void_p), ("out_batch_stride", c_int64), ("out_pitch", c_int),
+        ("out_col0", c_int), ("head_dim_padded", c_int), ("head_dim_out", c_int), ("N", c_int), ("H", c_int),
+        ("batch", c_int),
+    ]
+
+
 # name -> (restype, argtypes); mirrors include/b200pair.h one to one
 SIGNATURES = {
     "b200_version": (c_int, []),
@@ -66,6 +79,7 @@ SIGNATURES = {
     "b200_opm_workspace_bytes": (c_size_t, [c_int, c_int]),
     "b200_opm_fwd": (c_int, [c_void_p, c_void_p, c_int, c_void_p, POINTER(OpmWeights), c_int, c_int, c_int, c_int,
                              c_int, c_void_p, c_size_t, c_void_p]),
+    "b200_attention_core_fwd": (c_int, [POINTER(AttentionCoreArgs), c_void_p]),
     "b200_apb_workspace_bytes": (c_size_t, [c_int, c_int, c_int, c_int, c_int]),
     "b200_apb_fwd": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, POINTER(ApbWeights), c_int, c_int, c_int, c_int,
                              c_int, c_int, c_int, c_void_p, c_size_t, c_void_p]),

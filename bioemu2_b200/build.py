@@ -24,7 +24,7 @@ NVCC_FLAGS = [
 def sources() -> list[str]:
     csrc = os.path.join(HERE, "csrc")
     inc = os.path.join(os.path.dirname(HERE), "include")
-    out = [os.path.join(csrc, f) for f in sorted(os.listdir(csrc)) if f.endswith((".cu", ".cuh"))]
+    out = [os.path.join(csrc, f) for f in sorted(os.listdir(csrc)) if f.endswith((".cu", ".cuh", ".inc"))]
     out += [os.path.join(inc, f) for f in sorted(os.listdir(inc)) if f.endswith(".h")]
     return out
 

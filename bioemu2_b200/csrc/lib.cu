@@ -12,6 +12,7 @@
 #include "elementwise.cuh"
 #include "opm.cuh"
 #include "attention.cuh"
+#include "pair_bias.cuh"
 #include "triatt.cuh"
 
 namespace b200 {
@@ -110,9 +111,9 @@ struct FlashLaunch {
   FlashParams p;
 };
 
-template <int DH>
+template <int DH, int G>
 static int launch_flash_t(const FlashLaunch& a, cudaStream_t stream) {
-  using Cfg = FlashCfg<DH>;
+  using Cfg = FlashCfg<DH, G>;
   const FlashParams& p0 = a.p;
   CUtensorMap tmQ, tmV, tmB;
   {
@@ -138,16 +139,19 @@ static int launch_flash_t(const FlashLaunch& a, cudaStream_t stream) {
   FlashParams p = p0;
   p.nqt = (p.N + 127) / 128;
   p.nkt = (p.N + 127) / 128;
-  p.total_work = p.Bt * p.H * p.nqt;
-  if (int e = set_smem(flash_core_kernel<DH>, Cfg::SMEM_BYTES)) return e;
+  if (p.nkt > Cfg::MAX_T)
+    return fail(B200_ERR_INVALID_ARGUMENT, "attention supports at most %d tokens (got %d)", Cfg::MAX_T * 128, p.N);
+  p.nqg = (p.nqt + G - 1) / G;
+  p.total_work = p.Bt * p.H * p.nqg;
+  if (int e = set_smem(flash_core_kernel<DH, G>, Cfg::SMEM_BYTES)) return e;
   const int grid = p.total_work < sm_count() ? p.total_work : sm_count();
-  flash_core_kernel<DH><<<grid, Cfg::THREADS, Cfg::SMEM_BYTES, stream>>>(tmQ, tmQ, tmV, tmB, p);
+  flash_core_kernel<DH, G><<<grid, Cfg::THREADS, Cfg::SMEM_BYTES, stream>>>(tmQ, tmQ, tmV, tmB, p);
   B200_CUDA(cudaGetLastError());
   return 0;
 }
 
 static int launch_flash(const FlashLaunch& a, int DH, cudaStream_t stream) {
-  return DH == 32 ? launch_flash_t<32>(a, stream) : launch_flash_t<64>(a, stream);
+  return DH == 32 ? launch_flash_t<32, 2>(a, stream) : launch_flash_t<64, 1>(a, stream);
 }
 
 static int launch_pair_bias(const void* z, bool f32, const float* ln_w, const float* ln_b, const void* w_z,
@@ -537,6 +541,55 @@ int b200_opm_fwd(const void* m, const uint8_t* mask, int mask_ndim, void* out, c
     }
   }
   return B200_OK;
+}
+
+// ------------------------------------------------------------------------------------------------ attention core
+int b200_attention_core_fwd(const b200_attention_core_args* a, b200_stream_t stream) {
+  if (int e = b200_check_device()) return e;
+  B200_CHECK_ARG(a != nullptr, "args is NULL");
+  B200_CHECK_ARG(a->qk && a->vT && a->bias && a->mask && a->out, "qk/vT/bias/mask/out is NULL");
+  B200_CHECK_ARG(a->head_dim_padded == 32 || a->head_dim_padded == 64, "head_dim_padded must be 32 or 64");
+  B200_CHECK_ARG(a->N > 0 && a->H > 0 && a->batch > 0, "N/H/batch must be positive");
+  B200_CHECK_ARG(a->head_dim_out > 0 && a->head_dim_out % 8 == 0 && a->head_dim_out <= a->head_dim_padded,
+                 "head_dim_out must be a multiple of 8 and <= head_dim_padded");
+  B200_CHECK_ARG(a->qk_width % 8 == 0 && a->v_pitch % 8 == 0 && a->bias_pitch % 8 == 0 && a->out_pitch % 8 == 0 &&
+                     a->q_col0 % 8 == 0 && a->k_col0 % 8 == 0 && a->out_col0 % 8 == 0 && a->gate_col0 % 8 == 0 &&
+                     a->gate_pitch % 8 == 0,
+                 "pitches and column offsets must be multiples of 8 elements");
+  B200_CHECK_ARG(a->bias_div > 0 && a->mask_div > 0 && a->bias_groups > 0, "bias_div/mask_div/bias_groups must be positive");
+  B200_CHECK_ARG(aligned(a->qk, 16) && aligned(a->vT, 16) && aligned(a->bias, 16) && aligned(a->out, 16) &&
+                     (!a->gate || aligned(a->gate, 16)), "operands must be 16-byte aligned");
+  FlashLaunch l;
+  l.qk = a->qk;
+  l.qk_width = a->qk_width;
+  l.qk_b_stride = a->qk_batch_stride;
+  l.vT = a->vT;
+  l.v_pitch = a->v_pitch;
+  l.bias = a->bias;
+  l.bias_pitch = a->bias_pitch;
+  l.bias_groups = a->bias_groups;
+  FlashParams& p = l.p;
+  p.mask = a->mask;
+  p.mask_div = a->mask_div;
+  p.mask_row_stride = a->mask_row_stride;
+  p.mask_key_stride = a->mask_key_stride;
+  p.bias_div = a->bias_div;
+  p.gate = static_cast<const __nv_bfloat16*>(a->gate);
+  p.gate_b_stride = a->gate_batch_stride;
+  p.gate_pitch = a->gate_pitch;
+  p.gate_col0 = a->gate_col0;
+  p.out = static_cast<__nv_bfloat16*>(a->out);
+  p.out_b_stride = a->out_batch_stride;
+  p.out_pitch = a->out_pitch;
+  p.out_col0 = a->out_col0;
+  p.dh_out = a->head_dim_out;
+  p.N = a->N;
+  p.H = a->H;
+  p.Bt = a->batch;
+  p.q_col0 = a->q_col0;
+  p.k_col0 = a->k_col0;
+  p.v_row0 = 0;
+  return launch_flash(l, a->head_dim_padded, static_cast<cudaStream_t>(stream));
 }
 
 // ------------------------------------------------------------------------------------------------ APB

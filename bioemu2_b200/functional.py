@@ -412,3 +412,36 @@ def transition_generic(x: Tensor, w: TransitionGenericPacked, add_residual: bool
     if add_residual and not same_width:
         raise ValueError("the residual needs out_dim == dim")
     return linear_bf16(h, w.w3, residual=x if add_residual else None, out_dtype=x.dtype, out=out)
+
+
+def attention_core(q: Tensor, k: Tensor, v: Tensor, bias: Tensor, key_mask: Tensor, gate: Tensor | None = None,
+                   bias_div: int = 1, mask_div: int = 1) -> Tensor:
+    """softmax(q.k/sqrt(dh) + bias, masked keys -> -1e6) v [* sigmoid(gate)] on the tcgen05 flash kernel.
+
+    ``q, k, v, gate``: ``[batch, N, H, dh]`` (dh a multiple of 8, <= 64); ``bias``: ``[groups, H, N, N]`` (natural-log
+    units); ``key_mask``: ``[batch // mask_div, N]``.  Returns bf16 ``[batch, N, H, dh]``.  The operand re-layout
+    (head padding, scaling, V transposition) done here with torch ops is what the fused projection kernels of
+    ``attention_pair_bias`` / ``triangle_attention`` produce directly; this entry serves tests and benchmarks.
+    """
+    _require_cuda(q, k, v, bias, key_mask)
+    Bt, N, H, dh = q.shape
+    DH = 32 if dh <= 32 else 64
+    bf = torch.bfloat16
+    qk = torch.zeros(Bt, N, 2 * H * DH, dtype=bf, device=q.device)
+    qk.view(Bt, N, 2, H, DH)[:, :, 0, :, :dh] = (q.float() * (LOG2E / dh ** 0.5)).to(bf)
+    qk.view(Bt, N, 2, H, DH)[:, :, 1, :, :dh] = k.to(bf)
+    Nk = (N + 7) // 8 * 8
+    vT = torch.zeros(Bt, H * DH, Nk, dtype=bf, device=q.device)
+    vT.view(Bt, H, DH, Nk)[:, :, :dh, :N] = v.to(bf).permute(0, 2, 3, 1)
+    groups = bias.shape[0]
+    b2 = torch.zeros(groups * H, N, Nk, dtype=bf, device=q.device)
+    b2[:, :, :N] = (bias.float() * LOG2E).to(bf).reshape(groups * H, N, N)
+    out = torch.empty(Bt, N, H * dh, dtype=bf, device=q.device)
+    g = gate.to(bf).reshape(Bt, N, H * dh).contiguous() if gate is not None else None
+    m8 = mask_u8(key_mask)
+    a = _lib.AttentionCoreArgs(
+        qk.data_ptr(), 2 * H * DH, N * 2 * H * DH, 0, H * DH, vT.data_ptr(), Nk, b2.data_ptr(), Nk, groups, bias_div,
+        m8.data_ptr(), mask_div, N, 1, _ptr(g), N * H * dh, H * dh, 0, out.data_ptr(), N * H * dh, H * dh, 0, DH, dh,
+        N, H, Bt)
+    _lib.check(lib.b200_attention_core_fwd(ctypes.byref(a), _stream()))
+    return out.view(Bt, N, H, dh)

@@ -169,6 +169,46 @@ int b200_opm_fwd(const void* m, const uint8_t* mask, int mask_ndim, void* out, c
                  b200_stream_t stream);
 
 /* ---------------------------------------------------------------------------------------------------
+ * Attention core on already projected operands: the fp32 softmax(q.k + bias, key mask) v section of
+ * AttentionPairBias.forward (src/bioemu2/biomoa/ops/attention_pair_bias.py:165-222) and the core of the
+ * context-parallel flash kernel (src/bioemu2/context_parallel/ops/triton/flash_attn_impl.py:9-228).
+ * b200_apb_fwd and b200_triatt_fwd call it internally; it is exported for hosts that do their own projections.
+ *
+ *   out[b, q, h*dh_out + d] = sigmoid(gate[...]) * sum_k softmax_k(Q[b,q,h,:].K[b,k,h,:] + bias[b/bias_div, h, q, k]) V[b,k,h,d]
+ *
+ * All operands bf16.  Q and K live in one row-major buffer qk[batch][N][qk_width]: head h of Q at columns
+ * q_col0 + h*DH, of K at k_col0 + h*DH (DH = head_dim_padded, 32 or 64; pad columns zero).  Q and bias must be
+ * pre-multiplied by log2(e) (Q also by 1/sqrt(head dim)).  vT[batch][H*DH][v_pitch] is V transposed (keys
+ * contiguous).  bias[bias_groups*H][N][bias_pitch].  mask: one byte per key at
+ * mask[(b / mask_div) * mask_row_stride + k * mask_key_stride]; masked keys get the finite logit -1e6.
+ * gate (raw logits, may be NULL) and out are addressed as base + b*batch_stride + q*pitch + col0 + h*dh_out + d.
+ * N <= 8192.
+ * ------------------------------------------------------------------------------------------------- */
+typedef struct {
+  const void* qk;
+  int64_t qk_width, qk_batch_stride;
+  int q_col0, k_col0;
+  const void* vT;
+  int64_t v_pitch;
+  const void* bias;
+  int64_t bias_pitch;
+  int bias_groups, bias_div;
+  const uint8_t* mask;
+  int mask_div;
+  int64_t mask_row_stride, mask_key_stride;
+  const void* gate;
+  int64_t gate_batch_stride;
+  int gate_pitch, gate_col0;
+  void* out;
+  int64_t out_batch_stride;
+  int out_pitch, out_col0;
+  int head_dim_padded, head_dim_out;
+  int N, H, batch;
+} b200_attention_core_args;
+
+int b200_attention_core_fwd(const b200_attention_core_args* args, b200_stream_t stream);
+
+/* ---------------------------------------------------------------------------------------------------
  * Single-track attention with pair bias, AttentionPairBias.forward
  * (src/bioemu2/biomoa/ops/attention_pair_bias.py:128-225):
  *   s' = LN(s) (if initial_norm);  q = Wq s' + b_q, k, v;  g = sigmoid(Wg s');  bias = proj_z(LN_z(z));

@@ -81,3 +81,24 @@ def test_apb_fully_masked_and_padding():
     with torch.no_grad():
         out_p = mod(sp.cuda(), zp.cuda(), mp.cuda())
     torch.testing.assert_close(out_p[0, :N], out[0], atol=2e-3, rtol=0)
+
+
+@pytest.mark.parametrize("Bt,N,H,dh", [(3, 200, 4, 32), (2, 130, 2, 48), (1, 512, 4, 32)])
+def test_attention_core_entry_point(Bt, N, H, dh):
+    """The exported flash core against a plain fp64 softmax on the same (bf16-rounded) operands."""
+    import math
+
+    from bioemu2_b200 import functional as F
+
+    g = torch.Generator(device="cuda").manual_seed(Bt * 100 + N)
+    q = torch.randn(Bt, N, H, dh, device="cuda", generator=g).bfloat16()
+    k = torch.randn(Bt, N, H, dh, device="cuda", generator=g).bfloat16()
+    v = torch.randn(Bt, N, H, dh, device="cuda", generator=g).bfloat16()
+    gate = torch.randn(Bt, N, H, dh, device="cuda", generator=g).bfloat16()
+    bias = torch.randn(1, H, N, N, device="cuda", generator=g).bfloat16()
+    mask = torch.rand(Bt, N, device="cuda", generator=g) > 0.2
+    out = F.attention_core(q, k, v, bias, mask, gate, bias_div=Bt)
+    logits = torch.einsum("bihd,bjhd->bhij", q.double(), k.double()) / math.sqrt(dh) + bias.double()
+    logits = torch.where(mask[:, None, None, :], logits, torch.full_like(logits, -1e6))
+    ref = torch.einsum("bhij,bjhd->bihd", logits.softmax(-1), v.double()) * torch.sigmoid(gate.double())
+    assert_close(f"attention_core_B{Bt}_N{N}_H{H}_dh{dh}", out, ref)
