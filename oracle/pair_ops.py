@@ -149,7 +149,8 @@ def pairmixer_module(z: Tensor, pair_mask: Tensor, w: dict, num_blocks: int) -> 
     return z
 
 
-def triangle_attention(x: Tensor, mask: Tensor, w: dict, num_heads: int, ending: bool, inf: float = 1e6) -> Tensor:
+def triangle_attention(x: Tensor, mask: Tensor, w: dict, num_heads: int, ending: bool, inf: float = 1e6,
+                       row_chunk: int | None = None) -> Tensor:
     """Triangle self-attention around the starting (or ending) node.
 
     NOT IN THE REFERENCE -- parity unpinned.  The reference removed this op
@@ -176,19 +177,26 @@ def triangle_attention(x: Tensor, mask: Tensor, w: dict, num_heads: int, ending:
     v = linear(h, w["linear_v.weight"]).view(B, N, N, H, dh)
     tri_bias = linear(h, w["linear_b.weight"]).permute(0, 3, 1, 2)  # [B,H,j,k]
     g = torch.sigmoid(linear(h, w["linear_g.weight"], w["linear_g.bias"]))
-    logits = torch.einsum("bijhd,bikhd->bihjk", q, k) / math.sqrt(dh)
-    logits = logits + tri_bias.unsqueeze(1)
-    key_mask = mask.bool().view(B, N, 1, 1, N)
-    logits = torch.where(key_mask, logits, torch.full_like(logits, -inf))
-    p = logits.softmax(dim=-1)
-    o = torch.einsum("bihjk,bikhd->bijhd", p, v).reshape(B, N, N, H * dh)
+    # rows i are independent; row_chunk only bounds the size of the [B, rows, H, N, N] logits tensor
+    step = N if row_chunk is None else row_chunk
+    o_rows = []
+    for i0 in range(0, N, step):
+        sl = slice(i0, min(i0 + step, N))
+        logits = torch.einsum("bijhd,bikhd->bihjk", q[:, sl], k[:, sl]) / math.sqrt(dh)
+        logits = logits + tri_bias.unsqueeze(1)
+        key_mask = mask[:, sl].bool().view(B, -1, 1, 1, N)
+        logits = torch.where(key_mask, logits, torch.full_like(logits, -inf))
+        p = logits.softmax(dim=-1)
+        o_rows.append(torch.einsum("bihjk,bikhd->bijhd", p, v[:, sl]))
+    o = torch.cat(o_rows, dim=1).reshape(B, N, N, H * dh)
     out = linear(g * o, w["linear_o.weight"])
     if ending:
         out = out.transpose(1, 2)
     return out
 
 
-def pairformer_block(s: Tensor, z: Tensor, token_mask: Tensor, w: dict, *, tri_heads: int = 4, apb_heads: int = 16):
+def pairformer_block(s: Tensor, z: Tensor, token_mask: Tensor, w: dict, *, tri_heads: int = 4, apb_heads: int = 16,
+                     row_chunk: int | None = None):
     """The composite block the benchmark configs describe.
 
     Pair track: triangle multiplication out/in, triangle attention start/end,
@@ -201,8 +209,8 @@ def pairformer_block(s: Tensor, z: Tensor, token_mask: Tensor, w: dict, *, tri_h
     pair_mask = token_mask[:, :, None] & token_mask[:, None, :]
     z = z + triangle_multiplication(z, pair_mask, _sub(w, "tri_mul_out"), "outgoing")
     z = z + triangle_multiplication(z, pair_mask, _sub(w, "tri_mul_in"), "incoming")
-    z = z + triangle_attention(z, pair_mask, _sub(w, "tri_att_start"), tri_heads, ending=False)
-    z = z + triangle_attention(z, pair_mask, _sub(w, "tri_att_end"), tri_heads, ending=True)
+    z = z + triangle_attention(z, pair_mask, _sub(w, "tri_att_start"), tri_heads, ending=False, row_chunk=row_chunk)
+    z = z + triangle_attention(z, pair_mask, _sub(w, "tri_att_end"), tri_heads, ending=True, row_chunk=row_chunk)
     z = z + transition(z, _sub(w, "transition_z"))
     s = s + attention_pair_bias(s, z, token_mask, _sub(w, "attention"), apb_heads)
     s = s + transition(s, _sub(w, "transition_s"))
