@@ -72,6 +72,12 @@ SIGNATURES = {
     "b200_trimul_workspace_bytes": (c_size_t, [c_int]),
     "b200_trimul_fwd": (c_int, [c_void_p, c_void_p, c_void_p, POINTER(TriMulWeights), c_int, c_int, c_int, c_int,
                                 c_int, c_void_p, c_size_t, c_void_p]),
+    "b200_trimul_project": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, POINTER(TriMulWeights), c_int, c_int, c_int64,
+                                    c_int64, c_int, c_int, c_int, c_void_p]),
+    "b200_trimul_output": (c_int, [c_void_p, c_void_p, c_void_p, POINTER(TriMulWeights), c_int, c_int, c_int64, c_int,
+                                   c_int, c_int, c_int, c_void_p]),
+    "b200_bmm_nt": (c_int, [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int64, c_int64, c_int64, c_int64,
+                            c_int64, c_int64, c_float, c_int, c_void_p]),
     "b200_trimul_fwd_static": (c_int, [c_void_p, c_void_p, c_void_p, POINTER(TriMulWeights), c_int, c_int, c_int,
                                        c_int, c_int, c_void_p]),
     "b200_transition_fwd": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_int,

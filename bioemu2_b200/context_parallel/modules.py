@@ -1,0 +1,98 @@
+"""Context-parallel wrappers with the call pattern of the reference's distributed modules.
+
+Reference: ``TriangleMultiplicationAddRes`` (src/bioemu2/context_parallel/ops/triangle_multiplication.py:45-182,
+``forward(x, mask) -> x``, in place, returns the same object), ``DTensorAwareTransition``
+(ops/transition.py:16-64, communication-free, returns the update), ``DistributedPairMixerLayer/Module``
+(modules/pairmixer.py:77-115).  Each wrapper adopts an already loaded serial module, as the reference's do.
+
+Arguments may be plain local blocks ``[B, n_r, n_c, ...]`` or ``DTensor``s with the reference's pair placements
+``(Shard(0), Shard(1), Shard(2))`` over ``(dp, cp_axis_0, cp_axis_1)``; a DTensor is updated through its local shard
+and handed back as the same object.
+"""
+from __future__ import annotations
+
+import torch
+import torch.nn as nn
+from torch import Tensor
+
+from ..transition import Transition
+from ..triangle_multiplication import TriangleMultiplication
+from .mesh import CPGrid
+from .trimul import cp_triangle_multiplication_
+
+
+def _local(x):
+    return x.to_local() if hasattr(x, "to_local") else x
+
+
+class CPTriangleMultiplication(nn.Module):
+    """``forward(x, mask)``: ``x += TriMul(x)`` on the sharded pair tensor, in place; returns ``x`` itself."""
+
+    def __init__(self, layer: TriangleMultiplication, grid: CPGrid, backend=None) -> None:
+        super().__init__()
+        self.layer = layer
+        self.grid = grid
+        self.backend = backend
+
+    def forward(self, x, mask):
+        xl, ml = _local(x), _local(mask)
+        if xl.ndim != 4 or ml.ndim != 3 or xl.shape[:3] != ml.shape:
+            raise ValueError(f"expected x[B,n_r,n_c,D] and mask[B,n_r,n_c], got {tuple(xl.shape)}, {tuple(ml.shape)}")
+        if not xl.is_contiguous():
+            raise ValueError("the local block must be contiguous (it is updated in place)")
+        n_tokens = xl.shape[1] * self.grid.rows
+        if xl.shape[2] * self.grid.cols != n_tokens:
+            raise ValueError(f"block {xl.shape[1]}x{xl.shape[2]} is not one cell of a {self.grid.rows}x{self.grid.cols} "
+                             "grid over a square pair tensor: pad the token axis to shard_multiple(R, C) first")
+        packed = self.layer.packed()
+        for b in range(xl.shape[0]):
+            cp_triangle_multiplication_(xl[b], ml[b], packed, self.grid, self.layer.mode == "incoming", n_tokens,
+                                        backend=self.backend)
+        return x
+
+
+class CPTransition(nn.Module):
+    """Per-position transition on the local block: no communication (reference ops/transition.py:28-64)."""
+
+    def __init__(self, serial: Transition, grid: CPGrid | None = None) -> None:
+        super().__init__()
+        self.serial = serial
+
+    def forward(self, x):
+        out = self.serial(_local(x))
+        if hasattr(x, "to_local"):
+            from torch.distributed.tensor import DTensor
+
+            return DTensor.from_local(out, x.device_mesh, x.placements, run_check=False)
+        return out
+
+    def forward_residual_(self, x):
+        self.serial.forward_residual_(_local(x))
+        return x
+
+
+class CPPairMixerLayer(nn.Module):
+    """``z -> z`` after triangle multiplication out / in and the pair transition, all in place on the local block."""
+
+    def __init__(self, serial, grid: CPGrid, backend=None) -> None:
+        super().__init__()
+        self.tri_mul_out = CPTriangleMultiplication(serial.tri_mul_out, grid, backend)
+        self.tri_mul_in = CPTriangleMultiplication(serial.tri_mul_in, grid, backend)
+        self.transition_z = CPTransition(serial.transition_z, grid)
+
+    def forward(self, z, pair_mask):
+        self.tri_mul_out(z, pair_mask)
+        self.tri_mul_in(z, pair_mask)
+        return self.transition_z.forward_residual_(z)
+
+
+class CPPairMixerModule(nn.Module):
+    def __init__(self, serial, grid: CPGrid, backend=None) -> None:
+        super().__init__()
+        self.layers = nn.ModuleList(CPPairMixerLayer(layer, grid, backend) for layer in serial.layers)
+
+    def forward(self, z, pair_mask):
+        with torch.no_grad():
+            for layer in self.layers:
+                z = layer(z, pair_mask)
+        return z

@@ -264,18 +264,104 @@ size_t b200_trimul_workspace_bytes(int N) {
   return 3 * size_t(kD) * Np * Np * sizeof(__nv_bfloat16);  // a, b, t
 }
 
+// Slab geometry of the two pair-walking kernels of triangle multiplication.
+struct TriMulGeom {
+  int n_lines, n_pos, lines_alloc, pos_pitch;
+  long long z_line_stride, z_pos_stride;  // bytes
+  long long m_line_stride, m_pos_stride;  // bytes
+};
+
+static int launch_trimul_project(const void* z, const uint8_t* mask, __nv_bfloat16* a_buf, __nv_bfloat16* b_buf,
+                                 const b200_trimul_weights* w, const TriMulGeom& g, bool f32, cudaStream_t stream) {
+  CUtensorMap tmWin;
+  const uint64_t dims[2] = {128, 512};
+  const uint64_t str[1] = {256};
+  const uint32_t box[2] = {64, 128};
+  if (int e = make_tmap_bf16(&tmWin, w->w_in, 2, dims, str, box, CU_TENSOR_MAP_SWIZZLE_128B)) return e;
+  if (int e = set_smem(trimul_in_kernel<true>, trimul_in::SMEM_BYTES)) return e;
+  if (int e = set_smem(trimul_in_kernel<false>, trimul_in::SMEM_BYTES)) return e;
+  TriMulInParams pi;
+  pi.z = z;
+  pi.mask = mask;
+  pi.ln_w = w->ln_in_w;
+  pi.ln_b = w->ln_in_b;
+  pi.a_out = a_buf;
+  pi.b_out = b_buf;
+  pi.n_lines = g.n_lines;
+  pi.n_pos = g.n_pos;
+  pi.lines_alloc = g.lines_alloc;
+  pi.pos_pitch = g.pos_pitch;
+  pi.z_line_stride = g.z_line_stride;
+  pi.z_pos_stride = g.z_pos_stride;
+  pi.m_line_stride = g.m_line_stride;
+  pi.m_pos_stride = g.m_pos_stride;
+  pi.num_tiles = g.n_lines * (g.pos_pitch / 128);
+  pi.eps = 1e-5f;
+  const int grid = pi.num_tiles < sm_count() ? pi.num_tiles : sm_count();
+  if (f32)
+    trimul_in_kernel<true><<<grid, trimul_in::THREADS, trimul_in::SMEM_BYTES, stream>>>(tmWin, pi);
+  else
+    trimul_in_kernel<false><<<grid, trimul_in::THREADS, trimul_in::SMEM_BYTES, stream>>>(tmWin, pi);
+  B200_CUDA(cudaGetLastError());
+  return 0;
+}
+
+static int launch_trimul_output(const void* z, void* out, const __nv_bfloat16* t_buf, const b200_trimul_weights* w,
+                                const TriMulGeom& g, bool add_residual, bool f32, cudaStream_t stream) {
+  CUtensorMap tmWout, tmT;
+  {
+    const uint64_t dims[2] = {128, 256};
+    const uint64_t str[1] = {256};
+    const uint32_t box[2] = {64, 128};
+    if (int e = make_tmap_bf16(&tmWout, w->w_out, 2, dims, str, box, CU_TENSOR_MAP_SWIZZLE_128B)) return e;
+  }
+  {
+    const uint64_t dims[3] = {uint64_t(g.pos_pitch), uint64_t(g.lines_alloc), uint64_t(kD)};
+    const uint64_t str[2] = {uint64_t(g.pos_pitch) * 2, uint64_t(g.pos_pitch) * g.lines_alloc * 2};
+    const uint32_t box[3] = {128, 1, 128};
+    if (int e = make_tmap_bf16(&tmT, t_buf, 3, dims, str, box, CU_TENSOR_MAP_SWIZZLE_NONE)) return e;
+  }
+  if (int e = set_smem(trimul_out_kernel<true>, trimul_out::SMEM_BYTES)) return e;
+  if (int e = set_smem(trimul_out_kernel<false>, trimul_out::SMEM_BYTES)) return e;
+  TriMulOutParams po;
+  po.z = z;
+  po.out = out;
+  po.ln_in_w = w->ln_in_w;
+  po.ln_in_b = w->ln_in_b;
+  po.ln_out_w = w->ln_out_w;
+  po.ln_out_b = w->ln_out_b;
+  po.n_lines = g.n_lines;
+  po.n_pos = g.n_pos;
+  po.pos_pitch = g.pos_pitch;
+  po.z_line_stride = g.z_line_stride;
+  po.z_pos_stride = g.z_pos_stride;
+  po.num_tiles = g.n_lines * (g.pos_pitch / 128);
+  po.add_residual = add_residual ? 1 : 0;
+  po.eps = 1e-5f;
+  const int grid = po.num_tiles < sm_count() ? po.num_tiles : sm_count();
+  if (f32)
+    trimul_out_kernel<true><<<grid, trimul_out::THREADS, trimul_out::SMEM_BYTES, stream>>>(tmWout, tmT, po);
+  else
+    trimul_out_kernel<false><<<grid, trimul_out::THREADS, trimul_out::SMEM_BYTES, stream>>>(tmWout, tmT, po);
+  B200_CUDA(cudaGetLastError());
+  return 0;
+}
+
+static bool trimul_weights_ok(const b200_trimul_weights* w) {
+  return w && w->w_in && w->w_out && w->ln_in_w && w->ln_in_b && w->ln_out_w && w->ln_out_b && aligned(w->w_in, 16) &&
+         aligned(w->w_out, 16);
+}
+
 int b200_trimul_fwd(const void* z, const uint8_t* mask, void* out, const b200_trimul_weights* w, int B, int N,
                     int incoming, int add_residual, int z_dtype, void* workspace, size_t workspace_bytes,
                     b200_stream_t stream_) {
   if (int e = b200_check_device()) return e;
   cudaStream_t stream = static_cast<cudaStream_t>(stream_);
   B200_CHECK_ARG(z && mask && out && w, "z/mask/out/w is NULL");
-  B200_CHECK_ARG(w->w_in && w->w_out && w->ln_in_w && w->ln_in_b && w->ln_out_w && w->ln_out_b,
-                 "a weight pointer is NULL");
+  B200_CHECK_ARG(trimul_weights_ok(w), "a weight pointer is NULL or not 16-byte aligned");
   B200_CHECK_ARG(B > 0 && N > 0, "B=%d, N=%d must be positive", B, N);
   B200_CHECK_ARG(z_dtype == B200_DTYPE_BF16 || z_dtype == B200_DTYPE_F32, "unknown z_dtype %d", z_dtype);
-  B200_CHECK_ARG(aligned(z, 32) && aligned(out, 32) && aligned(w->w_in, 16) && aligned(w->w_out, 16),
-                 "z/out must be 32-byte aligned, weights 16-byte aligned");
+  B200_CHECK_ARG(aligned(z, 32) && aligned(out, 32), "z/out must be 32-byte aligned");
   const bool f32 = z_dtype == B200_DTYPE_F32;
   const size_t esz = f32 ? 4 : 2;
   const size_t need = b200_trimul_workspace_bytes(N);
@@ -287,79 +373,87 @@ int b200_trimul_fwd(const void* z, const uint8_t* mask, void* out, const b200_tr
   __nv_bfloat16* a_buf = static_cast<__nv_bfloat16*>(workspace);
   __nv_bfloat16* b_buf = a_buf + plane;
   __nv_bfloat16* t_buf = b_buf + plane;
-
-  CUtensorMap tmWin, tmWout, tmT;
-  {
-    const uint64_t dims[2] = {128, 512};
-    const uint64_t str[1] = {256};
-    const uint32_t box[2] = {64, 128};
-    if (int e = make_tmap_bf16(&tmWin, w->w_in, 2, dims, str, box, CU_TENSOR_MAP_SWIZZLE_128B)) return e;
-  }
-  {
-    const uint64_t dims[2] = {128, 256};
-    const uint64_t str[1] = {256};
-    const uint32_t box[2] = {64, 128};
-    if (int e = make_tmap_bf16(&tmWout, w->w_out, 2, dims, str, box, CU_TENSOR_MAP_SWIZZLE_128B)) return e;
-  }
-  {
-    const uint64_t dims[3] = {uint64_t(Np), uint64_t(Np), uint64_t(kD)};
-    const uint64_t str[2] = {uint64_t(Np) * 2, uint64_t(Np) * Np * 2};
-    const uint32_t box[3] = {128, 1, 128};
-    if (int e = make_tmap_bf16(&tmT, t_buf, 3, dims, str, box, CU_TENSOR_MAP_SWIZZLE_NONE)) return e;
-  }
-  if (int e = set_smem(trimul_in_kernel<true>, trimul_in::SMEM_BYTES)) return e;
-  if (int e = set_smem(trimul_in_kernel<false>, trimul_in::SMEM_BYTES)) return e;
-  if (int e = set_smem(trimul_out_kernel<true>, trimul_out::SMEM_BYTES)) return e;
-  if (int e = set_smem(trimul_out_kernel<false>, trimul_out::SMEM_BYTES)) return e;
-
-  const int num_tiles = N * (Np / 128);
-  const int grid = num_tiles < sm_count() ? num_tiles : sm_count();
+  const long long row_b = (long long)N * kD * esz, col_b = (long long)kD * esz;
+  // projection walks rows (outgoing) or columns (incoming); the output stage always walks rows
+  TriMulGeom gin{N, N, Np, Np, incoming ? col_b : row_b, incoming ? row_b : col_b, incoming ? 1 : N, incoming ? N : 1};
+  TriMulGeom gout{N, N, Np, Np, row_b, col_b, 0, 0};
   for (int bi = 0; bi < B; ++bi) {
     const uint8_t* zb = static_cast<const uint8_t*>(z) + size_t(bi) * N * N * kD * esz;
     uint8_t* ob = static_cast<uint8_t*>(out) + size_t(bi) * N * N * kD * esz;
-    TriMulInParams pi;
-    pi.z = zb;
-    pi.mask = mask + size_t(bi) * N * N;
-    pi.ln_w = w->ln_in_w;
-    pi.ln_b = w->ln_in_b;
-    pi.a_out = a_buf;
-    pi.b_out = b_buf;
-    pi.N = N;
-    pi.Np = Np;
-    pi.incoming = incoming ? 1 : 0;
-    pi.num_tiles = num_tiles;
-    pi.eps = 1e-5f;
-    if (f32)
-      trimul_in_kernel<true><<<grid, trimul_in::THREADS, trimul_in::SMEM_BYTES, stream>>>(tmWin, pi);
-    else
-      trimul_in_kernel<false><<<grid, trimul_in::THREADS, trimul_in::SMEM_BYTES, stream>>>(tmWin, pi);
-    B200_CUDA(cudaGetLastError());
-
+    if (int e = launch_trimul_project(zb, mask + size_t(bi) * N * N, a_buf, b_buf, w, gin, f32, stream)) return e;
     {
       const int64_t plane_el = int64_t(Np) * Np;
       BmmLaunch a{a_buf, b_buf, t_buf, kD, Np, Np, Np, Np, Np, Np, plane_el, plane_el, plane_el};
       if (int e = launch_bmm(a, stream)) return e;
     }
-
-    TriMulOutParams po;
-    po.z = zb;
-    po.out = ob;
-    po.ln_in_w = w->ln_in_w;
-    po.ln_in_b = w->ln_in_b;
-    po.ln_out_w = w->ln_out_w;
-    po.ln_out_b = w->ln_out_b;
-    po.N = N;
-    po.Np = Np;
-    po.num_tiles = num_tiles;
-    po.add_residual = add_residual ? 1 : 0;
-    po.eps = 1e-5f;
-    if (f32)
-      trimul_out_kernel<true><<<grid, trimul_out::THREADS, trimul_out::SMEM_BYTES, stream>>>(tmWout, tmT, po);
-    else
-      trimul_out_kernel<false><<<grid, trimul_out::THREADS, trimul_out::SMEM_BYTES, stream>>>(tmWout, tmT, po);
-    B200_CUDA(cudaGetLastError());
+    if (int e = launch_trimul_output(zb, ob, t_buf, w, gout, add_residual != 0, f32, stream)) return e;
   }
   return B200_OK;
+}
+
+// Staged form for sharded callers: the projection and output stages on a rectangular slab, the contraction
+// (b200_bmm_nt) and whatever exchange the caller needs in between.
+int b200_trimul_project(const void* z, const uint8_t* mask, void* a_out, void* b_out, const b200_trimul_weights* w,
+                        int n_rows, int n_cols, int64_t z_row_stride, int64_t mask_row_stride, int incoming,
+                        int pos_pitch, int z_dtype, b200_stream_t stream) {
+  if (int e = b200_check_device()) return e;
+  B200_CHECK_ARG(z && mask && a_out && b_out, "z/mask/a_out/b_out is NULL");
+  B200_CHECK_ARG(trimul_weights_ok(w), "a weight pointer is NULL or not 16-byte aligned");
+  B200_CHECK_ARG(n_rows > 0 && n_cols > 0, "n_rows=%d, n_cols=%d must be positive", n_rows, n_cols);
+  B200_CHECK_ARG((z_dtype | 1) == 1, "unknown z_dtype %d", z_dtype);
+  const int n_pos = incoming ? n_rows : n_cols, n_lines = incoming ? n_cols : n_rows;
+  B200_CHECK_ARG(pos_pitch % 128 == 0 && pos_pitch >= n_pos, "pos_pitch=%d must be a multiple of 128 and >= %d", pos_pitch,
+                 n_pos);
+  B200_CHECK_ARG(z_row_stride >= int64_t(n_cols) * kD && z_row_stride % 8 == 0 && mask_row_stride >= n_cols,
+                 "row strides smaller than a row");
+  B200_CHECK_ARG(aligned(z, 32) && aligned(a_out, 16) && aligned(b_out, 16), "z must be 32-byte aligned, a/b 16-byte");
+  const bool f32 = z_dtype == B200_DTYPE_F32;
+  const long long esz = f32 ? 4 : 2;
+  const long long row_b = z_row_stride * esz, col_b = kD * esz;
+  TriMulGeom g{n_lines, n_pos, n_lines, pos_pitch, incoming ? col_b : row_b, incoming ? row_b : col_b,
+               incoming ? 1 : mask_row_stride, incoming ? mask_row_stride : 1};
+  return launch_trimul_project(z, mask, static_cast<__nv_bfloat16*>(a_out), static_cast<__nv_bfloat16*>(b_out), w, g, f32,
+                               static_cast<cudaStream_t>(stream));
+}
+
+int b200_trimul_output(const void* t, const void* z, void* out, const b200_trimul_weights* w, int n_rows, int n_cols,
+                       int64_t z_row_stride, int transposed_t, int pos_pitch, int add_residual, int z_dtype,
+                       b200_stream_t stream) {
+  if (int e = b200_check_device()) return e;
+  B200_CHECK_ARG(t && z && out, "t/z/out is NULL");
+  B200_CHECK_ARG(trimul_weights_ok(w), "a weight pointer is NULL or not 16-byte aligned");
+  B200_CHECK_ARG(n_rows > 0 && n_cols > 0, "n_rows=%d, n_cols=%d must be positive", n_rows, n_cols);
+  B200_CHECK_ARG((z_dtype | 1) == 1, "unknown z_dtype %d", z_dtype);
+  const int n_pos = transposed_t ? n_rows : n_cols, n_lines = transposed_t ? n_cols : n_rows;
+  B200_CHECK_ARG(pos_pitch % 128 == 0 && pos_pitch >= n_pos, "pos_pitch=%d must be a multiple of 128 and >= %d", pos_pitch,
+                 n_pos);
+  B200_CHECK_ARG(z_row_stride >= int64_t(n_cols) * kD && z_row_stride % 8 == 0, "row stride smaller than a row");
+  B200_CHECK_ARG(aligned(z, 32) && aligned(out, 32) && aligned(t, 16), "z/out must be 32-byte aligned, t 16-byte");
+  const bool f32 = z_dtype == B200_DTYPE_F32;
+  const long long esz = f32 ? 4 : 2;
+  const long long row_b = z_row_stride * esz, col_b = kD * esz;
+  TriMulGeom g{n_lines, n_pos, n_lines, pos_pitch, transposed_t ? col_b : row_b, transposed_t ? row_b : col_b, 0, 0};
+  return launch_trimul_output(z, out, static_cast<const __nv_bfloat16*>(t), w, g, add_residual != 0, f32,
+                              static_cast<cudaStream_t>(stream));
+}
+
+int b200_bmm_nt(const void* A, const void* B, void* C, int batch, int M, int N, int K, int64_t lda, int64_t ldb,
+                int64_t ldc, int64_t a_batch_stride, int64_t b_batch_stride, int64_t c_batch_stride, float scale,
+                int out_dtype, b200_stream_t stream) {
+  if (int e = b200_check_device()) return e;
+  B200_CHECK_ARG(A && B && C, "A/B/C is NULL");
+  B200_CHECK_ARG(batch > 0 && M > 0 && N > 0 && K > 0, "batch/M/N/K must be positive");
+  B200_CHECK_ARG(N % 8 == 0 && lda % 8 == 0 && ldb % 8 == 0 && ldc % 8 == 0, "N and the row pitches must be multiples of 8");
+  B200_CHECK_ARG(a_batch_stride % 8 == 0 && b_batch_stride % 8 == 0 && c_batch_stride % 8 == 0,
+                 "batch strides must be multiples of 8 elements");
+  B200_CHECK_ARG(batch == 1 || (a_batch_stride > 0 && b_batch_stride > 0), "batch strides must be positive");
+  B200_CHECK_ARG(lda >= K && ldb >= K && ldc >= N, "row pitch smaller than the row");
+  B200_CHECK_ARG((out_dtype | 1) == 1, "unknown out_dtype %d", out_dtype);
+  B200_CHECK_ARG(aligned(A, 16) && aligned(B, 16) && aligned(C, 32), "A/B must be 16-byte aligned, C 32-byte aligned");
+  BmmLaunch a{A, B, C, batch, M, N, K, lda, ldb, ldc, a_batch_stride, b_batch_stride, c_batch_stride};
+  a.scale = scale;
+  a.out_f32 = out_dtype == B200_DTYPE_F32;
+  return launch_bmm(a, static_cast<cudaStream_t>(stream));
 }
 
 int b200_transition_fwd(const void* x, void* out, const void* w13, const void* w3, const float* ln_w,

@@ -16,16 +16,22 @@
 
 namespace b200 {
 
+// Geometry is given as lines x positions over a (possibly rectangular, possibly strided) slab of the pair
+// tensor: pair (line, pos) sits at z + line*z_line_stride + pos*z_pos_stride (bytes), its mask byte at
+// mask + line*m_line_stride + pos*m_pos_stride.  Outgoing: line = row, pos = column; incoming: line =
+// column, pos = row.
 struct TriMulInParams {
-  const void* z;           // [N][N][128] z stream (fp32 or bf16)
-  const uint8_t* mask;     // [N][N], non-zero = valid
+  const void* z;           // z stream (fp32 or bf16), 128 channels per pair
+  const uint8_t* mask;     // non-zero = valid
   const float* ln_w;
   const float* ln_b;
-  __nv_bfloat16* a_out;    // [128][Np][Np]
+  __nv_bfloat16* a_out;    // [128][lines_alloc][pos_pitch]
   __nv_bfloat16* b_out;
-  int N, Np;
-  int incoming;
-  int num_tiles;           // N * Np/128
+  int n_lines, n_pos;
+  int lines_alloc, pos_pitch;  // pos_pitch: multiple of 128 >= n_pos
+  long long z_line_stride, z_pos_stride;
+  long long m_line_stride, m_pos_stride;
+  int num_tiles;           // n_lines * pos_pitch/128
   float eps;
 };
 
@@ -54,7 +60,7 @@ trimul_in_kernel(const __grid_constant__ CUtensorMap tmW, TriMulInParams p) {
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
-  const int tiles_per_line = p.Np >> 7;
+  const int tiles_per_line = p.pos_pitch >> 7;
 
   if (threadIdx.x == 0) {
     mbar_init(w_full, 1);
@@ -106,10 +112,8 @@ trimul_in_kernel(const __grid_constant__ CUtensorMap tmW, TriMulInParams p) {
     const int pt = threadIdx.x - 128;  // 0..255
     float gamma[8], beta[8];
     load_gamma_beta(p.ln_w, p.ln_b, pt, gamma, beta);
-    const long long pos_stride = (p.incoming ? (long long)p.N * kD : kD) * (long long)zbytes<F32>();
-    const long long line_stride = (p.incoming ? kD : (long long)p.N * kD) * (long long)zbytes<F32>();
-    const long long mpos_stride = p.incoming ? p.N : 1;
-    const long long mline_stride = p.incoming ? 1 : p.N;
+    const long long pos_stride = p.z_pos_stride, line_stride = p.z_line_stride;
+    const long long mpos_stride = p.m_pos_stride, mline_stride = p.m_line_stride;
     RowTile<256> regs;
     uint8_t mreg = 0;
     auto load_tile = [&](int tile) {
@@ -120,12 +124,12 @@ trimul_in_kernel(const __grid_constant__ CUtensorMap tmW, TriMulInParams p) {
           pt,
           [&](int r) -> const void* {
             const int pos = pos0 + r;
-            return pos < p.N ? base + pos * pos_stride : nullptr;
+            return pos < p.n_pos ? base + pos * pos_stride : nullptr;
           },
           gamma, beta, p.eps);
       if (pt < 128) {
         const int pos = pos0 + pt;
-        mreg = (pos < p.N) ? p.mask[line * mline_stride + pos * mpos_stride] : 0;
+        mreg = (pos < p.n_pos) ? p.mask[line * mline_stride + pos * mpos_stride] : 0;
       }
     };
     int it = 0;
@@ -152,7 +156,7 @@ trimul_in_kernel(const __grid_constant__ CUtensorMap tmW, TriMulInParams p) {
       for (int half = 0; half < 2; ++half) {
         mbar_wait(&acc_full[half], it & 1, 14);
         tc_fence_after_sync();
-        __nv_bfloat16* dst = (half ? p.b_out : p.a_out) + ((long long)d * p.Np + line) * p.Np + pos0;
+        __nv_bfloat16* dst = (half ? p.b_out : p.a_out) + ((long long)d * p.lines_alloc + line) * p.pos_pitch + pos0;
 #pragma unroll 1
         for (int c = 0; c < 4; ++c) {
           uint32_t pv[32], gv[32];
@@ -190,15 +194,18 @@ trimul_in_kernel(const __grid_constant__ CUtensorMap tmW, TriMulInParams p) {
 
 // ---------------------------------------------------------------------------------------------
 
+// Same lines x positions geometry as TriMulInParams; t is [128][lines_alloc][pos_pitch] (tensor map) and is
+// indexed by (line, pos), so a transposed t goes with line = column, pos = row.
 struct TriMulOutParams {
-  const void* z;           // [N][N][128]  z stream: input of the op (gate and, optionally, residual)
-  void* out;               // [N][N][128]  same dtype as z, may alias it
+  const void* z;           // z stream: input of the op (gate and, optionally, residual)
+  void* out;               // same dtype and strides as z, may alias it
   const float* ln_in_w;
   const float* ln_in_b;
   const float* ln_out_w;
   const float* ln_out_b;
-  int N, Np;
-  int num_tiles;           // N * Np/128
+  int n_lines, n_pos, pos_pitch;
+  long long z_line_stride, z_pos_stride;
+  int num_tiles;           // n_lines * pos_pitch/128
   int add_residual;
   float eps;
 };
@@ -234,7 +241,7 @@ trimul_out_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
-  const int tiles_per_line = p.Np >> 7;
+  const int tiles_per_line = p.pos_pitch >> 7;
 
   if (threadIdx.x == 0) {
     mbar_init(w_full, 1);
@@ -350,10 +357,10 @@ trimul_out_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant
     auto load_tile = [&](int tile) {
       const int line = tile / tiles_per_line;
       const int pos0 = (tile - line * tiles_per_line) << 7;
-      const uint8_t* base = static_cast<const uint8_t*>(p.z) + ((long long)line * p.N + pos0) * kD * zbytes<F32>();
+      const uint8_t* base = static_cast<const uint8_t*>(p.z) + line * p.z_line_stride + pos0 * p.z_pos_stride;
       regs.template load<F32, true>(
           pt,
-          [&](int r) -> const void* { return (pos0 + r) < p.N ? base + (long long)r * kD * zbytes<F32>() : nullptr; },
+          [&](int r) -> const void* { return (pos0 + r) < p.n_pos ? base + r * p.z_pos_stride : nullptr; },
           gamma, beta, p.eps);
     };
     int it = 0;
@@ -375,8 +382,8 @@ trimul_out_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant
       const int line = tile / tiles_per_line;
       const int pos0 = (tile - line * tiles_per_line) << 7;
       const int acc = it & 1;
-      const bool valid = (pos0 + r) < p.N;
-      const long long off = ((long long)line * p.N + pos0 + r) * kD * zbytes<F32>();
+      const bool valid = (pos0 + r) < p.n_pos;
+      const long long off = line * p.z_line_stride + (pos0 + r) * p.z_pos_stride;
       const uint8_t* zrow = static_cast<const uint8_t*>(p.z) + off;
       uint8_t* orow = static_cast<uint8_t*>(p.out) + off;
       mbar_wait(&acc_full[acc], (it >> 1) & 1, 28);

@@ -445,3 +445,50 @@ def attention_core(q: Tensor, k: Tensor, v: Tensor, bias: Tensor, key_mask: Tens
         N, H, Bt)
     _lib.check(lib.b200_attention_core_fwd(ctypes.byref(a), _stream()))
     return out.view(Bt, N, H, dh)
+
+
+# ----------------------------------------------------------------------------------- staged triangle multiplication
+def pad128(n: int) -> int:
+    return (n + 127) // 128 * 128
+
+
+def trimul_project(z_slab: Tensor, mask_slab: Tensor, w: TriMulPacked, incoming: bool) -> tuple[Tensor, Tensor]:
+    """Projection stage on a slab ``z[n_rows, n_cols, 128]``: returns ``a, b`` as bf16 ``[128, lines, pos_pitch]``
+    with (line, pos) = (row, col) for outgoing and (col, row) for incoming, zero-padded in ``pos``."""
+    _require_cuda(z_slab, mask_slab)
+    zd = _zdtype(z_slab)
+    z_slab = z_slab.contiguous()
+    n_rows, n_cols = z_slab.shape[0], z_slab.shape[1]
+    lines, pos = (n_cols, n_rows) if incoming else (n_rows, n_cols)
+    pitch = pad128(pos)
+    a = torch.empty(128, lines, pitch, dtype=torch.bfloat16, device=z_slab.device)
+    b = torch.empty_like(a)
+    m8 = mask_u8(mask_slab)
+    _lib.check(lib.b200_trimul_project(z_slab.data_ptr(), m8.data_ptr(), a.data_ptr(), b.data_ptr(), ctypes.byref(w.struct),
+                                       n_rows, n_cols, n_cols * 128, n_cols, 1 if incoming else 0, pitch, zd, _stream()))
+    return a, b
+
+
+def trimul_output_(z_slab: Tensor, t: Tensor, w: TriMulPacked, transposed_t: bool, add_residual: bool = True) -> Tensor:
+    """Output stage on the slab, in place: ``z (+)= p_out(LN(t)) * sigmoid(g_out(LN(z)))`` with ``t`` bf16
+    ``[128, lines, pos_pitch]``."""
+    zd = _zdtype(z_slab)
+    if not z_slab.is_contiguous() or t.dtype != torch.bfloat16 or not t.is_contiguous():
+        raise ValueError("trimul_output_ needs a contiguous slab and a contiguous bf16 t")
+    n_rows, n_cols = z_slab.shape[0], z_slab.shape[1]
+    _lib.check(lib.b200_trimul_output(t.data_ptr(), z_slab.data_ptr(), z_slab.data_ptr(), ctypes.byref(w.struct), n_rows,
+                                      n_cols, n_cols * 128, 1 if transposed_t else 0, t.shape[2], 1 if add_residual else 0,
+                                      zd, _stream()))
+    return z_slab
+
+
+def bmm_nt_into(a: Tensor, b: Tensor, out: Tensor, scale: float = 1.0) -> Tensor:
+    """``out[n] = scale * a[n] @ b[n].T`` for bf16 ``a[batch, M, K]``, ``b[batch, N, K]`` given as (possibly strided in
+    batch and row) views with unit stride in K; ``out[batch, M, N]`` bf16 or fp32, unit stride in N."""
+    if a.stride(2) != 1 or b.stride(2) != 1 or out.stride(2) != 1:
+        raise ValueError("bmm_nt_into needs unit stride along the last axis")
+    batch, M, K = a.shape
+    N = b.shape[1]
+    _lib.check(lib.b200_bmm_nt(a.data_ptr(), b.data_ptr(), out.data_ptr(), batch, M, N, K, a.stride(1), b.stride(1),
+                               out.stride(1), a.stride(0), b.stride(0), out.stride(0), scale, _zdtype(out), _stream()))
+    return out

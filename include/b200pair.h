@@ -107,6 +107,31 @@ int b200_trimul_fwd(const void* z, const uint8_t* mask, void* out, const b200_tr
                     b200_stream_t stream);
 
 /* ---------------------------------------------------------------------------------------------------
+ * Triangle multiplication in stages, for callers that shard the pair tensor (the 2D context-parallel form,
+ * src/bioemu2/context_parallel/ops/triangle_multiplication.py:45-182 and ops/triangular_mult_impl.py:113-385):
+ * the projection and the output stage run on a rectangular slab z[n_rows][n_cols][128] (row pitch
+ * z_row_stride elements), the contraction is b200_bmm_nt on whatever the caller has gathered in between.
+ *
+ * b200_trimul_project  a, b = halves of mask * p_in(LN_in(z)) * sigmoid(g_in(LN_in(z))), written channel-major
+ *                      [128][lines][pos_pitch] bf16 with (line, pos) = (row, column) for incoming = 0 and
+ *                      (column, row) for incoming = 1; positions >= n_pos are written as zero up to pos_pitch
+ *                      (a multiple of 128), so the buffers can be used as zero-padded K-major GEMM operands.
+ * b200_trimul_output   out = p_out(LN_out(t)) * sigmoid(g_out(LN_in(z))) [+ z] on the slab, with t bf16
+ *                      [128][lines][pos_pitch] indexed (row, column), or (column, row) when transposed_t = 1.
+ * b200_bmm_nt          b200_bmm_nt_bf16 with a selectable output type (fp32 for partial sums that are reduced
+ *                      across GPUs afterwards).
+ * ------------------------------------------------------------------------------------------------- */
+int b200_trimul_project(const void* z, const uint8_t* mask, void* a_out, void* b_out, const b200_trimul_weights* w,
+                        int n_rows, int n_cols, int64_t z_row_stride, int64_t mask_row_stride, int incoming,
+                        int pos_pitch, int z_dtype, b200_stream_t stream);
+int b200_trimul_output(const void* t, const void* z, void* out, const b200_trimul_weights* w, int n_rows, int n_cols,
+                       int64_t z_row_stride, int transposed_t, int pos_pitch, int add_residual, int z_dtype,
+                       b200_stream_t stream);
+int b200_bmm_nt(const void* A, const void* B, void* C, int batch, int M, int N, int K, int64_t lda, int64_t ldb,
+                int64_t ldc, int64_t a_batch_stride, int64_t b_batch_stride, int64_t c_batch_stride, float scale,
+                int out_dtype, b200_stream_t stream);
+
+/* ---------------------------------------------------------------------------------------------------
  * Triangle multiplication without a caller workspace and without any allocation.
  * (No counterpart in the reference: it exists for callers of this library that must not allocate device
  * memory -- a serving loop whose memory is fully handed to another framework's pool, a latency-critical

@@ -1,0 +1,99 @@
+"""Context-parallel host logic on CPU: grid geometry against the reference's own helpers, and the
+all-gather / reduce-scatter exchange of triangle multiplication as gloo ranks (world sizes 2 and 4) with the
+oracle doing the local arithmetic."""
+import os
+import sys
+
+import pytest
+import torch
+import torch.distributed as dist
+import torch.multiprocessing as mp
+
+sys.path.insert(0, os.path.dirname(os.path.abspath(__file__)))
+import helpers as H  # noqa: E402
+from oracle import pair_ops as O  # noqa: E402
+from oracle import reference_shim  # noqa: E402
+
+
+def test_shard_range_is_torch_chunk():
+    from bioemu2_b200.context_parallel import shard_range
+
+    for n in (1, 7, 8, 64, 100, 129):
+        for parts in (1, 2, 3, 4, 8):
+            chunks = torch.arange(n).chunk(parts)
+            for i in range(parts):
+                lo, hi = shard_range(n, parts, i)
+                expect = chunks[i].tolist() if i < len(chunks) else []
+                assert list(range(lo, hi)) == expect
+
+
+@pytest.mark.skipif(not reference_shim.available(), reason="reference checkout not on this machine")
+def test_geometry_matches_reference_helpers():
+    """src/bioemu2/context_parallel/utils/mesh.py:17-55 in the reference."""
+    reference_shim.install()
+    from bioemu2.context_parallel.utils import mesh as ref_mesh
+
+    from bioemu2_b200.context_parallel import pad_amount, shard_multiple, shard_range
+
+    class FakeMesh:  # shard_multiple only asks a DeviceMesh for ndim and size(axis)
+        def __init__(self, shape):
+            self.shape, self.ndim = shape, len(shape)
+
+        def size(self, i):
+            return self.shape[i]
+
+    for g in ((1, 1), (2, 2), (1, 2), (2, 4), (4, 4), (3, 2)):
+        assert shard_multiple(*g) == ref_mesh.shard_multiple(FakeMesh((1,) + g))
+        assert ref_mesh.pad_amount(37, shard_multiple(*g)) == pad_amount(37, shard_multiple(*g))
+    for n in (7, 64, 100):
+        for parts in (1, 2, 4):
+            for i in range(parts):
+                lo, hi = shard_range(n, parts, i)
+                assert (lo, hi) == tuple(ref_mesh._shard_range(n, parts, i))
+
+
+def _worker(rank, world, rows, cols, port, n_tokens, q):
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    torch.set_num_threads(1)
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        from bioemu2_b200.context_parallel import CPGrid
+        from bioemu2_b200.context_parallel.trimul import cp_triangle_multiplication_
+        from cp_cpu_backend import CpuTriMulBackend, OracleWeights
+
+        grid = CPGrid(rows, cols)
+        g = torch.Generator().manual_seed(3)
+        w_out = {k: v.double() for k, v in H.trimul_weights(g, 16).items()}
+        w_in = {k: v.double() for k, v in H.trimul_weights(g, 16).items()}
+        z = torch.randn(1, n_tokens, n_tokens, 16, generator=g).double()
+        mask = torch.rand(1, n_tokens, n_tokens, generator=g) > 0.25
+        ref = z + O.triangle_multiplication(z, mask, w_out, "outgoing")
+        ref = ref + O.triangle_multiplication(ref, mask, w_in, "incoming")
+        z_loc, m_loc = grid.shard_pair(z)[0], grid.shard_pair(mask)[0]
+        be = CpuTriMulBackend()
+        cp_triangle_multiplication_(z_loc, m_loc, OracleWeights(w_out, "outgoing"), grid, False, n_tokens, backend=be)
+        cp_triangle_multiplication_(z_loc, m_loc, OracleWeights(w_in, "incoming"), grid, True, n_tokens, backend=be)
+        err = float((z_loc - grid.shard_pair(ref)[0]).abs().max())
+        q.put((rank, err))
+    finally:
+        dist.destroy_process_group()
+
+
+@pytest.mark.parametrize("rows,cols,n_tokens", [(1, 2, 12), (2, 1, 12), (2, 2, 12), (1, 4, 8), (4, 1, 8)])
+def test_cp_trimul_matches_serial_on_gloo(rows, cols, n_tokens):
+    """Outgoing then incoming triangle multiplication, sharded, against the serial oracle (reference's analogous
+    test: tests/context_parallel/ops/test_trimul_serial_vs_cp.py, fp32 atol 2e-6; fp64 here)."""
+    world = rows * cols
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    port = 29500 + (os.getpid() + rows * 7 + cols * 13 + n_tokens) % 2000
+    procs = [ctx.Process(target=_worker, args=(r, world, rows, cols, port, n_tokens, q)) for r in range(world)]
+    for p in procs:
+        p.start()
+    for p in procs:
+        p.join(120)
+        assert p.exitcode == 0
+    errs = dict(q.get(timeout=5) for _ in range(world))
+    assert len(errs) == world
+    assert max(errs.values()) < 1e-10, errs
