@@ -50,6 +50,9 @@ def parse_args():
                          "pair transition, single-track pair-bias attention, single transition); "
                          "pairmixer: the reference trunk's own block (no attention)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--cp", default=None, metavar="RxC",
+                    help="context-parallel mode: ONE pair tensor tiled over an RxC grid of the --gpus ranks (strong "
+                         "scaling) running the PairMixer blocks; the default without --cp is independent replicas")
     return ap.parse_args()
 
 
@@ -441,10 +444,81 @@ def run_b200(args) -> None:
         dist.destroy_process_group()
 
 
+def run_cp(args) -> None:
+    """One pair tensor sharded over an RxC grid: triangle multiplication exchanges b-operands (all-gather over the
+    column / row group) and fp32 partial sums (reduce-scatter); everything else is local to the block."""
+    import torch.distributed as dist
+
+    import bioemu2_b200 as b
+    from bioemu2_b200.context_parallel import CPGrid, CPPairMixerModule, kernel_shard_multiple
+
+    rows, cols = (int(v) for v in args.cp.lower().split("x"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    if rows * cols != world:
+        raise SystemExit(f"--cp {args.cp} needs {rows * cols} ranks, got {world}")
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+    os.environ.setdefault("MASTER_PORT", "29511")
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=dev)
+    N = args.tokens
+    if N % kernel_shard_multiple(rows, cols):
+        raise SystemExit(f"--tokens must be a multiple of {kernel_shard_multiple(rows, cols)} for a {args.cp} grid")
+    grid = CPGrid(rows, cols)
+    torch.manual_seed(2)
+    serial = b.PairMixerModule(384, 128, args.blocks).eval().to(dev)  # same seed on every rank: replicated weights
+    cp = CPPairMixerModule(serial, grid)
+    (r0, r1), (c0, c1) = grid.coords.my_rows(N), grid.coords.my_cols(N)
+    g = torch.Generator(device=dev).manual_seed(100 + rank)
+    z0 = torch.randn(1, r1 - r0, c1 - c0, 128, device=dev, generator=g)
+    z = torch.empty_like(z0)
+    mask = torch.ones(1, r1 - r0, c1 - c0, dtype=torch.uint8, device=dev)
+
+    def step():
+        z.copy_(z0)
+        cp(z, mask)
+
+    with torch.no_grad():
+        sampler = ClockSampler(local)
+        if rank == 0:
+            sampler.start()
+        for _ in range(max(args.warmup, 3)):
+            step()
+        dist.barrier()
+        torch.cuda.synchronize()
+        ms = event_time_ms(step, args.steps)
+        dist.barrier()
+        torch.cuda.synchronize()
+        clocks = sampler.stop() if rank == 0 else None
+        status = b._lib.device_status()
+    tt = torch.tensor([ms], device=dev, dtype=torch.float64)
+    dist.all_reduce(tt, op=dist.ReduceOp.MAX)
+    ms = float(tt[0])
+    if rank == 0:
+        fl = block_flops(N, "pairmixer")
+        line = {
+            "metric": METRIC, "value": N * N / (ms * 1e-3), "unit": UNIT, "n_gpus": world, "steps": args.steps,
+            "warmup": max(args.warmup, 3), "ms_per_step": ms, "higher_is_better": True, "scaling": "strong",
+            "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+            "config": {"workload": f"context-parallel PairMixer trunk, {args.blocks} blocks, N={N}, one pair tensor tiled "
+                                   f"{rows}x{cols} (block {r1 - r0}x{c1 - c0}), full mask", "grid": args.cp, "tokens": N,
+                       "blocks": args.blocks, "z_stream": "fp32",
+                       "exchange": "all-gather of the b operand + fp32 reduce-scatter of partial sums per direction (NCCL)"},
+            "clocks": clocks, "gpu_launches": args.steps * args.blocks * (2 * (3 + rows + cols) + 1),
+            "ops": {"trunk_tflops_aggregate": args.blocks * fl["block"] / (ms * 1e-3) / 1e12}, "device_status": status,
+        }
+        print(json.dumps(line), flush=True)
+    dist.destroy_process_group()
+
+
 def main():
     args = parse_args()
     if args.impl == "reference":
         run_reference(args)
+    elif args.cp:
+        run_cp(args)
     else:
         run_b200(args)
 
