@@ -86,12 +86,21 @@ SIGNATURES = {
     "b200_opm_fwd": (c_int, [c_void_p, c_void_p, c_int, c_void_p, POINTER(OpmWeights), c_int, c_int, c_int, c_int,
                              c_int, c_void_p, c_size_t, c_void_p]),
     "b200_attention_core_fwd": (c_int, [POINTER(AttentionCoreArgs), c_void_p]),
+    "b200_opm_cols_fwd": (c_int, [c_void_p, c_void_p, c_void_p, POINTER(OpmWeights), c_int, c_int, c_int, c_int, c_void_p,
+                                  c_int, c_int, c_int, c_void_p, c_size_t, c_void_p]),
     "b200_apb_workspace_bytes": (c_size_t, [c_int, c_int, c_int, c_int, c_int]),
     "b200_apb_fwd": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, POINTER(ApbWeights), c_int, c_int, c_int, c_int,
                              c_int, c_int, c_int, c_void_p, c_size_t, c_void_p]),
     "b200_triatt_workspace_bytes": (c_size_t, [c_int]),
     "b200_triatt_fwd": (c_int, [c_void_p, c_void_p, c_void_p, POINTER(TriAttWeights), c_int, c_int, c_int, c_int,
                                 c_int, c_void_p, c_size_t, c_void_p]),
+    "b200_pair_bias_fwd": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int64, c_int64,
+                                   c_int64, c_int, c_int, c_int, c_void_p]),
+    "b200_apb_fwd_bias": (c_int, [c_void_p, c_void_p, c_int64, c_void_p, c_void_p, POINTER(ApbWeights), c_int, c_int,
+                                  c_int, c_int, c_int, c_int, c_void_p, c_size_t, c_void_p]),
+    "b200_triatt_slab_workspace_bytes": (c_size_t, [c_int, c_int, c_int]),
+    "b200_triatt_slab_fwd": (c_int, [c_void_p, c_void_p, c_void_p, c_int64, c_void_p, POINTER(TriAttWeights), c_int,
+                                     c_int, c_int, c_int, c_int, c_void_p, c_size_t, c_void_p]),
     "b200_rows_to_bf16": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_int, c_int, c_int, c_int, c_void_p]),
     "b200_linear_bf16": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_int, c_int, c_int,
                                  c_void_p]),

@@ -1,15 +1,22 @@
 """2D context parallelism for the pair-representation path: one process per GPU, the pair tensor tiled over an
 R x C grid, NCCL all-gather / reduce-scatter over row and column groups around the single-GPU kernels."""
 from .mesh import CPGrid, GridCoords, kernel_shard_multiple, pad_amount, shard_multiple, shard_range
+from .attention import cp_attention_pair_bias, cp_outer_product_mean, cp_triangle_attention_
 from .modules import (
+    CPAttentionPairBias,
+    CPOuterProductMean,
+    CPPairformerBlock,
     CPPairMixerLayer,
     CPPairMixerModule,
     CPTransition,
+    CPTriangleAttention,
     CPTriangleMultiplication,
 )
 from .trimul import cp_triangle_multiplication_
 
 __all__ = [
     "CPGrid", "GridCoords", "kernel_shard_multiple", "pad_amount", "shard_multiple", "shard_range",
-    "CPPairMixerLayer", "CPPairMixerModule", "CPTransition", "CPTriangleMultiplication", "cp_triangle_multiplication_",
+    "CPAttentionPairBias", "CPOuterProductMean", "CPPairformerBlock", "CPPairMixerLayer", "CPPairMixerModule", "CPTransition",
+    "CPTriangleAttention", "CPTriangleMultiplication", "cp_attention_pair_bias", "cp_outer_product_mean",
+    "cp_triangle_attention_", "cp_triangle_multiplication_",
 ]

@@ -15,8 +15,12 @@ import torch
 import torch.nn as nn
 from torch import Tensor
 
+from ..attention_pair_bias import AttentionPairBias
+from ..outer_product_mean import OuterProductMean
 from ..transition import Transition
+from ..triangle_attention import TriangleAttention
 from ..triangle_multiplication import TriangleMultiplication
+from .attention import cp_attention_pair_bias, cp_outer_product_mean, cp_triangle_attention_
 from .mesh import CPGrid
 from .trimul import cp_triangle_multiplication_
 
@@ -96,3 +100,86 @@ class CPPairMixerModule(nn.Module):
             for layer in self.layers:
                 z = layer(z, pair_mask)
         return z
+
+
+class CPAttentionPairBias(nn.Module):
+    """``forward(s, z, mask, multiplicity)`` on sharded inputs: ``s`` rows of this rank (replicated over grid columns),
+    ``z`` this rank's pair block, ``mask`` this rank's token rows; returns the update for the same rows
+    (reference wrapper: src/bioemu2/context_parallel/ops/attention.py:74-105)."""
+
+    def __init__(self, attention: AttentionPairBias, grid: CPGrid, local=None) -> None:
+        super().__init__()
+        self.attention = attention
+        self.grid = grid
+        self.local = local
+
+    def forward(self, s, z, mask, multiplicity: int = 1):
+        out = cp_attention_pair_bias(_local(s), _local(z), _local(mask), self.attention.packed(), self.grid, multiplicity,
+                                     local=self.local)
+        if hasattr(s, "to_local"):
+            from torch.distributed.tensor import DTensor
+
+            return DTensor.from_local(out, s.device_mesh, s.placements, run_check=False)
+        return out
+
+
+class CPTriangleAttention(nn.Module):
+    """``forward(x, mask)``: ``x += TriangleAttention(x)`` on the sharded pair tensor, in place; returns ``x``."""
+
+    def __init__(self, layer: TriangleAttention, grid: CPGrid, local=None) -> None:
+        super().__init__()
+        self.layer = layer
+        self.grid = grid
+        self.local = local
+
+    def forward(self, x, mask):
+        xl, ml = _local(x), _local(mask)
+        packed = self.layer.packed()
+        for b in range(xl.shape[0]):
+            cp_triangle_attention_(xl[b], ml[b], packed, self.grid, self.layer.ending, local=self.local)
+        return x
+
+
+class CPOuterProductMean(nn.Module):
+    """``forward(m, mask, row_count)`` with ``m[B, S_r, n_c, 64]`` sharded over (depth -> grid rows, tokens -> grid
+    columns); returns this rank's pair block ``[B, n_r, n_c, 128]``
+    (reference: src/bioemu2/context_parallel/ops/outer_product_mean.py:199-262)."""
+
+    def __init__(self, serial: OuterProductMean, grid: CPGrid, local=None) -> None:
+        super().__init__()
+        self.serial = serial
+        self.grid = grid
+        self.local = local
+
+    def forward(self, m, mask, row_count):
+        ml, kl = _local(m), _local(mask)
+        packed = self.serial.packed()
+        outs = [cp_outer_product_mean(ml[b], kl[b], row_count[b:b + 1], packed, self.grid, local=self.local)
+                for b in range(ml.shape[0])]
+        return torch.stack(outs).to(ml.dtype)
+
+
+class CPPairformerBlock(nn.Module):
+    """The composite block on sharded inputs: ``(s_rows, z_block, token_mask_rows, token_mask_cols) -> (s_rows, z_block)``."""
+
+    def __init__(self, serial, grid: CPGrid) -> None:
+        super().__init__()
+        self.grid = grid
+        self.tri_mul_out = CPTriangleMultiplication(serial.tri_mul_out, grid)
+        self.tri_mul_in = CPTriangleMultiplication(serial.tri_mul_in, grid)
+        self.tri_att_start = CPTriangleAttention(serial.tri_att_start, grid)
+        self.tri_att_end = CPTriangleAttention(serial.tri_att_end, grid)
+        self.transition_z = CPTransition(serial.transition_z, grid)
+        self.attention = CPAttentionPairBias(serial.attention, grid)
+        self.transition_s = CPTransition(serial.transition_s, grid)
+
+    def forward(self, s, z, mask_rows, mask_cols):
+        pm = (mask_rows[:, :, None] & mask_cols[:, None, :]).to(torch.uint8)
+        self.tri_mul_out(z, pm)
+        self.tri_mul_in(z, pm)
+        self.tri_att_start(z, pm)
+        self.tri_att_end(z, pm)
+        self.transition_z.forward_residual_(z)
+        s += self.attention(s, z, mask_rows)
+        self.transition_s.forward_residual_(s)
+        return s, z

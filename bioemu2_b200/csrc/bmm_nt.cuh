@@ -28,9 +28,9 @@ struct BmmParams {
   int opm_ntok;
   // Residual and transposed pair store (output projection of triangle attention): with residual != nullptr
   // the value read from it at the destination offset is added; with remap_n > 0 row r = line * remap_n + pos
-  // is stored as row pos * remap_n + line.
+  // (line < remap_m) is stored as row pos * remap_m + line.
   const void* residual;
-  int remap_n;
+  int remap_n, remap_m;
 };
 
 template <int BN>
@@ -160,7 +160,7 @@ bmm_nt_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ C
           if (p.opm_ntok > 0)
             off0 = (((long long)(row >> 5) * p.opm_ntok + (col0 >> 5)) * 32 + (row & 31)) * 32;
           else if (p.remap_n > 0)
-            off0 = ((long long)(row % p.remap_n) * p.remap_n + row / p.remap_n) * p.ldc + col0;
+            off0 = ((long long)(row % p.remap_n) * p.remap_m + row / p.remap_n) * p.ldc + col0;
           else
             off0 = (long long)row * p.ldc + col0;
 #pragma unroll

@@ -35,7 +35,7 @@ struct BmmLaunch {
   int out_f32 = 0;
   int opm_ntok = 0;
   const void* residual = nullptr;
-  int remap_n = 0;
+  int remap_n = 0, remap_m = 0;
 };
 
 static int launch_bmm(const BmmLaunch& a, cudaStream_t stream) {
@@ -70,6 +70,7 @@ static int launch_bmm(const BmmLaunch& a, cudaStream_t stream) {
   p.opm_ntok = a.opm_ntok;
   p.residual = a.residual;
   p.remap_n = a.remap_n;
+  p.remap_m = a.remap_m > 0 ? a.remap_m : a.remap_n;
   const int total = p.tiles_m * p.tiles_n * a.batch;
   const int grid = total < sm_count() ? total : sm_count();
   if (BN == 256) {
@@ -155,7 +156,8 @@ static int launch_flash(const FlashLaunch& a, int DH, cudaStream_t stream) {
 }
 
 static int launch_pair_bias(const void* z, bool f32, const float* ln_w, const float* ln_b, const void* w_z,
-                            __nv_bfloat16* zb, int N, int Nk, int H, cudaStream_t stream, bool transposed = false) {
+                            __nv_bfloat16* zb, int n_lines, int n_pos, long long z_line_stride, long long z_pos_stride,
+                            long long out_plane, long long out_pitch, int H, cudaStream_t stream) {
   CUtensorMap tmW;
   const uint64_t dims[2] = {128, 16};
   const uint64_t str[1] = {256};
@@ -168,11 +170,14 @@ static int launch_pair_bias(const void* z, bool f32, const float* ln_w, const fl
   p.ln_w = ln_w;
   p.ln_b = ln_b;
   p.zb = zb;
-  p.N = N;
-  p.Nk = Nk;
+  p.n_lines = n_lines;
+  p.n_pos = n_pos;
+  p.z_line_stride = z_line_stride;
+  p.z_pos_stride = z_pos_stride;
+  p.out_plane = out_plane;
+  p.out_pitch = out_pitch;
   p.H = H;
-  p.transposed = transposed ? 1 : 0;
-  p.num_tiles = N * ((N + 127) / 128);
+  p.num_tiles = n_lines * ((n_pos + 127) / 128);
   p.scale = 1.4426950408889634f;
   p.eps = 1e-5f;
   const int grid = p.num_tiles < sm_count() ? p.num_tiles : sm_count();
@@ -554,9 +559,12 @@ size_t b200_opm_workspace_bytes(int S, int N) {
   return 2 * ab + outer + 1024;
 }
 
-int b200_opm_fwd(const void* m, const uint8_t* mask, int mask_ndim, void* out, const b200_opm_weights* w, int B,
-                 int S, int N, int m_dtype, int out_dtype, void* workspace, size_t workspace_bytes,
-                 b200_stream_t stream_) {
+// j0, nj: the token columns of the output to compute (all N rows always); ext_scale: device scalar replacing
+// 1 / (number of valid MSA rows) -- for a caller that holds only part of the MSA depth; add_bias: whether proj_o's bias
+// is added (exactly one of the partial results that are later summed should carry it).
+static int opm_run(const void* m, const uint8_t* mask, int mask_ndim, void* out, const b200_opm_weights* w, int B,
+                   int S, int N, int j0, int nj, const float* ext_scale, bool add_bias, int m_dtype, int out_dtype,
+                   void* workspace, size_t workspace_bytes, b200_stream_t stream_) {
   if (int e = b200_check_device()) return e;
   cudaStream_t stream = static_cast<cudaStream_t>(stream_);
   B200_CHECK_ARG(m && mask && out && w, "m/mask/out/w is NULL");
@@ -611,8 +619,8 @@ int b200_opm_fwd(const void* m, const uint8_t* mask, int mask_ndim, void* out, c
     else
       opm_proj_kernel<false><<<grid, opm_proj::THREADS, opm_proj::SMEM_BYTES, stream>>>(tmW, pp);
     B200_CUDA(cudaGetLastError());
-    const float* scale_ptr = nullptr;
-    if (mask_ndim == 3) {
+    const float* scale_ptr = ext_scale;
+    if (mask_ndim == 3 && !ext_scale) {
       opm_inv_row_count_kernel<<<1, 1024, 0, stream>>>(pp.mask, S, N, inv);
       B200_CUDA(cudaGetLastError());
       scale_ptr = inv;
@@ -620,21 +628,37 @@ int b200_opm_fwd(const void* m, const uint8_t* mask, int mask_ndim, void* out, c
     for (int i0 = 0; i0 < N; i0 += CI) {
       const int ci = (N - i0) < CI ? (N - i0) : CI;
       {
-        BmmLaunch a{aT + size_t(i0) * 32 * Sp, bT, outer, 1, ci * 32, N * 32, S, Sp, Sp, 0, 0, 0, 0};
+        BmmLaunch a{aT + size_t(i0) * 32 * Sp, bT + size_t(j0) * 32 * Sp, outer, 1, ci * 32, nj * 32, S, Sp, Sp, 0, 0, 0, 0};
         a.scale_ptr = scale_ptr;
-        a.opm_ntok = N;
+        a.opm_ntok = nj;
         if (int e = launch_bmm(a, stream)) return e;
       }
       {
-        void* dst = static_cast<uint8_t*>(out) + (size_t(bi) * N * N + size_t(i0) * N) * 128 * o_esz;
-        BmmLaunch a{outer, w->w_o, dst, 1, ci * N, 128, 1024, 1024, 1024, 128, 0, 0, 0};
-        a.bias = w->bias_o;
+        void* dst = static_cast<uint8_t*>(out) + (size_t(bi) * N * nj + size_t(i0) * nj) * 128 * o_esz;
+        BmmLaunch a{outer, w->w_o, dst, 1, ci * nj, 128, 1024, 1024, 1024, 128, 0, 0, 0};
+        a.bias = add_bias ? w->bias_o : nullptr;
         a.out_f32 = out_dtype == B200_DTYPE_F32;
         if (int e = launch_bmm(a, stream)) return e;
       }
     }
   }
   return B200_OK;
+}
+
+int b200_opm_fwd(const void* m, const uint8_t* mask, int mask_ndim, void* out, const b200_opm_weights* w, int B,
+                 int S, int N, int m_dtype, int out_dtype, void* workspace, size_t workspace_bytes,
+                 b200_stream_t stream) {
+  return opm_run(m, mask, mask_ndim, out, w, B, S, N, 0, N, nullptr, true, m_dtype, out_dtype, workspace, workspace_bytes,
+                 stream);
+}
+
+int b200_opm_cols_fwd(const void* m, const uint8_t* mask, void* out, const b200_opm_weights* w, int S, int N, int j0,
+                      int nj, const float* scale, int add_bias, int m_dtype, int out_dtype, void* workspace,
+                      size_t workspace_bytes, b200_stream_t stream) {
+  if (j0 < 0 || nj <= 0 || j0 + nj > N) return fail(B200_ERR_INVALID_ARGUMENT, "column range [%d, %d) outside [0, %d)", j0, j0 + nj, N);
+  if (!scale) return fail(B200_ERR_INVALID_ARGUMENT, "scale is NULL");
+  return opm_run(m, mask, 3, out, w, 1, S, N, j0, nj, scale, add_bias != 0, m_dtype, out_dtype, workspace, workspace_bytes,
+                 stream);
 }
 
 // ------------------------------------------------------------------------------------------------ attention core
@@ -717,19 +741,21 @@ size_t b200_apb_workspace_bytes(int B, int M, int N, int c_s, int H) {
   return pl.total;
 }
 
-int b200_apb_fwd(const void* s, const void* z, const uint8_t* mask, void* out, const b200_apb_weights* w, int B,
-                 int M, int N, int c_s, int H, int s_dtype, int z_dtype, void* workspace, size_t workspace_bytes,
-                 b200_stream_t stream_) {
+static int apb_run(const void* s, const void* z, const void* ext_bias, int64_t ext_bias_pitch, const uint8_t* mask,
+                   void* out, const b200_apb_weights* w, int B, int M, int N, int c_s, int H, int s_dtype, int z_dtype,
+                   void* workspace, size_t workspace_bytes, b200_stream_t stream_) {
   if (int e = b200_check_device()) return e;
   cudaStream_t stream = static_cast<cudaStream_t>(stream_);
-  B200_CHECK_ARG(s && z && mask && out && w, "s/z/mask/out/w is NULL");
+  B200_CHECK_ARG(s && (z || ext_bias) && mask && out && w, "s/z/mask/out/w is NULL");
   B200_CHECK_ARG(w->w_qkg && w->b_qkg && w->w_v && w->w_z && w->ln_z_w && w->w_o, "a weight pointer is NULL");
   B200_CHECK_ARG(B > 0 && M > 0 && N > 0, "B=%d, M=%d, N=%d must be positive", B, M, N);
   B200_CHECK_ARG((s_dtype | 1) == 1 && (z_dtype | 1) == 1, "unknown dtype");
   ApbPlan pl;
   B200_CHECK_ARG(apb_plan(B, M, N, c_s, H, &pl),
                  "unsupported c_s=%d, H=%d: need H <= 16, head dim a multiple of 8 and <= 64", c_s, H);
-  B200_CHECK_ARG(aligned(s, 32) && aligned(z, 32) && aligned(out, 32), "s/z/out must be 32-byte aligned");
+  B200_CHECK_ARG(aligned(s, 32) && (!z || aligned(z, 32)) && aligned(out, 32), "s/z/out must be 32-byte aligned");
+  B200_CHECK_ARG(!ext_bias || (aligned(ext_bias, 16) && ext_bias_pitch % 8 == 0 && ext_bias_pitch >= N),
+                 "bias must be 16-byte aligned with a pitch that is a multiple of 8 and >= N");
   if (!workspace || workspace_bytes < pl.total || !aligned(workspace, 1024))
     return fail(B200_ERR_WORKSPACE, "workspace must be 1024-byte aligned and hold %zu bytes (got %zu)", pl.total,
                 workspace_bytes);
@@ -757,12 +783,13 @@ int b200_apb_fwd(const void* s, const void* z, const uint8_t* mask, void* out, c
     BmmLaunch a{w->w_v, s_ln + size_t(b) * N * c_s, vT + size_t(b) * HD * pl.Nk, 1, HD, N, c_s, c_s, c_s, pl.Nk, 0, 0, 0};
     if (int e = launch_bmm(a, stream)) return e;
   }
-  // 3. pair bias, one pass over z per batch element
+  // 3. pair bias, one pass over z per batch element (unless the caller supplies it)
   const size_t z_esz = z_dtype == B200_DTYPE_F32 ? 4 : 2;
-  for (int b = 0; b < B; ++b) {
+  for (int b = 0; b < B && !ext_bias; ++b) {
     if (int e = launch_pair_bias(static_cast<const uint8_t*>(z) + size_t(b) * N * N * kD * z_esz,
                                  z_dtype == B200_DTYPE_F32, w->ln_z_w, w->ln_z_b, w->w_z,
-                                 zb + size_t(b) * H * N * pl.Nk, N, pl.Nk, H, stream))
+                                 zb + size_t(b) * H * N * pl.Nk, N, N, (long long)N * kD * z_esz, (long long)kD * z_esz,
+                                 (long long)N * pl.Nk, pl.Nk, H, stream))
       return e;
   }
   // 4. attention core
@@ -773,8 +800,8 @@ int b200_apb_fwd(const void* s, const void* z, const uint8_t* mask, void* out, c
     a.qk_b_stride = int64_t(N) * pl.W1;
     a.vT = vT;
     a.v_pitch = pl.Nk;
-    a.bias = zb;
-    a.bias_pitch = pl.Nk;
+    a.bias = ext_bias ? ext_bias : static_cast<const void*>(zb);
+    a.bias_pitch = ext_bias ? ext_bias_pitch : pl.Nk;
     a.bias_groups = B;
     FlashParams& p = a.p;
     p.mask = mask;
@@ -808,52 +835,79 @@ int b200_apb_fwd(const void* s, const void* z, const uint8_t* mask, void* out, c
   return B200_OK;
 }
 
+int b200_apb_fwd(const void* s, const void* z, const uint8_t* mask, void* out, const b200_apb_weights* w, int B,
+                 int M, int N, int c_s, int H, int s_dtype, int z_dtype, void* workspace, size_t workspace_bytes,
+                 b200_stream_t stream) {
+  if (!z) return fail(B200_ERR_INVALID_ARGUMENT, "z is NULL");
+  return apb_run(s, z, nullptr, 0, mask, out, w, B, M, N, c_s, H, s_dtype, z_dtype, workspace, workspace_bytes, stream);
+}
+
+int b200_apb_fwd_bias(const void* s, const void* bias, int64_t bias_pitch, const uint8_t* mask, void* out,
+                      const b200_apb_weights* w, int B, int M, int N, int c_s, int H, int s_dtype, void* workspace,
+                      size_t workspace_bytes, b200_stream_t stream) {
+  if (!bias) return fail(B200_ERR_INVALID_ARGUMENT, "bias is NULL");
+  return apb_run(s, nullptr, bias, bias_pitch, mask, out, w, B, M, N, c_s, H, s_dtype, B200_DTYPE_F32, workspace,
+                 workspace_bytes, stream);
+}
+
+int b200_pair_bias_fwd(const void* z, const float* ln_w, const float* ln_b, const void* w_z, void* out, int n_rows,
+                       int n_cols, int64_t z_row_stride, int64_t out_plane, int64_t out_pitch, int H, int transposed,
+                       int z_dtype, b200_stream_t stream) {
+  if (int e = b200_check_device()) return e;
+  B200_CHECK_ARG(z && ln_w && w_z && out, "z/ln_w/w_z/out is NULL");
+  B200_CHECK_ARG(n_rows > 0 && n_cols > 0 && H > 0 && H <= 16, "n_rows/n_cols must be positive, 1 <= H <= 16");
+  B200_CHECK_ARG((z_dtype | 1) == 1, "unknown z_dtype %d", z_dtype);
+  B200_CHECK_ARG(z_row_stride >= int64_t(n_cols) * kD && z_row_stride % 8 == 0, "row stride smaller than a row");
+  const int n_lines = transposed ? n_cols : n_rows, n_pos = transposed ? n_rows : n_cols;
+  B200_CHECK_ARG(out_pitch >= n_pos && out_plane >= int64_t(n_lines) * out_pitch, "output pitch/plane too small");
+  B200_CHECK_ARG(aligned(z, 32) && aligned(w_z, 16), "z must be 32-byte aligned, w_z 16-byte aligned");
+  const long long esz = z_dtype == B200_DTYPE_F32 ? 4 : 2;
+  const long long row_b = z_row_stride * esz, col_b = kD * esz;
+  return launch_pair_bias(z, z_dtype == B200_DTYPE_F32, ln_w, ln_b, w_z, static_cast<__nv_bfloat16*>(out), n_lines, n_pos,
+                          transposed ? col_b : row_b, transposed ? row_b : col_b, out_plane, out_pitch, H,
+                          static_cast<cudaStream_t>(stream));
+}
+
 // ------------------------------------------------------------------------------------------------ triangle attention
+// A slab holds `lines` complete attention rows: for the starting node a line is a row of z (the slab must span all
+// columns), for the ending node a line is a column (the slab must span all rows); `pos` is the token axis attended over.
 struct TriAttPlan {
-  int Nk;
+  int lines, pos, Nk;
   size_t off_qkg, off_vT, off_tb, off_og, total;
 };
 
-static void triatt_plan(int N, TriAttPlan* pl) {
-  pl->Nk = (N + 7) / 8 * 8;
+static void triatt_plan(int lines, int pos, bool own_bias, TriAttPlan* pl) {
+  pl->lines = lines;
+  pl->pos = pos;
+  pl->Nk = (pos + 7) / 8 * 8;
   auto up = [](size_t x) { return (x + 1023) / 1024 * 1024; };
   size_t o = 0;
-  pl->off_qkg = o; o += up(size_t(N) * N * 384 * 2);
-  pl->off_vT = o;  o += up(size_t(N) * kD * pl->Nk * 2);
-  pl->off_tb = o;  o += up(size_t(4) * N * pl->Nk * 2);
-  pl->off_og = o;  o += up(size_t(N) * N * kD * 2);
+  pl->off_qkg = o; o += up(size_t(lines) * pos * 384 * 2);
+  pl->off_vT = o;  o += up(size_t(lines) * kD * pl->Nk * 2);
+  pl->off_tb = o;  o += own_bias ? up(size_t(4) * pos * pl->Nk * 2) : 0;
+  pl->off_og = o;  o += up(size_t(lines) * pos * kD * 2);
   pl->total = o;
 }
 
-size_t b200_triatt_workspace_bytes(int N) {
-  if (N <= 0) return 0;
+static int triatt_slab(const void* z, const uint8_t* mask, const void* ext_bias, int64_t ext_bias_pitch, void* out,
+                       const b200_triatt_weights* w, int n_rows, int n_cols, bool ending, bool add_residual, bool f32,
+                       void* workspace, size_t workspace_bytes, cudaStream_t stream) {
+  const int lines = ending ? n_cols : n_rows, pos = ending ? n_rows : n_cols;
   TriAttPlan pl;
-  triatt_plan(N, &pl);
-  return pl.total;
-}
-
-int b200_triatt_fwd(const void* z, const uint8_t* mask, void* out, const b200_triatt_weights* w, int B, int N,
-                    int ending, int add_residual, int z_dtype, void* workspace, size_t workspace_bytes,
-                    b200_stream_t stream_) {
-  if (int e = b200_check_device()) return e;
-  cudaStream_t stream = static_cast<cudaStream_t>(stream_);
-  B200_CHECK_ARG(z && mask && out && w, "z/mask/out/w is NULL");
-  B200_CHECK_ARG(w->w_qkgv && w->g_bias && w->w_b && w->w_o && w->ln_w && w->ln_b, "a weight pointer is NULL");
-  B200_CHECK_ARG(B > 0 && N > 0, "B=%d, N=%d must be positive", B, N);
-  B200_CHECK_ARG((z_dtype | 1) == 1, "unknown z_dtype %d", z_dtype);
-  B200_CHECK_ARG(aligned(z, 32) && aligned(out, 32), "z/out must be 32-byte aligned");
-  TriAttPlan pl;
-  triatt_plan(N, &pl);
+  triatt_plan(lines, pos, ext_bias == nullptr, &pl);
   if (!workspace || workspace_bytes < pl.total || !aligned(workspace, 1024))
     return fail(B200_ERR_WORKSPACE, "workspace must be 1024-byte aligned and hold %zu bytes (got %zu)", pl.total,
                 workspace_bytes);
+  if (!ext_bias && n_rows != n_cols)
+    return fail(B200_ERR_INVALID_ARGUMENT, "a rectangular slab needs the triangle bias of the whole pair tensor");
   uint8_t* ws = static_cast<uint8_t*>(workspace);
   __nv_bfloat16* qkg = reinterpret_cast<__nv_bfloat16*>(ws + pl.off_qkg);
   __nv_bfloat16* vT = reinterpret_cast<__nv_bfloat16*>(ws + pl.off_vT);
   __nv_bfloat16* tb = reinterpret_cast<__nv_bfloat16*>(ws + pl.off_tb);
   __nv_bfloat16* og = reinterpret_cast<__nv_bfloat16*>(ws + pl.off_og);
-  const bool f32 = z_dtype == B200_DTYPE_F32;
-  const size_t esz = f32 ? 4 : 2;
+  const long long esz = f32 ? 4 : 2;
+  const long long row_b = (long long)n_cols * kD * esz, col_b = kD * esz;
+  const long long line_b = ending ? col_b : row_b, pos_b = ending ? row_b : col_b;
 
   CUtensorMap tmW;
   {
@@ -864,72 +918,128 @@ int b200_triatt_fwd(const void* z, const uint8_t* mask, void* out, const b200_tr
   }
   if (int e = set_smem(triatt_proj_kernel<true>, triatt_proj::SMEM_BYTES)) return e;
   if (int e = set_smem(triatt_proj_kernel<false>, triatt_proj::SMEM_BYTES)) return e;
-
-  for (int bi = 0; bi < B; ++bi) {
-    const uint8_t* zb_ = static_cast<const uint8_t*>(z) + size_t(bi) * N * N * kD * esz;
-    uint8_t* ob = static_cast<uint8_t*>(out) + size_t(bi) * N * N * kD * esz;
-    TriAttProjParams pp;
-    pp.z = zb_;
-    pp.ln_w = w->ln_w;
-    pp.ln_b = w->ln_b;
-    pp.g_bias = w->g_bias;
-    pp.qkg = qkg;
-    pp.vT = vT;
-    pp.N = N;
-    pp.Nk = pl.Nk;
-    pp.transposed = ending ? 1 : 0;
-    pp.num_tiles = N * ((N + 127) / 128);
-    pp.eps = 1e-5f;
-    const int grid = pp.num_tiles < sm_count() ? pp.num_tiles : sm_count();
-    if (f32)
-      triatt_proj_kernel<true><<<grid, triatt_proj::THREADS, triatt_proj::SMEM_BYTES, stream>>>(tmW, pp);
-    else
-      triatt_proj_kernel<false><<<grid, triatt_proj::THREADS, triatt_proj::SMEM_BYTES, stream>>>(tmW, pp);
-    B200_CUDA(cudaGetLastError());
-    if (int e = launch_pair_bias(zb_, f32, w->ln_w, w->ln_b, w->w_b, tb, N, pl.Nk, 4, stream, ending != 0)) return e;
-    {
-      FlashLaunch a;
-      a.qk = qkg;
-      a.qk_width = 384;
-      a.qk_b_stride = int64_t(N) * 384;
-      a.vT = vT;
-      a.v_pitch = pl.Nk;
-      a.bias = tb;
-      a.bias_pitch = pl.Nk;
-      a.bias_groups = 1;
-      FlashParams& p = a.p;
-      p.mask = mask + size_t(bi) * N * N;
-      p.mask_div = 1;
-      // line l attends over keys k with mask[l][k] (starting node) or mask[k][l] (ending node)
-      p.mask_row_stride = ending ? 1 : N;
-      p.mask_key_stride = ending ? N : 1;
-      p.bias_div = N;
-      p.gate = qkg;
-      p.gate_b_stride = int64_t(N) * 384;
-      p.gate_pitch = 384;
-      p.gate_col0 = 256;
-      p.out = og;
-      p.out_b_stride = int64_t(N) * kD;
-      p.out_pitch = kD;
-      p.out_col0 = 0;
-      p.dh_out = 32;
-      p.N = N;
-      p.H = 4;
-      p.Bt = N;
-      p.q_col0 = 0;
-      p.k_col0 = 128;
-      p.v_row0 = 0;
-      if (int e = launch_flash(a, 32, stream)) return e;
-    }
-    {
-      BmmLaunch a{og, w->w_o, ob, 1, N * N, kD, kD, kD, kD, kD, 0, 0, 0};
-      a.out_f32 = f32;
-      a.residual = add_residual ? static_cast<const void*>(zb_) : nullptr;
-      a.remap_n = ending ? N : 0;
-      if (int e = launch_bmm(a, stream)) return e;
-    }
+  TriAttProjParams pp;
+  pp.z = z;
+  pp.ln_w = w->ln_w;
+  pp.ln_b = w->ln_b;
+  pp.g_bias = w->g_bias;
+  pp.qkg = qkg;
+  pp.vT = vT;
+  pp.n_lines = lines;
+  pp.n_pos = pos;
+  pp.Nk = pl.Nk;
+  pp.z_line_stride = line_b;
+  pp.z_pos_stride = pos_b;
+  pp.num_tiles = lines * ((pos + 127) / 128);
+  pp.eps = 1e-5f;
+  const int grid = pp.num_tiles < sm_count() ? pp.num_tiles : sm_count();
+  if (f32)
+    triatt_proj_kernel<true><<<grid, triatt_proj::THREADS, triatt_proj::SMEM_BYTES, stream>>>(tmW, pp);
+  else
+    triatt_proj_kernel<false><<<grid, triatt_proj::THREADS, triatt_proj::SMEM_BYTES, stream>>>(tmW, pp);
+  B200_CUDA(cudaGetLastError());
+  if (!ext_bias) {
+    if (int e = launch_pair_bias(z, f32, w->ln_w, w->ln_b, w->w_b, tb, lines, pos, line_b, pos_b, (long long)pos * pl.Nk,
+                                 pl.Nk, 4, stream))
+      return e;
+  }
+  {
+    FlashLaunch a;
+    a.qk = qkg;
+    a.qk_width = 384;
+    a.qk_b_stride = int64_t(pos) * 384;
+    a.vT = vT;
+    a.v_pitch = pl.Nk;
+    a.bias = ext_bias ? ext_bias : static_cast<const void*>(tb);
+    a.bias_pitch = ext_bias ? ext_bias_pitch : pl.Nk;
+    a.bias_groups = 1;
+    FlashParams& p = a.p;
+    p.mask = mask;
+    p.mask_div = 1;
+    // line l attends over keys k with mask[l][k] (starting node) or mask[k][l] (ending node)
+    p.mask_row_stride = ending ? 1 : n_cols;
+    p.mask_key_stride = ending ? n_cols : 1;
+    p.bias_div = lines;
+    p.gate = qkg;
+    p.gate_b_stride = int64_t(pos) * 384;
+    p.gate_pitch = 384;
+    p.gate_col0 = 256;
+    p.out = og;
+    p.out_b_stride = int64_t(pos) * kD;
+    p.out_pitch = kD;
+    p.out_col0 = 0;
+    p.dh_out = 32;
+    p.N = pos;
+    p.H = 4;
+    p.Bt = lines;
+    p.q_col0 = 0;
+    p.k_col0 = 128;
+    p.v_row0 = 0;
+    if (int e = launch_flash(a, 32, stream)) return e;
+  }
+  {
+    BmmLaunch a{og, w->w_o, out, 1, lines * pos, kD, kD, kD, kD, kD, 0, 0, 0};
+    a.out_f32 = f32;
+    a.residual = add_residual ? z : nullptr;
+    a.remap_n = ending ? pos : 0;
+    a.remap_m = ending ? lines : 0;
+    if (int e = launch_bmm(a, stream)) return e;
   }
   return B200_OK;
+}
+
+static bool triatt_weights_ok(const b200_triatt_weights* w) {
+  return w && w->w_qkgv && w->g_bias && w->w_b && w->w_o && w->ln_w && w->ln_b;
+}
+
+size_t b200_triatt_workspace_bytes(int N) {
+  if (N <= 0) return 0;
+  TriAttPlan pl;
+  triatt_plan(N, N, true, &pl);
+  return pl.total;
+}
+
+size_t b200_triatt_slab_workspace_bytes(int n_rows, int n_cols, int ending) {
+  if (n_rows <= 0 || n_cols <= 0) return 0;
+  TriAttPlan pl;
+  triatt_plan(ending ? n_cols : n_rows, ending ? n_rows : n_cols, false, &pl);
+  return pl.total;
+}
+
+int b200_triatt_fwd(const void* z, const uint8_t* mask, void* out, const b200_triatt_weights* w, int B, int N,
+                    int ending, int add_residual, int z_dtype, void* workspace, size_t workspace_bytes,
+                    b200_stream_t stream_) {
+  if (int e = b200_check_device()) return e;
+  B200_CHECK_ARG(z && mask && out, "z/mask/out is NULL");
+  B200_CHECK_ARG(triatt_weights_ok(w), "a weight pointer is NULL");
+  B200_CHECK_ARG(B > 0 && N > 0, "B=%d, N=%d must be positive", B, N);
+  B200_CHECK_ARG((z_dtype | 1) == 1, "unknown z_dtype %d", z_dtype);
+  B200_CHECK_ARG(aligned(z, 32) && aligned(out, 32), "z/out must be 32-byte aligned");
+  const bool f32 = z_dtype == B200_DTYPE_F32;
+  const size_t esz = f32 ? 4 : 2;
+  for (int bi = 0; bi < B; ++bi) {
+    const size_t off = size_t(bi) * N * N * kD * esz;
+    if (int e = triatt_slab(static_cast<const uint8_t*>(z) + off, mask + size_t(bi) * N * N, nullptr, 0,
+                            static_cast<uint8_t*>(out) + off, w, N, N, ending != 0, add_residual != 0, f32, workspace,
+                            workspace_bytes, static_cast<cudaStream_t>(stream_)))
+      return e;
+  }
+  return B200_OK;
+}
+
+int b200_triatt_slab_fwd(const void* z, const uint8_t* mask, const void* bias, int64_t bias_pitch, void* out,
+                         const b200_triatt_weights* w, int n_rows, int n_cols, int ending, int add_residual, int z_dtype,
+                         void* workspace, size_t workspace_bytes, b200_stream_t stream) {
+  if (int e = b200_check_device()) return e;
+  B200_CHECK_ARG(z && mask && bias && out, "z/mask/bias/out is NULL");
+  B200_CHECK_ARG(triatt_weights_ok(w), "a weight pointer is NULL");
+  B200_CHECK_ARG(n_rows > 0 && n_cols > 0, "n_rows=%d, n_cols=%d must be positive", n_rows, n_cols);
+  B200_CHECK_ARG((z_dtype | 1) == 1, "unknown z_dtype %d", z_dtype);
+  B200_CHECK_ARG(aligned(z, 32) && aligned(out, 32) && aligned(bias, 16), "z/out must be 32-byte aligned, bias 16-byte");
+  const int pos = ending ? n_rows : n_cols;
+  B200_CHECK_ARG(bias_pitch % 8 == 0 && bias_pitch >= pos, "bias pitch must be a multiple of 8 and >= %d", pos);
+  return triatt_slab(z, mask, bias, bias_pitch, out, w, n_rows, n_cols, ending != 0, add_residual != 0,
+                     z_dtype == B200_DTYPE_F32, workspace, workspace_bytes, static_cast<cudaStream_t>(stream));
 }
 
 // ------------------------------------------------------------------------------------------------ single-track helpers

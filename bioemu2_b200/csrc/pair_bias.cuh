@@ -10,13 +10,15 @@ namespace b200 {
 // 128 x 16 x 128 product per tile, lanes = pairs so every head's row is stored coalesced.
 //   warps 0-3 epilogue, warps 4-11 producers, warp 12 control.
 struct PairBiasParams {
-  const void* z;        // [N][N][128] fp32 or bf16
+  const void* z;        // pair-tensor slab, fp32 or bf16, 128 channels per pair
   const float* ln_w;
   const float* ln_b;    // nullptr: LayerNorm without bias
-  __nv_bfloat16* zb;    // [H][N][Nk]
-  int N, Nk, H;
-  int transposed;       // 1: bias of the transposed pair tensor, zb[h][i][j] from z[j][i]
-  int num_tiles;        // N * ceil(N/128)
+  __nv_bfloat16* zb;    // [H][lines][pitch]
+  int n_lines, n_pos;   // slab geometry: pair (line, pos) at z + line*z_line_stride + pos*z_pos_stride (bytes);
+  long long z_line_stride, z_pos_stride;  // swap the strides to get the bias of the transposed pair tensor
+  long long out_plane, out_pitch;         // zb[h*out_plane + line*out_pitch + pos] (elements)
+  int H;
+  int num_tiles;        // n_lines * ceil(n_pos/128)
   float scale;          // log2(e)
   float eps;
 };
@@ -43,7 +45,7 @@ pair_bias_kernel(const __grid_constant__ CUtensorMap tmW, PairBiasParams p) {
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_empty + 2);
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
-  const int tiles_per_row = (p.N + 127) >> 7;
+  const int tiles_per_row = (p.n_pos + 127) >> 7;
 
   if (threadIdx.x == 0) {
     mbar_init(w_full, 1);
@@ -90,14 +92,13 @@ pair_bias_kernel(const __grid_constant__ CUtensorMap tmW, PairBiasParams p) {
     float gamma[8], beta[8];
     load_gamma_beta(p.ln_w, p.ln_b, pt, gamma, beta);
     RowTile<256> regs;
-    const long long pos_stride = (p.transposed ? (long long)p.N * kD : kD) * (long long)zbytes<F32>();
-    const long long line_stride = (p.transposed ? kD : (long long)p.N * kD) * (long long)zbytes<F32>();
+    const long long pos_stride = p.z_pos_stride, line_stride = p.z_line_stride;
     auto load_tile = [&](int tile) {
       const int i = tile / tiles_per_row;
       const int j0 = (tile - i * tiles_per_row) << 7;
       const uint8_t* base = static_cast<const uint8_t*>(p.z) + i * line_stride;
       regs.template load<F32, true>(
-          pt, [&](int r) -> const void* { return (j0 + r) < p.N ? base + (j0 + r) * pos_stride : nullptr; },
+          pt, [&](int r) -> const void* { return (j0 + r) < p.n_pos ? base + (j0 + r) * pos_stride : nullptr; },
           gamma, beta, p.eps);
     };
     int it = 0;
@@ -125,10 +126,10 @@ pair_bias_kernel(const __grid_constant__ CUtensorMap tmW, PairBiasParams p) {
       tmem_ld_wait();
       tc_fence_before_sync();
       mbar_arrive(&acc_empty[acc]);
-      if (j < p.N) {
+      if (j < p.n_pos) {
 #pragma unroll
         for (int h = 0; h < 16; ++h)
-          if (h < p.H) p.zb[((long long)h * p.N + i) * p.Nk + j] = __float2bfloat16(__uint_as_float(v[h]) * p.scale);
+          if (h < p.H) p.zb[h * p.out_plane + i * p.out_pitch + j] = __float2bfloat16(__uint_as_float(v[h]) * p.scale);
       }
     }
   }

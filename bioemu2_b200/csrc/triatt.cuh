@@ -14,15 +14,15 @@
 namespace b200 {
 
 struct TriAttProjParams {
-  const void* z;         // [N][N][128] fp32 or bf16
+  const void* z;         // pair-tensor slab, fp32 or bf16: pair (line, pos) at z + line*z_line_stride + pos*z_pos_stride
   const float* ln_w;
   const float* ln_b;
   const float* g_bias;   // [128]
-  __nv_bfloat16* qkg;    // [N lines][N pos][384]
-  __nv_bfloat16* vT;     // [N lines][128][Nk]
-  int N, Nk;
-  int transposed;        // 0: starting node, 1: ending node
-  int num_tiles;         // N * ceil(N/128)
+  __nv_bfloat16* qkg;    // [lines][n_pos][384]
+  __nv_bfloat16* vT;     // [lines][128][Nk]
+  int n_lines, n_pos, Nk;
+  long long z_line_stride, z_pos_stride;  // bytes; starting node: line = row, ending node: line = column
+  int num_tiles;         // n_lines * ceil(n_pos/128)
   float eps;
 };
 
@@ -51,7 +51,7 @@ triatt_proj_kernel(const __grid_constant__ CUtensorMap tmW, TriAttProjParams p) 
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
-  const int tiles_per_line = (p.N + 127) >> 7;
+  const int tiles_per_line = (p.n_pos + 127) >> 7;
 
   if (threadIdx.x == 0) {
     mbar_init(w_full, 1);
@@ -102,8 +102,7 @@ triatt_proj_kernel(const __grid_constant__ CUtensorMap tmW, TriAttProjParams p) 
     const int pt = threadIdx.x - 128;
     float gamma[8], beta[8];
     load_gamma_beta(p.ln_w, p.ln_b, pt, gamma, beta);
-    const long long pos_stride = (p.transposed ? (long long)p.N * kD : kD) * (long long)zbytes<F32>();
-    const long long line_stride = (p.transposed ? kD : (long long)p.N * kD) * (long long)zbytes<F32>();
+    const long long pos_stride = p.z_pos_stride, line_stride = p.z_line_stride;
     RowTile<256> regs;
     auto load_tile = [&](int tile) {
       const int line = tile / tiles_per_line;
@@ -113,7 +112,7 @@ triatt_proj_kernel(const __grid_constant__ CUtensorMap tmW, TriAttProjParams p) 
           pt,
           [&](int r) -> const void* {
             const int pos = pos0 + r;
-            return pos < p.N ? base + pos * pos_stride : nullptr;
+            return pos < p.n_pos ? base + pos * pos_stride : nullptr;
           },
           gamma, beta, p.eps);
     };
@@ -135,8 +134,8 @@ triatt_proj_kernel(const __grid_constant__ CUtensorMap tmW, TriAttProjParams p) 
     for (int tile = blockIdx.x; tile < p.num_tiles; tile += gridDim.x, ++it) {
       const int line = tile / tiles_per_line;
       const int pos0 = (tile - line * tiles_per_line) << 7;
-      const bool valid = (pos0 + r) < p.N;
-      __nv_bfloat16* row = p.qkg + ((long long)line * p.N + pos0 + r) * 384;
+      const bool valid = (pos0 + r) < p.n_pos;
+      __nv_bfloat16* row = p.qkg + ((long long)line * p.n_pos + pos0 + r) * 384;
       // ---- group A: q, k
       mbar_wait(&acc_full[0], it & 1, 95);
       tc_fence_after_sync();
@@ -184,7 +183,7 @@ triatt_proj_kernel(const __grid_constant__ CUtensorMap tmW, TriAttProjParams p) 
         tmem_ld_wait();
 #pragma unroll
         for (int g = 0; g < 4; ++g) {
-          if (pos0 + c * 32 + g * 8 < p.N)
+          if (pos0 + c * 32 + g * 8 < p.n_pos)
             *reinterpret_cast<uint4*>(vrow + c * 32 + g * 8) = make_uint4(
                 pack_bf16x2(__uint_as_float(v[g * 8 + 0]), __uint_as_float(v[g * 8 + 1])),
                 pack_bf16x2(__uint_as_float(v[g * 8 + 2]), __uint_as_float(v[g * 8 + 3])),

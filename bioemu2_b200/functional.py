@@ -492,3 +492,80 @@ def bmm_nt_into(a: Tensor, b: Tensor, out: Tensor, scale: float = 1.0) -> Tensor
     _lib.check(lib.b200_bmm_nt(a.data_ptr(), b.data_ptr(), out.data_ptr(), batch, M, N, K, a.stride(1), b.stride(1),
                                out.stride(1), a.stride(0), b.stride(0), out.stride(0), scale, _zdtype(out), _stream()))
     return out
+
+
+# ----------------------------------------------------------------------------------- pieces for sharded attention
+def pad8(n: int) -> int:
+    return (n + 7) // 8 * 8
+
+
+def pair_bias_slab(z_slab: Tensor, ln_w: Tensor, ln_b: Tensor | None, w_z_bf16: Tensor, H: int,
+                   transposed: bool = False) -> Tensor:
+    """``log2(e) * proj(LN(z))`` on a slab ``z[n_rows, n_cols, 128]`` -> bf16 ``[H, lines, pad8(pos)]`` with
+    (line, pos) = (row, col), or (col, row) when ``transposed``."""
+    _require_cuda(z_slab)
+    zd = _zdtype(z_slab)
+    z_slab = z_slab.contiguous()
+    n_rows, n_cols = z_slab.shape[0], z_slab.shape[1]
+    lines, pos = (n_cols, n_rows) if transposed else (n_rows, n_cols)
+    out = torch.zeros(H, lines, pad8(pos), dtype=torch.bfloat16, device=z_slab.device)
+    _lib.check(lib.b200_pair_bias_fwd(z_slab.data_ptr(), ln_w.data_ptr(), _ptr(ln_b), w_z_bf16.data_ptr(), out.data_ptr(),
+                                      n_rows, n_cols, n_cols * 128, lines * pad8(pos), pad8(pos), H,
+                                      1 if transposed else 0, zd, _stream()))
+    return out
+
+
+def attention_pair_bias_with_bias(s: Tensor, bias: Tensor, mask: Tensor, w: ApbPacked, multiplicity: int = 1) -> Tensor:
+    """Pair-bias attention with a precomputed bias ``[B, H, N, pitch]`` (bf16, log2(e)-scaled, see ``pair_bias_slab``)."""
+    _require_cuda(s, bias, mask)
+    B, N = mask.shape
+    if s.shape[0] != B * multiplicity or s.shape[1] != N or s.shape[2] != w.c_s:
+        raise ValueError(f"{tuple(s.shape)}, mask {tuple(mask.shape)}, multiplicity={multiplicity}")
+    if bias.dtype != torch.bfloat16 or tuple(bias.shape[:3]) != (B, w.H, N) or not bias.is_contiguous():
+        raise ValueError(f"bias must be contiguous bf16 [B, H, N, pitch], got {tuple(bias.shape)}")
+    sd = _zdtype(s)
+    s = s.contiguous()
+    out = torch.empty_like(s)
+    m8 = mask_u8(mask)
+    nbytes = lib.b200_apb_workspace_bytes(B, multiplicity, N, w.c_s, w.H)
+    ws = workspace(nbytes, s.device)
+    _lib.check(lib.b200_apb_fwd_bias(s.data_ptr(), bias.data_ptr(), bias.shape[3], m8.data_ptr(), out.data_ptr(),
+                                     ctypes.byref(w.struct), B, multiplicity, N, w.c_s, w.H, sd, ws.data_ptr(), nbytes,
+                                     _stream()))
+    return out
+
+
+def triangle_attention_slab(z_slab: Tensor, mask_slab: Tensor, bias: Tensor, w: TriAttPacked, ending: bool,
+                            add_residual: bool = False) -> Tensor:
+    """Triangle attention for the complete attention rows held in ``z_slab[n_rows, n_cols, 128]`` (all columns for the
+    starting node, all rows for the ending node), with the whole tensor's triangle bias ``[4, tokens, pitch]``."""
+    _require_cuda(z_slab, mask_slab, bias)
+    zd = _zdtype(z_slab)
+    z_slab = z_slab.contiguous()
+    n_rows, n_cols = z_slab.shape[0], z_slab.shape[1]
+    out = torch.empty_like(z_slab)
+    m8 = mask_u8(mask_slab)
+    nbytes = lib.b200_triatt_slab_workspace_bytes(n_rows, n_cols, 1 if ending else 0)
+    ws = workspace(nbytes, z_slab.device)
+    _lib.check(lib.b200_triatt_slab_fwd(z_slab.data_ptr(), m8.data_ptr(), bias.data_ptr(), bias.shape[2], out.data_ptr(),
+                                        ctypes.byref(w.struct), n_rows, n_cols, 1 if ending else 0,
+                                        1 if add_residual else 0, zd, ws.data_ptr(), nbytes, _stream()))
+    return out
+
+
+def outer_product_mean_cols(m: Tensor, mask: Tensor, w: OpmPacked, j0: int, nj: int, inv_count: Tensor,
+                            add_bias: bool) -> Tensor:
+    """Partial outer product mean over the MSA rows in ``m[S, N, 64]`` for output columns ``j0 .. j0+nj``: fp32
+    ``[N, nj, 128]`` scaled by the device scalar ``inv_count`` (fp32, 1 element)."""
+    _require_cuda(m, mask, inv_count)
+    S, N, _ = m.shape
+    zd = _zdtype(m)
+    m = m.contiguous()
+    out = torch.empty(N, nj, 128, dtype=torch.float32, device=m.device)
+    m8 = mask_u8(mask)
+    nbytes = lib.b200_opm_workspace_bytes(S, N)
+    ws = workspace(nbytes, m.device)
+    _lib.check(lib.b200_opm_cols_fwd(m.data_ptr(), m8.data_ptr(), out.data_ptr(), ctypes.byref(w.struct), S, N, j0, nj,
+                                     inv_count.data_ptr(), 1 if add_bias else 0, zd, _lib.DTYPE_F32, ws.data_ptr(), nbytes,
+                                     _stream()))
+    return out

@@ -193,6 +193,16 @@ int b200_opm_fwd(const void* m, const uint8_t* mask, int mask_ndim, void* out, c
                  int S, int N, int m_dtype, int out_dtype, void* workspace, size_t workspace_bytes,
                  b200_stream_t stream);
 
+/* Partial form for callers that shard the MSA depth and the pair columns (DistributedOuterProductMean,
+ * src/bioemu2/context_parallel/ops/outer_product_mean.py:116-262): m[S][N][64] holds only this caller's MSA rows,
+ * the output is out[N][nj][128] for token columns j0 .. j0+nj-1, scaled by the device scalar *scale (1 / global
+ * number of valid MSA rows) and, with add_bias = 0, without proj_o's bias -- partial results of different MSA
+ * slices are summed by the caller and exactly one of them should carry the bias.  mask: uint8 [S][N].
+ * Workspace: b200_opm_workspace_bytes(S, N). */
+int b200_opm_cols_fwd(const void* m, const uint8_t* mask, void* out, const b200_opm_weights* w, int S, int N, int j0,
+                      int nj, const float* scale, int add_bias, int m_dtype, int out_dtype, void* workspace,
+                      size_t workspace_bytes, b200_stream_t stream);
+
 /* ---------------------------------------------------------------------------------------------------
  * Attention core on already projected operands: the fp32 softmax(q.k + bias, key mask) v section of
  * AttentionPairBias.forward (src/bioemu2/biomoa/ops/attention_pair_bias.py:165-222) and the core of the
@@ -302,6 +312,35 @@ size_t b200_triatt_workspace_bytes(int N);
 int b200_triatt_fwd(const void* z, const uint8_t* mask, void* out, const b200_triatt_weights* w, int B, int N,
                     int ending, int add_residual, int z_dtype, void* workspace, size_t workspace_bytes,
                     b200_stream_t stream);
+
+/* ---------------------------------------------------------------------------------------------------
+ * Pieces for sharded callers of the two attention ops (context-parallel wrappers,
+ * src/bioemu2/context_parallel/ops/attention.py:45-105 and ops/attention_impl.py:558-706,984-1183).
+ *
+ * b200_pair_bias_fwd   out[h][line][pos] = log2(e) * proj(LN(z[line,pos]))[h] on a rectangular slab
+ *                      z[n_rows][n_cols][128] (row pitch z_row_stride elements): the bias projection of
+ *                      AttentionPairBias (w_z = proj_z, 16 x 128 zero padded) or of triangle attention (w_z = W_b).
+ *                      (line, pos) = (row, column), or (column, row) with transposed = 1.  out is bf16 with element
+ *                      strides out_plane (between heads) and out_pitch (between lines).
+ * b200_apb_fwd_bias    b200_apb_fwd with the pair bias supplied by the caller: bias bf16 [B][H][N][bias_pitch] as
+ *                      produced by b200_pair_bias_fwd (it may have been assembled from several GPUs' slabs).
+ *                      Workspace as for b200_apb_fwd.
+ * b200_triatt_slab_fwd triangle attention for `lines` complete attention rows: the slab z[n_rows][n_cols][128]
+ *                      (contiguous) must span all columns for the starting node (lines = rows) or all rows for the
+ *                      ending node (lines = columns); bias bf16 [4][tokens][bias_pitch] is the triangle bias of the
+ *                      WHOLE pair tensor (transposed for the ending node), mask uint8 [n_rows][n_cols].
+ *                      Workspace: b200_triatt_slab_workspace_bytes(n_rows, n_cols, ending).
+ * ------------------------------------------------------------------------------------------------- */
+int b200_pair_bias_fwd(const void* z, const float* ln_w, const float* ln_b, const void* w_z, void* out, int n_rows,
+                       int n_cols, int64_t z_row_stride, int64_t out_plane, int64_t out_pitch, int H, int transposed,
+                       int z_dtype, b200_stream_t stream);
+int b200_apb_fwd_bias(const void* s, const void* bias, int64_t bias_pitch, const uint8_t* mask, void* out,
+                      const b200_apb_weights* w, int B, int M, int N, int c_s, int H, int s_dtype, void* workspace,
+                      size_t workspace_bytes, b200_stream_t stream);
+size_t b200_triatt_slab_workspace_bytes(int n_rows, int n_cols, int ending);
+int b200_triatt_slab_fwd(const void* z, const uint8_t* mask, const void* bias, int64_t bias_pitch, void* out,
+                         const b200_triatt_weights* w, int n_rows, int n_cols, int ending, int add_residual, int z_dtype,
+                         void* workspace, size_t workspace_bytes, b200_stream_t stream);
 
 /* ---------------------------------------------------------------------------------------------------
  * Single-track building blocks (token stream [rows][cols], rows = B*M*N): the pieces of

@@ -74,15 +74,17 @@ def attention_pair_bias(
     num_heads: int,
     multiplicity: int = 1,
     inf: float = 1e6,
+    bias: Tensor | None = None,
 ) -> Tensor:
-    """``AttentionPairBias.forward`` (un-tiled branch).
+    """``AttentionPairBias.forward`` (un-tiled branch).  ``bias`` ([B,H,N,N]) replaces ``proj_z(norm_z(z))`` when given
+    (used to check sharded callers that assemble the bias themselves).
 
     src/bioemu2/biomoa/ops/attention_pair_bias.py:128-192,224-225.  The key
     mask *replaces* masked logits by ``-inf`` (finite 1e6, :183-190); the pair
     bias ``proj_z(norm_z(z))`` is shared by the ``multiplicity`` copies (:172-179).
     """
     BM, N, c_s = s.shape
-    B = z.shape[0]
+    B = z.shape[0] if bias is None else bias.shape[0]
     assert BM == B * multiplicity
     H = num_heads
     dh = c_s // H
@@ -94,8 +96,11 @@ def attention_pair_bias(
     k = k.view(BM, N, H, dh)
     v = v.view(BM, N, H, dh)
     g = torch.sigmoid(linear(s, w["proj_g.weight"]))
-    zb = linear(layer_norm(z, w["norm_z.weight"], w.get("norm_z.bias")), w["proj_z.weight"])
-    zb = zb.permute(0, 3, 1, 2)  # [B, H, N, N]
+    if bias is None:
+        zb = linear(layer_norm(z, w["norm_z.weight"], w.get("norm_z.bias")), w["proj_z.weight"])
+        zb = zb.permute(0, 3, 1, 2)  # [B, H, N, N]
+    else:
+        zb = bias
     attn = torch.einsum("bihd,bjhd->bhij", q, k) / math.sqrt(dh)
     attn = attn.view(B, multiplicity, H, N, N) + zb.unsqueeze(1)
     key_mask = mask.bool().view(B, 1, 1, 1, N)

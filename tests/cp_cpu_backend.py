@@ -52,3 +52,62 @@ class CpuTriMulBackend:
 
     def check_block(self, n_rows, n_cols):
         pass
+
+
+class Packed:
+    """Stand-in for a packed-weights object on CPU: the state dict and the head count."""
+
+    def __init__(self, w: dict, H: int = 0):
+        self.w = w
+        self.H = H
+
+
+def _pad_last(t: torch.Tensor) -> torch.Tensor:
+    pitch = (t.shape[-1] + 7) // 8 * 8
+    out = t.new_zeros(t.shape[:-1] + (pitch,))
+    out[..., :t.shape[-1]] = t
+    return out
+
+
+class CpuAttentionLocal:
+    """Oracle-backed local steps of the context-parallel attention ops (biases in natural-log units)."""
+
+    def pair_bias(self, z_slab, packed):
+        w = packed.w
+        zb = O.linear(O.layer_norm(z_slab, w["norm_z.weight"], w.get("norm_z.bias")), w["proj_z.weight"])
+        return _pad_last(zb.permute(2, 0, 1))
+
+    def attention(self, s_full, bias_full, mask_full, packed, multiplicity):
+        n = s_full.shape[1]
+        return O.attention_pair_bias(s_full, None, mask_full, packed.w, packed.H, multiplicity, bias=bias_full[..., :n])
+
+    def tri_bias(self, z_slab, packed, ending):
+        w = packed.w
+        tb = O.linear(O.layer_norm(z_slab, w["layer_norm.weight"], w["layer_norm.bias"]), w["linear_b.weight"])
+        return _pad_last(tb.permute(2, 1, 0) if ending else tb.permute(2, 0, 1))
+
+    def tri_slab(self, slab, mask_slab, bias_full, packed, ending):
+        import math
+
+        w = packed.w
+        x, m = (slab.transpose(0, 1), mask_slab.transpose(0, 1)) if ending else (slab, mask_slab)  # [lines, N, D]
+        L, N, _ = x.shape
+        H, dh = 4, w["linear_q.weight"].shape[0] // 4
+        h = O.layer_norm(x, w["layer_norm.weight"], w["layer_norm.bias"])
+        q = O.linear(h, w["linear_q.weight"]).view(L, N, H, dh)
+        k = O.linear(h, w["linear_k.weight"]).view(L, N, H, dh)
+        v = O.linear(h, w["linear_v.weight"]).view(L, N, H, dh)
+        g = torch.sigmoid(O.linear(h, w["linear_g.weight"], w["linear_g.bias"]))
+        logits = torch.einsum("ijhd,ikhd->ihjk", q, k) / math.sqrt(dh) + bias_full[None, :, :, :N]
+        logits = torch.where(m.bool().view(L, 1, 1, N), logits, torch.full_like(logits, -1e6))
+        o = torch.einsum("ihjk,ikhd->ijhd", logits.softmax(-1), v).reshape(L, N, H * dh)
+        out = O.linear(g * o, w["linear_o.weight"])
+        return out.transpose(0, 1) if ending else out
+
+    def opm_partial(self, m_rows, mask_rows, packed, j0, nj, inv_count, add_bias):
+        w = packed.w
+        mp = O.linear(O.layer_norm(m_rows, w["norm.weight"], w["norm.bias"]), w["proj_ab.weight"])
+        mp = torch.where(mask_rows.bool().unsqueeze(-1), mp, torch.zeros_like(mp))
+        a, b = mp.chunk(2, dim=-1)
+        z = torch.einsum("sic,sjd->ijcd", a, b[:, j0:j0 + nj]).reshape(a.shape[1], nj, -1) * inv_count.to(m_rows.dtype)
+        return O.linear(z, w["proj_o.weight"], w["proj_o.bias"] if add_bias else None)

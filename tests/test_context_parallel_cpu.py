@@ -97,3 +97,74 @@ def test_cp_trimul_matches_serial_on_gloo(rows, cols, n_tokens):
     errs = dict(q.get(timeout=5) for _ in range(world))
     assert len(errs) == world
     assert max(errs.values()) < 1e-10, errs
+
+
+def _attn_worker(rank, world, rows, cols, port, n, q):
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    torch.set_num_threads(1)
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        from bioemu2_b200.context_parallel import (CPGrid, cp_attention_pair_bias, cp_outer_product_mean,
+                                                   cp_triangle_attention_, shard_range)
+        from cp_cpu_backend import CpuAttentionLocal, Packed
+
+        grid = CPGrid(rows, cols)
+        loc = CpuAttentionLocal()
+        dbl = lambda w: {k: v.double() for k, v in w.items()}  # noqa: E731
+        g = torch.Generator().manual_seed(5)
+        errs = {}
+        # ---- single-track pair-bias attention (B=1, multiplicity 2)
+        w = dbl(H.apb_weights(g, 32, 128, 4))
+        s = torch.randn(2, n, 32, generator=g).double()
+        z = torch.randn(1, n, n, 128, generator=g).double()
+        mask = torch.ones(1, n, dtype=torch.bool)
+        mask[0, n - 3:] = False
+        ref = O.attention_pair_bias(s, z, mask, w, 4, 2)
+        out = cp_attention_pair_bias(grid.shard_single(s), grid.shard_pair(z), grid.shard_single(mask), Packed(w, 4), grid,
+                                     2, local=loc)
+        errs["apb"] = float((out - grid.shard_single(ref)).abs().max())
+        # ---- triangle attention, both nodes
+        wt = dbl(H.triatt_weights(g))
+        pm = torch.rand(1, n, n, generator=g) > 0.2
+        for ending in (False, True):
+            ref = z + O.triangle_attention(z, pm, wt, 4, ending)
+            z_loc = grid.shard_pair(z)[0].clone()
+            cp_triangle_attention_(z_loc, grid.shard_pair(pm)[0], Packed(wt), grid, ending, local=loc)
+            errs[f"triatt_end{int(ending)}"] = float((z_loc - grid.shard_pair(ref)[0]).abs().max())
+        # ---- outer product mean: MSA depth over grid rows, tokens over grid columns
+        wo = dbl(H.opm_weights(g))
+        S = 6 * rows
+        m = torch.randn(1, S, n, 64, generator=g).double()
+        mm = torch.ones(1, S, n, dtype=torch.bool)
+        mm[0, 1] = False
+        mm[0, :, n - 2:] = False
+        ref = O.outer_product_mean(m, mm, wo)
+        s0, s1 = shard_range(S, rows, grid.coords.r)
+        c0, c1 = grid.coords.my_cols(n)
+        row_count = mm.any(-1).sum(1)
+        out = cp_outer_product_mean(m[0, s0:s1, c0:c1].contiguous(), mm[0, s0:s1, c0:c1].contiguous(), row_count,
+                                    Packed(wo), grid, local=loc)
+        errs["opm"] = float((out - grid.shard_pair(ref)[0]).abs().max())
+        q.put((rank, errs))
+    finally:
+        dist.destroy_process_group()
+
+
+@pytest.mark.parametrize("rows,cols,n", [(1, 2, 12), (2, 2, 12), (2, 1, 12)])
+def test_cp_attention_ops_match_serial_on_gloo(rows, cols, n):
+    """Sharded pair-bias attention, triangle attention (both nodes) and outer product mean against the serial oracle
+    (reference's analogous tests: tests/context_parallel/ops/test_attention.py atol 5e-7, test_outer_product_mean.py)."""
+    world = rows * cols
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    port = 31000 + (os.getpid() + rows * 7 + cols * 13 + n) % 2000
+    procs = [ctx.Process(target=_attn_worker, args=(r, world, rows, cols, port, n, q)) for r in range(world)]
+    for p in procs:
+        p.start()
+    for p in procs:
+        p.join(180)
+        assert p.exitcode == 0
+    for _ in range(world):
+        rank, errs = q.get(timeout=5)
+        assert max(errs.values()) < 1e-7, (rank, errs)  # the 1/row_count scale is an fp32 scalar

@@ -86,3 +86,81 @@ def test_cp_grid_matches_serial(rows, cols, n_tokens):
     if torch.cuda.device_count() < rows * cols:
         pytest.skip(f"needs {rows * cols} GPUs")
     _launch(rows, cols, n_tokens)
+
+
+def _run_block_rank(rank, world, rows, cols, port, n, q):
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    os.environ.setdefault("NCCL_NVLS_ENABLE", "0")
+    torch.cuda.set_device(rank)
+    dev = torch.device("cuda", rank)
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=dev)
+    try:
+        import bioemu2_b200 as b
+        from bioemu2_b200.context_parallel import CPGrid, CPOuterProductMean, CPPairformerBlock, shard_range
+
+        torch.manual_seed(21)  # same seed on every rank: replicated weights
+        blk = b.PairformerBlock().eval().to(dev)
+        opm = b.OuterProductMean(64, 32, 128).eval().to(dev)
+        g = torch.Generator().manual_seed(22)
+        z = torch.randn(1, n, n, 128, generator=g)
+        s = torch.randn(1, n, 384, generator=g)
+        tok = torch.ones(1, n, dtype=torch.bool)
+        tok[0, n - 6:] = False
+        S = 16 * rows
+        m = torch.randn(1, S, n, 64, generator=g)
+        mm = torch.ones(1, S, n, dtype=torch.bool)
+        mm[0, 3] = False
+        mm[0, :, n - 6:] = False
+        with torch.no_grad():
+            s_ref, z_ref = blk(s.to(dev), z.to(dev), tok.to(dev))
+            o_ref = opm(m.to(dev), mm.to(dev))
+        grid = CPGrid(rows, cols)
+        cpb = CPPairformerBlock(blk, grid)
+        z_loc, s_loc = grid.shard_pair(z).to(dev), grid.shard_single(s).to(dev)
+        (r0, r1), (c0, c1) = grid.coords.my_rows(n), grid.coords.my_cols(n)
+        with torch.no_grad():
+            s_out, z_out = cpb(s_loc, z_loc, tok[:, r0:r1].to(dev), tok[:, c0:c1].to(dev))
+            s0, s1 = shard_range(S, rows, grid.coords.r)
+            o_out = CPOuterProductMean(opm, grid)(m[:, s0:s1, c0:c1].contiguous().to(dev),
+                                                   mm[:, s0:s1, c0:c1].contiguous().to(dev), mm.any(-1).sum(1).to(dev))
+        torch.cuda.synchronize()
+        pm = (tok[:, r0:r1, None] & tok[:, None, c0:c1])[0].to(dev)
+        rel = lambda a, e, sel: float((a - e)[sel].abs().max() / e.abs().max()) if sel.any() else 0.0  # noqa: E731
+        errs = {
+            "z": rel(z_out[0], z_ref[0, r0:r1, c0:c1], pm),
+            "s": rel(s_out[0], s_ref[0, r0:r1], tok[0, r0:r1].to(dev)),
+            "opm": rel(o_out[0], o_ref[0, r0:r1, c0:c1], pm),
+        }
+        q.put((rank, errs, b._lib.device_status()))
+    finally:
+        dist.destroy_process_group()
+
+
+def _launch_block(rows, cols, n):
+    world = rows * cols
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    port = 30200 + (os.getpid() + rows * 31 + cols * 17 + n) % 1500
+    procs = [ctx.Process(target=_run_block_rank, args=(r, world, rows, cols, port, n, q)) for r in range(world)]
+    for p in procs:
+        p.start()
+    for p in procs:
+        p.join(300)
+        assert p.exitcode == 0
+    for _ in range(world):
+        rank, errs, status = q.get(timeout=5)
+        assert status == 0, f"rank {rank}: device status {status:#x}"
+        # sharded vs single-GPU: same kernels on differently shaped slabs; bf16 roundings fall at other places
+        assert max(errs.values()) < 1e-2, (rank, errs)
+
+
+def test_cp_pairformer_block_and_opm_1x1():
+    _launch_block(1, 1, 136)
+
+
+@pytest.mark.parametrize("rows,cols,n", [(1, 2, 144), (2, 2, 272), (2, 4, 320)])
+def test_cp_pairformer_block_and_opm_grid(rows, cols, n):
+    if torch.cuda.device_count() < rows * cols:
+        pytest.skip(f"needs {rows * cols} GPUs")
+    _launch_block(rows, cols, n)
