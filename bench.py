@@ -50,6 +50,8 @@ def parse_args():
                          "pair transition, single-track pair-bias attention, single transition); "
                          "pairmixer: the reference trunk's own block (no attention)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-graph", action="store_true",
+                    help="launch the kernels of the HBM-resident step one by one instead of replaying a CUDA graph")
     ap.add_argument("--cp", default=None, metavar="RxC",
                     help="context-parallel mode: ONE pair tensor tiled over an RxC grid of the --gpus ranks (strong "
                          "scaling) running the PairMixer blocks; the default without --cp is independent replicas")
@@ -121,6 +123,7 @@ def config_dict(args, impl_note: str) -> dict:
         "z_stream": "fp32",
         "arithmetic": "bf16 tensor cores, fp32 accumulate",
         "cache": "inputs larger than L2: z is 134 MB fp32 at N=512 and every kernel streams >=200 MB of scratch",
+        "launch": "eager" if args.no_graph else "CUDA graph replay of the step (value); eager launches (e2e)",
         "parallelism": f"{args.gpus} independent replicas" if args.gpus > 1 else "single GPU",
         "note": impl_note,
     }
@@ -344,7 +347,24 @@ def run_b200(args) -> None:
         for _ in range(max(args.warmup, 3)):
             step_resident()
         barrier()
-        ms = event_time_ms(step_resident, args.steps)
+        timed_step = step_resident
+        graphed = False
+        if not args.no_graph:
+            # The step is a fixed sequence of ~1200 launches on fixed buffers: capture it once, replay it per step.
+            try:
+                graph = torch.cuda.CUDAGraph()
+                with torch.cuda.graph(graph):
+                    step_resident()
+                graph.replay()
+                torch.cuda.synchronize()
+                timed_step, graphed = graph.replay, True
+            except Exception as exc:  # keep the eager path if capture is refused
+                print(f"CUDA graph capture failed ({exc}); timing eager launches", file=sys.stderr)
+                torch.cuda.synchronize()
+        for _ in range(3 if graphed else 0):
+            timed_step()
+        barrier()
+        ms = event_time_ms(timed_step, args.steps)
         barrier()
 
         step_e2e()
@@ -467,9 +487,23 @@ def run_cp(args) -> None:
     if N % kernel_shard_multiple(rows, cols):
         raise SystemExit(f"--tokens must be a multiple of {kernel_shard_multiple(rows, cols)} for a {args.cp} grid")
     grid = CPGrid(rows, cols)
-    torch.manual_seed(2)
-    serial = b.PairMixerModule(384, 128, args.blocks).eval().to(dev)  # same seed on every rank: replicated weights
-    cp = CPPairMixerModule(serial, grid)
+    torch.manual_seed(2)  # same seed on every rank: replicated weights
+    tri = args.block == "pairformer"  # BASELINE config 3: triangle multiplication out/in + triangle attention start/end
+    if tri:
+        from bioemu2_b200.context_parallel import CPTriangleAttention, CPTriangleMultiplication
+
+        blocks = [b.PairformerBlock().eval().to(dev) for _ in range(args.blocks)]
+        ops = []
+        for blk in blocks:
+            ops += [CPTriangleMultiplication(blk.tri_mul_out, grid), CPTriangleMultiplication(blk.tri_mul_in, grid),
+                    CPTriangleAttention(blk.tri_att_start, grid), CPTriangleAttention(blk.tri_att_end, grid)]
+
+        def cp(zz, mm):
+            for op in ops:
+                op(zz, mm)
+    else:
+        serial = b.PairMixerModule(384, 128, args.blocks).eval().to(dev)
+        cp = CPPairMixerModule(serial, grid)
     (r0, r1), (c0, c1) = grid.coords.my_rows(N), grid.coords.my_cols(N)
     g = torch.Generator(device=dev).manual_seed(100 + rank)
     z0 = torch.randn(1, r1 - r0, c1 - c0, 128, device=dev, generator=g)
@@ -498,11 +532,13 @@ def run_cp(args) -> None:
     ms = float(tt[0])
     if rank == 0:
         fl = block_flops(N, "pairmixer")
+        if tri:
+            fl["block"] = 2 * fl["trimul"] + 2 * block_flops(N, "pairformer")["triatt"]
         line = {
             "metric": METRIC, "value": N * N / (ms * 1e-3), "unit": UNIT, "n_gpus": world, "steps": args.steps,
             "warmup": max(args.warmup, 3), "ms_per_step": ms, "higher_is_better": True, "scaling": "strong",
             "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
-            "config": {"workload": f"context-parallel PairMixer trunk, {args.blocks} blocks, N={N}, one pair tensor tiled "
+            "config": {"workload": f"context-parallel {'triangle multiplication out/in + triangle attention start/end' if tri else 'PairMixer trunk'}, {args.blocks} blocks, N={N}, one pair tensor tiled "
                                    f"{rows}x{cols} (block {r1 - r0}x{c1 - c0}), full mask", "grid": args.cp, "tokens": N,
                        "blocks": args.blocks, "z_stream": "fp32",
                        "exchange": "all-gather of the b operand + fp32 reduce-scatter of partial sums per direction (NCCL)"},
