@@ -149,40 +149,58 @@ bmm_nt_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ C
       const float scale = p.scale_ptr ? p.scale * p.scale_ptr[b] : p.scale;
       const size_t esz = p.out_f32 ? 4 : 2;
       uint8_t* cbase = static_cast<uint8_t*>(p.C) + (long long)b * p.c_batch_stride * esz;
-#pragma unroll 1
+      // 32 columns at a time; the next chunk's TMEM load and (when a residual is added) its residual row
+      // segment are requested before the current chunk is processed.
+      const uint8_t* rbase = p.residual ? static_cast<const uint8_t*>(p.residual) + (long long)b * p.c_batch_stride * esz
+                                        : nullptr;
+      auto chunk_off = [&](int c) -> long long {  // element offset of (row, first column of chunk c)
+        const int col0 = tn * BN + c * 32;
+        if (p.opm_ntok > 0) return (((long long)(row >> 5) * p.opm_ntok + (col0 >> 5)) * 32 + (row & 31)) * 32;
+        if (p.remap_n > 0) return ((long long)(row % p.remap_n) * p.remap_m + row / p.remap_n) * p.ldc + col0;
+        return (long long)row * p.ldc + col0;
+      };
+      auto load_res = [&](int c, float (&rz)[32]) {
+        const long long off0 = chunk_off(c);
+#pragma unroll
+        for (int g = 0; g < 4; ++g) {
+          float t8[8];
+          const bool ok = rbase && row < p.m_valid && (tn * BN + c * 32 + g * 8) < p.n_valid;
+          if (ok) {
+            if (p.out_f32)
+              load8<true>(rbase + (off0 + g * 8) * 4, 0, t8);
+            else
+              load8<false>(rbase + (off0 + g * 8) * 2, 0, t8);
+          }
+#pragma unroll
+          for (int e = 0; e < 8; ++e) rz[g * 8 + e] = ok ? t8[e] : 0.f;
+        }
+      };
+      uint32_t va[32], vb[32];
+      float ra[32], rb[32];
+      tmem_ld_32x32(tmem_addr(tmem_base, quarter * 32, acc * BN), va);
+      load_res(0, ra);
+#pragma unroll
       for (int c = 0; c < BN / 32; ++c) {
-        uint32_t v[32];
-        tmem_ld_32x32(tmem_addr(tmem_base, quarter * 32, acc * BN + c * 32), v);
+        uint32_t(&v)[32] = (c & 1) ? vb : va;
+        float(&rz)[32] = (c & 1) ? rb : ra;
         tmem_ld_wait();
+        if (c + 1 < BN / 32) {
+          tmem_ld_32x32(tmem_addr(tmem_base, quarter * 32, acc * BN + (c + 1) * 32), (c & 1) ? va : vb);
+          load_res(c + 1, (c & 1) ? ra : rb);
+        }
         if (row < p.m_valid) {
           const int col0 = tn * BN + c * 32;
-          long long off0;  // element offset of (row, col0)
-          if (p.opm_ntok > 0)
-            off0 = (((long long)(row >> 5) * p.opm_ntok + (col0 >> 5)) * 32 + (row & 31)) * 32;
-          else if (p.remap_n > 0)
-            off0 = ((long long)(row % p.remap_n) * p.remap_m + row / p.remap_n) * p.ldc + col0;
-          else
-            off0 = (long long)row * p.ldc + col0;
+          const long long off0 = chunk_off(c);
 #pragma unroll
           for (int g = 0; g < 4; ++g) {
             const int col = col0 + g * 8;
             if (col < p.n_valid) {
               float x[8];
 #pragma unroll
-              for (int e = 0; e < 8; ++e) x[e] = __uint_as_float(v[g * 8 + e]) * scale;
+              for (int e = 0; e < 8; ++e) x[e] = fmaf(__uint_as_float(v[g * 8 + e]), scale, rz[g * 8 + e]);
               if (p.bias) {
 #pragma unroll
                 for (int e = 0; e < 8; ++e) x[e] += p.bias[col + e];
-              }
-              if (p.residual) {
-                float rz[8];
-                const uint8_t* rb = static_cast<const uint8_t*>(p.residual) + (long long)b * p.c_batch_stride * esz;
-                if (p.out_f32)
-                  load8<true>(rb + (off0 + g * 8) * 4, 0, rz);
-                else
-                  load8<false>(rb + (off0 + g * 8) * 2, 0, rz);
-#pragma unroll
-                for (int e = 0; e < 8; ++e) x[e] += rz[e];
               }
               if (p.out_f32)
                 store8<true>(cbase + (off0 + g * 8) * 4, 0, x);

@@ -283,6 +283,14 @@ static int launch_trimul_project(const void* z, const uint8_t* mask, __nv_bfloat
   const uint64_t str[1] = {256};
   const uint32_t box[2] = {64, 128};
   if (int e = make_tmap_bf16(&tmWin, w->w_in, 2, dims, str, box, CU_TENSOR_MAP_SWIZZLE_128B)) return e;
+  CUtensorMap tmA, tmB;  // channel-major a/b planes, stored as [128 channels][64 pairs] boxes of one line
+  {
+    const uint64_t dims[3] = {uint64_t(g.pos_pitch), uint64_t(g.lines_alloc), uint64_t(kD)};
+    const uint64_t str[2] = {uint64_t(g.pos_pitch) * 2, uint64_t(g.pos_pitch) * g.lines_alloc * 2};
+    const uint32_t box[3] = {64, 1, 128};
+    if (int e = make_tmap_bf16(&tmA, a_buf, 3, dims, str, box, CU_TENSOR_MAP_SWIZZLE_128B)) return e;
+    if (int e = make_tmap_bf16(&tmB, b_buf, 3, dims, str, box, CU_TENSOR_MAP_SWIZZLE_128B)) return e;
+  }
   if (int e = set_smem(trimul_in_kernel<true>, trimul_in::SMEM_BYTES)) return e;
   if (int e = set_smem(trimul_in_kernel<false>, trimul_in::SMEM_BYTES)) return e;
   TriMulInParams pi;
@@ -304,9 +312,9 @@ static int launch_trimul_project(const void* z, const uint8_t* mask, __nv_bfloat
   pi.eps = 1e-5f;
   const int grid = pi.num_tiles < sm_count() ? pi.num_tiles : sm_count();
   if (f32)
-    trimul_in_kernel<true><<<grid, trimul_in::THREADS, trimul_in::SMEM_BYTES, stream>>>(tmWin, pi);
+    trimul_in_kernel<true><<<grid, trimul_in::THREADS, trimul_in::SMEM_BYTES, stream>>>(tmWin, tmA, tmB, pi);
   else
-    trimul_in_kernel<false><<<grid, trimul_in::THREADS, trimul_in::SMEM_BYTES, stream>>>(tmWin, pi);
+    trimul_in_kernel<false><<<grid, trimul_in::THREADS, trimul_in::SMEM_BYTES, stream>>>(tmWin, tmA, tmB, pi);
   B200_CUDA(cudaGetLastError());
   return 0;
 }
@@ -326,6 +334,19 @@ static int launch_trimul_output(const void* z, void* out, const __nv_bfloat16* t
     const uint32_t box[3] = {128, 1, 128};
     if (int e = make_tmap_bf16(&tmT, t_buf, 3, dims, str, box, CU_TENSOR_MAP_SWIZZLE_NONE)) return e;
   }
+  // Output tiles [128 pairs][128 B of channels]; the dimension with the smaller stride comes first.
+  CUtensorMap tmO;
+  const bool pos_first = g.z_pos_stride <= g.z_line_stride;
+  {
+    const uint64_t np = uint64_t(g.n_pos), nl = uint64_t(g.n_lines);
+    const uint64_t dims[3] = {uint64_t(kD), pos_first ? np : nl, pos_first ? nl : np};
+    const uint64_t str[2] = {uint64_t(pos_first ? g.z_pos_stride : g.z_line_stride),
+                             uint64_t(pos_first ? g.z_line_stride : g.z_pos_stride)};
+    const uint32_t box[3] = {f32 ? 32u : 64u, pos_first ? 128u : 1u, pos_first ? 1u : 128u};
+    if (int e = make_tmap(&tmO, f32 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, out, 3, dims,
+                          str, box, CU_TENSOR_MAP_SWIZZLE_128B))
+      return e;
+  }
   if (int e = set_smem(trimul_out_kernel<true>, trimul_out::SMEM_BYTES)) return e;
   if (int e = set_smem(trimul_out_kernel<false>, trimul_out::SMEM_BYTES)) return e;
   TriMulOutParams po;
@@ -340,14 +361,15 @@ static int launch_trimul_output(const void* z, void* out, const __nv_bfloat16* t
   po.pos_pitch = g.pos_pitch;
   po.z_line_stride = g.z_line_stride;
   po.z_pos_stride = g.z_pos_stride;
+  po.pos_is_dim1 = pos_first ? 1 : 0;
   po.num_tiles = g.n_lines * (g.pos_pitch / 128);
   po.add_residual = add_residual ? 1 : 0;
   po.eps = 1e-5f;
   const int grid = po.num_tiles < sm_count() ? po.num_tiles : sm_count();
   if (f32)
-    trimul_out_kernel<true><<<grid, trimul_out::THREADS, trimul_out::SMEM_BYTES, stream>>>(tmWout, tmT, po);
+    trimul_out_kernel<true><<<grid, trimul_out::THREADS, trimul_out::SMEM_BYTES, stream>>>(tmWout, tmT, tmO, po);
   else
-    trimul_out_kernel<false><<<grid, trimul_out::THREADS, trimul_out::SMEM_BYTES, stream>>>(tmWout, tmT, po);
+    trimul_out_kernel<false><<<grid, trimul_out::THREADS, trimul_out::SMEM_BYTES, stream>>>(tmWout, tmT, tmO, po);
   B200_CUDA(cudaGetLastError());
   return 0;
 }

@@ -120,13 +120,14 @@ struct RowTile {
   }
 };
 
+// scale multiplies the LayerNorm output; a power of two keeps the result a bit-exact multiple.
 __device__ __forceinline__ void load_gamma_beta(const float* w, const float* b, int pt, float (&gamma)[8],
-                                                float (&beta)[8]) {
+                                                float (&beta)[8], float scale = 1.0f) {
   const int c0 = (pt & 15) * 8;
 #pragma unroll
   for (int i = 0; i < 8; ++i) {
-    gamma[i] = w ? w[c0 + i] : 1.0f;
-    beta[i] = b ? b[c0 + i] : 0.0f;
+    gamma[i] = (w ? w[c0 + i] : 1.0f) * scale;
+    beta[i] = (b ? b[c0 + i] : 0.0f) * scale;
   }
 }
 

@@ -136,59 +136,56 @@ triatt_proj_kernel(const __grid_constant__ CUtensorMap tmW, TriAttProjParams p) 
       const int pos0 = (tile - line * tiles_per_line) << 7;
       const bool valid = (pos0 + r) < p.n_pos;
       __nv_bfloat16* row = p.qkg + ((long long)line * p.n_pos + pos0 + r) * 384;
+      // Both groups are read 32 columns at a time with the next chunk's TMEM load already in flight.
+      uint32_t va[32], vb[32];
+      auto pack8 = [](const uint32_t* v) {
+        return make_uint4(pack_bf16x2(__uint_as_float(v[0]), __uint_as_float(v[1])),
+                          pack_bf16x2(__uint_as_float(v[2]), __uint_as_float(v[3])),
+                          pack_bf16x2(__uint_as_float(v[4]), __uint_as_float(v[5])),
+                          pack_bf16x2(__uint_as_float(v[6]), __uint_as_float(v[7])));
+      };
       // ---- group A: q, k
       mbar_wait(&acc_full[0], it & 1, 95);
       tc_fence_after_sync();
-#pragma unroll 1
+      tmem_ld_32x32(tmem_addr(tmem_base, warp * 32, 0), va);
+#pragma unroll
       for (int c = 0; c < 8; ++c) {
-        uint32_t v[32];
-        tmem_ld_32x32(tmem_addr(tmem_base, warp * 32, c * 32), v);
+        uint32_t(&v)[32] = (c & 1) ? vb : va;
         tmem_ld_wait();
+        if (c < 7) tmem_ld_32x32(tmem_addr(tmem_base, warp * 32, (c + 1) * 32), (c & 1) ? va : vb);
         if (valid) {
 #pragma unroll
-          for (int g = 0; g < 4; ++g)
-            *reinterpret_cast<uint4*>(row + c * 32 + g * 8) = make_uint4(
-                pack_bf16x2(__uint_as_float(v[g * 8 + 0]), __uint_as_float(v[g * 8 + 1])),
-                pack_bf16x2(__uint_as_float(v[g * 8 + 2]), __uint_as_float(v[g * 8 + 3])),
-                pack_bf16x2(__uint_as_float(v[g * 8 + 4]), __uint_as_float(v[g * 8 + 5])),
-                pack_bf16x2(__uint_as_float(v[g * 8 + 6]), __uint_as_float(v[g * 8 + 7])));
+          for (int g = 0; g < 4; ++g) *reinterpret_cast<uint4*>(row + c * 32 + g * 8) = pack8(&v[g * 8]);
         }
       }
       tc_fence_before_sync();
       mbar_arrive(&acc_empty[0]);
-      // ---- group B: g (+ bias), V^T
+      // ---- group B: g (+ bias) in columns 256..383, V^T in 384..511
+      __nv_bfloat16* vrow = p.vT + ((long long)line * kD + r) * p.Nk + pos0;
       mbar_wait(&acc_full[1], it & 1, 96);
       tc_fence_after_sync();
-#pragma unroll 1
-      for (int c = 0; c < 4; ++c) {
-        uint32_t v[32];
-        tmem_ld_32x32(tmem_addr(tmem_base, warp * 32, 256 + c * 32), v);
+      tmem_ld_32x32(tmem_addr(tmem_base, warp * 32, 256), va);
+#pragma unroll
+      for (int c = 0; c < 8; ++c) {
+        uint32_t(&v)[32] = (c & 1) ? vb : va;
         tmem_ld_wait();
-        if (valid) {
+        if (c < 7) tmem_ld_32x32(tmem_addr(tmem_base, warp * 32, 256 + (c + 1) * 32), (c & 1) ? va : vb);
+        if (c < 4) {
+          if (valid) {
 #pragma unroll
-          for (int g = 0; g < 4; ++g) {
-            float y[8];
+            for (int g = 0; g < 4; ++g) {
+              float y[8];
 #pragma unroll
-            for (int e = 0; e < 8; ++e) y[e] = __uint_as_float(v[g * 8 + e]) + gb_s[c * 32 + g * 8 + e];
-            *reinterpret_cast<uint4*>(row + 256 + c * 32 + g * 8) = make_uint4(
-                pack_bf16x2(y[0], y[1]), pack_bf16x2(y[2], y[3]), pack_bf16x2(y[4], y[5]), pack_bf16x2(y[6], y[7]));
+              for (int e = 0; e < 8; ++e) y[e] = __uint_as_float(v[g * 8 + e]) + gb_s[c * 32 + g * 8 + e];
+              *reinterpret_cast<uint4*>(row + 256 + c * 32 + g * 8) = make_uint4(
+                  pack_bf16x2(y[0], y[1]), pack_bf16x2(y[2], y[3]), pack_bf16x2(y[4], y[5]), pack_bf16x2(y[6], y[7]));
+            }
           }
-        }
-      }
-      __nv_bfloat16* vrow = p.vT + ((long long)line * kD + r) * p.Nk + pos0;
-#pragma unroll 1
-      for (int c = 0; c < 4; ++c) {
-        uint32_t v[32];
-        tmem_ld_32x32(tmem_addr(tmem_base, warp * 32, 384 + c * 32), v);
-        tmem_ld_wait();
+        } else {
 #pragma unroll
-        for (int g = 0; g < 4; ++g) {
-          if (pos0 + c * 32 + g * 8 < p.n_pos)
-            *reinterpret_cast<uint4*>(vrow + c * 32 + g * 8) = make_uint4(
-                pack_bf16x2(__uint_as_float(v[g * 8 + 0]), __uint_as_float(v[g * 8 + 1])),
-                pack_bf16x2(__uint_as_float(v[g * 8 + 2]), __uint_as_float(v[g * 8 + 3])),
-                pack_bf16x2(__uint_as_float(v[g * 8 + 4]), __uint_as_float(v[g * 8 + 5])),
-                pack_bf16x2(__uint_as_float(v[g * 8 + 6]), __uint_as_float(v[g * 8 + 7])));
+          for (int g = 0; g < 4; ++g)
+            if (pos0 + (c - 4) * 32 + g * 8 < p.n_pos)
+              *reinterpret_cast<uint4*>(vrow + (c - 4) * 32 + g * 8) = pack8(&v[g * 8]);
         }
       }
       tc_fence_before_sync();

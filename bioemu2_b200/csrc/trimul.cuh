@@ -40,13 +40,18 @@ constexpr uint32_t W_OFF = 0;                       // 4 M-tiles x 32 KB
 constexpr uint32_t X_OFF = 4 * kOperandTile;        // 2 stages x 32 KB
 constexpr uint32_t MASK_OFF = X_OFF + 2 * kOperandTile;  // 4 stages x 128 B
 constexpr uint32_t BAR_OFF = MASK_OFF + 4 * 128;
-constexpr uint32_t SMEM_BYTES = BAR_OFF + 128 + 1024;
-constexpr int THREADS = 416;  // warps 0-3 epilogue, 4-11 producers, 12 control
+constexpr uint32_t FLAG_OFF = BAR_OFF + 96;          // 4 stages x 4 "every pair of this quarter valid" bytes
+constexpr uint32_t STAGE_OFF = MASK_OFF + 1024;      // per epilogue group a 16 KB tile [128 channels][64 pairs]
+constexpr uint32_t SMEM_BYTES = STAGE_OFF + 2 * kOperandHalf + 1024;
+constexpr int THREADS = 544;  // warps 0-3 epilogue of a, 4-7 epilogue of b, 8-15 producers, 16 control
 }  // namespace trimul_in
 
+// The LayerNorm output is halved (exactly) before the projections, so the accumulators hold p/2 and g/2
+// and the gate is p * sigmoid(g) = p/2 + p/2 * tanh(g/2): one MUFU and one FMA per element.
 template <bool F32>
-__global__ void __launch_bounds__(416, 1)
-trimul_in_kernel(const __grid_constant__ CUtensorMap tmW, TriMulInParams p) {
+__global__ void __launch_bounds__(544, 1)
+trimul_in_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUtensorMap tmA,
+                 const __grid_constant__ CUtensorMap tmB, TriMulInParams p) {
   using namespace trimul_in;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
@@ -57,6 +62,7 @@ trimul_in_kernel(const __grid_constant__ CUtensorMap tmW, TriMulInParams p) {
   uint64_t* acc_empty = acc_full + 2;
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_empty + 2);
   uint8_t* mask_s = smem + MASK_OFF;
+  uint8_t* flag_s = smem + FLAG_OFF;
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
@@ -72,14 +78,16 @@ trimul_in_kernel(const __grid_constant__ CUtensorMap tmW, TriMulInParams p) {
     }
     fence_mbar_init();
     prefetch_tmap(&tmW);
+    prefetch_tmap(&tmA);
+    prefetch_tmap(&tmB);
   }
-  if (warp == 12) tmem_alloc(tmem_slot, 512);
+  if (warp == 16) tmem_alloc(tmem_slot, 512);
   tc_fence_before_sync();
   __syncthreads();
   tc_fence_after_sync();
   const uint32_t tmem_base = *tmem_slot;
 
-  if (warp == 12) {
+  if (warp == 16) {
     // ------------------------------------------------------------------ control
     if (lane == 0) {
       mbar_arrive_expect_tx(w_full, 4 * kOperandTile);
@@ -107,11 +115,11 @@ trimul_in_kernel(const __grid_constant__ CUtensorMap tmW, TriMulInParams p) {
         umma_commit(&x_empty[s]);
       }
     }
-  } else if (warp >= 4) {
+  } else if (warp >= 8) {
     // ------------------------------------------------------------------ producers
-    const int pt = threadIdx.x - 128;  // 0..255
+    const int pt = threadIdx.x - 256;  // 0..255
     float gamma[8], beta[8];
-    load_gamma_beta(p.ln_w, p.ln_b, pt, gamma, beta);
+    load_gamma_beta(p.ln_w, p.ln_b, pt, gamma, beta, 0.5f);
     const long long pos_stride = p.z_pos_stride, line_stride = p.z_line_stride;
     const long long mpos_stride = p.m_pos_stride, mline_stride = p.m_line_stride;
     RowTile<256> regs;
@@ -139,7 +147,11 @@ trimul_in_kernel(const __grid_constant__ CUtensorMap tmW, TriMulInParams p) {
       const int s = it & 1;
       mbar_wait(&x_empty[s], ((it >> 1) & 1) ^ 1, 13);
       regs.store_operand(pt, smem + X_OFF + s * kOperandTile);
-      if (pt < 128) mask_s[(it & 3) * 128 + pt] = mreg;
+      if (pt < 128) {
+        mask_s[(it & 3) * 128 + pt] = mreg;
+        const bool quarter_valid = __all_sync(0xffffffffu, mreg != 0);
+        if (lane == 0) flag_s[(it & 3) * 4 + (pt >> 5)] = quarter_valid ? 1 : 0;
+      }
       fence_proxy_async_smem();
       mbar_arrive(&x_full[s]);
       const int next = tile + gridDim.x;
@@ -147,46 +159,76 @@ trimul_in_kernel(const __grid_constant__ CUtensorMap tmW, TriMulInParams p) {
     }
   } else {
     // ------------------------------------------------------------------ epilogue
-    const int d = warp * 32 + lane;  // channel inside the half == TMEM lane
+    // Group 0 (warps 0-3) gates and stores the a half, group 1 (warps 4-7) the b half, concurrently.  Lane =
+    // channel, columns = pairs; 16 columns at a time with the next chunk's TMEM loads in flight.  The gated
+    // values go to the group's swizzled [128 channels][64 pairs] staging tile and leave by TMA store (a row
+    // per channel of the channel-major plane).
+    const int half = warp >> 2;
+    const int d = (warp & 3) * 32 + lane;  // channel inside the half == TMEM lane
+    uint8_t* stage = smem + STAGE_OFF + half * kOperandHalf;
+    const CUtensorMap* tmOut = half ? &tmB : &tmA;
+    const uint32_t p_addr = tmem_addr(tmem_base, (warp & 3) * 32, (half * 2) * 128);
+    const uint32_t g_addr = p_addr + 128;
     int it = 0;
     for (int tile = blockIdx.x; tile < p.num_tiles; tile += gridDim.x, ++it) {
       const int line = tile / tiles_per_line;
       const int pos0 = (tile - line * tiles_per_line) << 7;
       const uint32_t* msk = reinterpret_cast<const uint32_t*>(mask_s + (it & 3) * 128);
-      for (int half = 0; half < 2; ++half) {
-        mbar_wait(&acc_full[half], it & 1, 14);
-        tc_fence_after_sync();
-        __nv_bfloat16* dst = (half ? p.b_out : p.a_out) + ((long long)d * p.lines_alloc + line) * p.pos_pitch + pos0;
-#pragma unroll 1
-        for (int c = 0; c < 4; ++c) {
-          uint32_t pv[32], gv[32];
-          tmem_ld_32x32(tmem_addr(tmem_base, warp * 32, (half * 2) * 128 + c * 32), pv);
-          tmem_ld_32x32(tmem_addr(tmem_base, warp * 32, (half * 2 + 1) * 128 + c * 32), gv);
-          tmem_ld_wait();
-          uint32_t packed[16];
+      mbar_wait(&acc_full[half], it & 1, 14);
+      tc_fence_after_sync();
+      // every pair of the tile unmasked?  (tiles away from the padding are, and then no select is needed)
+      const bool all_valid = *reinterpret_cast<const uint32_t*>(flag_s + (it & 3) * 4) == 0x01010101u;
+      uint32_t pa[16], ga[16], pb[16], gb[16];
+      tmem_ld_32x16(p_addr, pa);
+      tmem_ld_32x16(g_addr, ga);
 #pragma unroll
-          for (int j = 0; j < 32; j += 2) {
-            const uint32_t m4 = msk[(c * 32 + j) >> 2];
-            const bool m0 = (m4 >> (((j)&3) * 8)) & 0xff;
-            const bool m1 = (m4 >> (((j + 1) & 3) * 8)) & 0xff;
-            const float v0 = m0 ? __uint_as_float(pv[j]) * sigmoid_fast(__uint_as_float(gv[j])) : 0.f;
-            const float v1 = m1 ? __uint_as_float(pv[j + 1]) * sigmoid_fast(__uint_as_float(gv[j + 1])) : 0.f;
-            packed[j >> 1] = pack_bf16x2(v0, v1);
-          }
-#pragma unroll
-          for (int g = 0; g < 4; ++g)
-            *reinterpret_cast<uint4*>(dst + c * 32 + g * 8) =
-                make_uint4(packed[g * 4], packed[g * 4 + 1], packed[g * 4 + 2], packed[g * 4 + 3]);
+      for (int c = 0; c < 8; ++c) {
+        if ((c & 3) == 0) {  // the previous store has finished reading the staging tile
+          if (d == 0) tma_store_wait_read0();
+          named_bar_sync(1 + half, 128);
         }
-        tc_fence_before_sync();
-        mbar_arrive(&acc_empty[half]);
+        uint32_t(&pv)[16] = (c & 1) ? pb : pa;
+        uint32_t(&gv)[16] = (c & 1) ? gb : ga;
+        tmem_ld_wait();
+        if (c < 7) {
+          tmem_ld_32x16(p_addr + (c + 1) * 16, (c & 1) ? pa : pb);
+          tmem_ld_32x16(g_addr + (c + 1) * 16, (c & 1) ? ga : gb);
+        } else {
+          tc_fence_before_sync();
+          mbar_arrive(&acc_empty[half]);
+        }
+        uint32_t packed[8];
+#pragma unroll
+        for (int j = 0; j < 16; j += 2) {
+          const float h0 = __uint_as_float(pv[j]), h1 = __uint_as_float(pv[j + 1]);
+          float v0 = fmaf(h0, tanh_approx(__uint_as_float(gv[j])), h0);
+          float v1 = fmaf(h1, tanh_approx(__uint_as_float(gv[j + 1])), h1);
+          if (!all_valid) {
+            const uint32_t m4 = msk[(c * 16 + j) >> 2];
+            v0 = ((m4 >> ((j & 3) * 8)) & 0xff) ? v0 : 0.f;
+            v1 = ((m4 >> (((j + 1) & 3) * 8)) & 0xff) ? v1 : 0.f;
+          }
+          packed[j >> 1] = pack_bf16x2(v0, v1);
+        }
+        *reinterpret_cast<uint4*>(stage + sw128_offset(d, (c & 3) * 2)) = make_uint4(packed[0], packed[1], packed[2], packed[3]);
+        *reinterpret_cast<uint4*>(stage + sw128_offset(d, (c & 3) * 2 + 1)) =
+            make_uint4(packed[4], packed[5], packed[6], packed[7]);
+        if ((c & 3) == 3) {
+          fence_proxy_async_smem();
+          named_bar_sync(1 + half, 128);
+          if (d == 0) {
+            tma_store_3d(tmOut, stage, pos0 + (c >> 2) * 64, line, 0);
+            tma_store_commit();
+          }
+        }
       }
     }
+    if (d == 0) tma_store_wait0();
   }
 
   tc_fence_before_sync();
   __syncthreads();
-  if (warp == 12) {
+  if (warp == 16) {
     __syncwarp();
     tmem_dealloc(tmem_base, 512);
   }
@@ -207,6 +249,7 @@ struct TriMulOutParams {
   long long z_line_stride, z_pos_stride;
   int num_tiles;           // n_lines * pos_pitch/128
   int add_residual;
+  int pos_is_dim1;         // the output tensor map is {channel, pos, line} (1) or {channel, line, pos} (0)
   float eps;
 };
 
@@ -217,14 +260,15 @@ constexpr uint32_t A1_OFF = T_OFF + 2 * kOperandTile;  // LN_out(t) operand
 constexpr uint32_t A2_OFF = A1_OFF + kOperandTile;     // LN_in(z) operand
 constexpr uint32_t LN_OFF = A2_OFF + kOperandTile;     // gamma_out[128], beta_out[128] fp32
 constexpr uint32_t BAR_OFF = LN_OFF + 1024;
-constexpr uint32_t SMEM_BYTES = BAR_OFF + 128 + 1024;
+constexpr uint32_t STAGE_OFF = LN_OFF + 2048;          // 2 x 16 KB output tiles [128 pairs][128 B of channels]
+constexpr uint32_t SMEM_BYTES = STAGE_OFF + 2 * kOperandHalf + 1024;
 constexpr int THREADS = 544;  // warps 0-3 epilogue, 4-7 t transformers, 8-15 z producers, 16 control
 }  // namespace trimul_out
 
 template <bool F32>
 __global__ void __launch_bounds__(544, 1)
 trimul_out_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUtensorMap tmT,
-                  TriMulOutParams p) {
+                  const __grid_constant__ CUtensorMap tmO, TriMulOutParams p) {
   using namespace trimul_out;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
@@ -257,6 +301,7 @@ trimul_out_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant
     fence_mbar_init();
     prefetch_tmap(&tmW);
     prefetch_tmap(&tmT);
+    prefetch_tmap(&tmO);
   }
   if (threadIdx.x < 128) {
     ln_s[threadIdx.x] = p.ln_out_w[threadIdx.x];
@@ -376,44 +421,82 @@ trimul_out_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant
     }
   } else {
     // ------------------------------------------------------------------ epilogue
-    const int r = warp * 32 + lane;  // pair row of the tile == TMEM lane
+    // Lane = pair, columns = channels.  16 channels at a time with the next chunk's TMEM loads in flight; the
+    // gated update goes to a swizzled [128 pairs][128 B] staging tile and leaves by TMA, two tiles in
+    // rotation: added into z in place when the residual is wanted and out aliases z (a bulk reduce, so z is
+    // not read here), stored otherwise (with the residual added here from global memory if it is wanted).
+    constexpr int CPS = F32 ? 2 : 4;  // 16-channel chunks per staging tile (128 B of channels per pair)
+    const int r = warp * 32 + lane;   // pair row of the tile == TMEM lane
+    const bool reduce = p.add_residual && p.out == p.z;
+    const bool read_res = p.add_residual && !reduce;
     int it = 0;
     for (int tile = blockIdx.x; tile < p.num_tiles; tile += gridDim.x, ++it) {
       const int line = tile / tiles_per_line;
       const int pos0 = (tile - line * tiles_per_line) << 7;
       const int acc = it & 1;
       const bool valid = (pos0 + r) < p.n_pos;
-      const long long off = line * p.z_line_stride + (pos0 + r) * p.z_pos_stride;
-      const uint8_t* zrow = static_cast<const uint8_t*>(p.z) + off;
-      uint8_t* orow = static_cast<uint8_t*>(p.out) + off;
+      const uint8_t* zrow = static_cast<const uint8_t*>(p.z) + line * p.z_line_stride + (pos0 + r) * p.z_pos_stride;
       mbar_wait(&acc_full[acc], (it >> 1) & 1, 28);
       tc_fence_after_sync();
-#pragma unroll 1
-      for (int c = 0; c < 4; ++c) {
-        uint32_t pv[32], gv[32];
-        tmem_ld_32x32(tmem_addr(tmem_base, warp * 32, acc * 256 + c * 32), pv);
-        tmem_ld_32x32(tmem_addr(tmem_base, warp * 32, acc * 256 + 128 + c * 32), gv);
+      const uint32_t p_addr = tmem_addr(tmem_base, warp * 32, acc * 256);
+      const uint32_t g_addr = p_addr + 128;
+      uint32_t pa[16], ga[16], pb[16], gb[16];
+      tmem_ld_32x16(p_addr, pa);
+      tmem_ld_32x16(g_addr, ga);
+#pragma unroll
+      for (int c = 0; c < 8; ++c) {
+        uint8_t* stage = smem + STAGE_OFF + ((c / CPS) & 1) * kOperandHalf;
+        if (c % CPS == 0) {  // the store that last used this staging tile has finished reading it
+          if (r == 0) tma_store_wait_read1();
+          named_bar_sync(1, 128);
+        }
+        uint32_t(&pv)[16] = (c & 1) ? pb : pa;
+        uint32_t(&gv)[16] = (c & 1) ? gb : ga;
         tmem_ld_wait();
-        if (valid) {
+        if (c < 7) {
+          tmem_ld_32x16(p_addr + (c + 1) * 16, (c & 1) ? pa : pb);
+          tmem_ld_32x16(g_addr + (c + 1) * 16, (c & 1) ? ga : gb);
+        } else {
+          tc_fence_before_sync();
+          mbar_arrive(&acc_empty[acc]);
+        }
 #pragma unroll
-          for (int g = 0; g < 4; ++g) {
-            float zr[8];
-            if (p.add_residual) {
-              load8<F32>(zrow, c * 32 + g * 8, zr);
-            } else {
+        for (int g = 0; g < 2; ++g) {
+          float x[8];
+          if (read_res && valid) {
+            load8<F32>(zrow, c * 16 + g * 8, x);
+          } else {
 #pragma unroll
-              for (int e = 0; e < 8; ++e) zr[e] = 0.f;
-            }
+            for (int e = 0; e < 8; ++e) x[e] = 0.f;
+          }
 #pragma unroll
-            for (int e = 0; e < 8; ++e)
-              zr[e] = fmaf(__uint_as_float(pv[g * 8 + e]), sigmoid_fast(__uint_as_float(gv[g * 8 + e])), zr[e]);
-            store8<F32>(orow, c * 32 + g * 8, zr);
+          for (int e = 0; e < 8; ++e)
+            x[e] = fmaf(__uint_as_float(pv[g * 8 + e]), sigmoid_fast(__uint_as_float(gv[g * 8 + e])), x[e]);
+          if (F32) {
+            const int k = (c % CPS) * 4 + g * 2;
+            *reinterpret_cast<float4*>(stage + sw128_offset(r, k)) = make_float4(x[0], x[1], x[2], x[3]);
+            *reinterpret_cast<float4*>(stage + sw128_offset(r, k + 1)) = make_float4(x[4], x[5], x[6], x[7]);
+          } else {
+            *reinterpret_cast<uint4*>(stage + sw128_offset(r, (c % CPS) * 2 + g)) = make_uint4(
+                pack_bf16x2(x[0], x[1]), pack_bf16x2(x[2], x[3]), pack_bf16x2(x[4], x[5]), pack_bf16x2(x[6], x[7]));
+          }
+        }
+        if (c % CPS == CPS - 1) {
+          fence_proxy_async_smem();
+          named_bar_sync(1, 128);
+          if (r == 0) {
+            const int ch0 = (c / CPS) * (F32 ? 32 : 64);
+            const int c1 = p.pos_is_dim1 ? pos0 : line, c2 = p.pos_is_dim1 ? line : pos0;
+            if (reduce)
+              tma_reduce_add_3d(&tmO, stage, ch0, c1, c2);
+            else
+              tma_store_3d(&tmO, stage, ch0, c1, c2);
+            tma_store_commit();
           }
         }
       }
-      tc_fence_before_sync();
-      mbar_arrive(&acc_empty[acc]);
     }
+    if (r == 0) tma_store_wait0();
   }
 
   tc_fence_before_sync();
