@@ -14,8 +14,12 @@
 //                  accumulator lives in registers and takes each key tile's P.V from TMEM.  Two groups
 //                  put two warps on every scheduler, which is what hides the TMEM / shared-memory / ex2
 //                  latencies of the one-thread-per-row softmax.
-//   loader warp    TMA: Q tiles once per item, K and V^T through a ring, one bias tile per group
-//   MMA warp       S_g = Q_g.K^T and O_g = P_g.V, one TMEM buffer each per group
+//   loader warp    TMA: Q tiles once per item (two slots, so the next item's arrive early), K and V^T through a
+//                  ring, one bias tile per group
+//   MMA warp       S_g = Q_g.K^T into one of the group's two TMEM score buffers, alternating per key tile, so
+//                  the next scores are ready when a softmax pass ends; P_g.V lands in the first DH columns of
+//                  the score buffer its P came from (dead by then).  The tile stream runs on across work
+//                  items: the first scores of the next item are issued during the last tile of this one.
 // Head dim is padded to DH = 32 or 64 by the projections (zero rows/columns), V is supplied transposed
 // ([DH][keys]) so both products read K-major operands.
 #pragma once
@@ -51,13 +55,13 @@ struct FlashCfg {
   static constexpr uint32_t V_HALF = DH * 128;           // DH rows x 64 keys x 2 B
   static constexpr uint32_t V_BYTES = 2 * V_HALF;
   static constexpr uint32_t KV_BYTES = K_BYTES + V_BYTES;
-  static constexpr uint32_t Q_OFF = 0;
-  static constexpr uint32_t KV_OFF = G * 16384;          // every Q tile gets a 16 KB slot
+  static constexpr uint32_t Q_OFF = 0;                   // [2 slots][G] query tiles
+  static constexpr uint32_t KV_OFF = 2 * G * Q_BYTES;
   static constexpr uint32_t BIAS_OFF = KV_OFF + STAGES * KV_BYTES;   // G tiles x 32 KB
   static constexpr uint32_t P_OFF = BIAS_OFF + G * kOperandTile;     // G tiles x 32 KB
   static constexpr uint32_t MASK_OFF = P_OFF + G * kOperandTile;     // 2 x MAX_T x 8 words
   static constexpr uint32_t BAR_OFF = MASK_OFF + 2 * MAX_T * 32;
-  static constexpr uint32_t SMEM_BYTES = BAR_OFF + 256 + 1024;
+  static constexpr uint32_t SMEM_BYTES = BAR_OFF + 384 + 1024;
   static constexpr int THREADS = 128 * G + 128;        // G softmax warpgroups + one for loader / MMA (2 idle warps)
   static constexpr int SOFTMAX_REGS = 0;  // setmaxnreg targets when three warpgroups share the file
   static constexpr int OTHER_REGS = 40;
@@ -84,21 +88,20 @@ flash_core_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem + Cfg::BAR_OFF);
-  uint64_t* q_full = bars;            // TMA (all G query tiles)
-  uint64_t* q_empty = bars + 1;       // commit
-  uint64_t* kv_full = bars + 2;       // [3] TMA
-  uint64_t* kv_empty = bars + 5;      // [3] commit
-  uint64_t* bias_full = bars + 8;     // [G] TMA
-  uint64_t* bias_empty = bars + 10;   // [G] count 128
-  uint64_t* s_full = bars + 12;       // [G] commit
-  uint64_t* s_empty = bars + 14;      // [G] count 128
-  uint64_t* p_full = bars + 16;       // [G] count 128
-  uint64_t* p_empty = bars + 18;      // [G] commit
-  uint64_t* o_full = bars + 20;       // [G] commit
-  uint64_t* o_empty = bars + 22;      // [G] count 128
-  uint64_t* mask_full = bars + 24;    // [2] count 1 (mask warp)
-  uint64_t* mask_empty = bars + 26;   // [2] count 128*G
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 28);
+  uint64_t* q_full = bars;            // [2 slots] TMA (all G query tiles)
+  uint64_t* q_empty = bars + 2;       // [2] commit
+  uint64_t* kv_full = bars + 4;       // [3] TMA
+  uint64_t* kv_empty = bars + 7;      // [3] commit
+  uint64_t* bias_full = bars + 10;    // [G] TMA
+  uint64_t* bias_empty = bars + 12;   // [G] count 128
+  uint64_t* s_full = bars + 14;       // [G][2 buffers] commit
+  uint64_t* s_empty = bars + 18;      // [G][2] count 128: the P.V result in the buffer has been read
+  uint64_t* p_full = bars + 22;       // [G] count 128
+  uint64_t* p_empty = bars + 24;      // [G] commit
+  uint64_t* o_full = bars + 26;       // [G][2] commit
+  uint64_t* mask_full = bars + 30;    // [2] count 1 (mask warp)
+  uint64_t* mask_empty = bars + 32;   // [2] count 128*G
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 34);
   // Key-validity bits of a work item's mask row, two buffers of MAX_T x 8 words:
   //   word t*8 + w      bit j <=> key t*128 + 32*w + j exists and is unmasked
   //   word t*8 + 4 + w  bit j <=> key t*128 + 32*w + j exists
@@ -110,23 +113,24 @@ flash_core_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
   constexpr int kMmaWarp = 4 * G + 1;
 
   if (threadIdx.x == 0) {
-    mbar_init(q_full, 1);
-    mbar_init(q_empty, 1);
     for (int i = 0; i < 3; ++i) {
       mbar_init(&kv_full[i], 1);
       mbar_init(&kv_empty[i], 1);
     }
     for (int i = 0; i < 2; ++i) {
+      mbar_init(&q_full[i], 1);
+      mbar_init(&q_empty[i], 1);
       mbar_init(&bias_full[i], 1);
       mbar_init(&bias_empty[i], 128);
-      mbar_init(&s_full[i], 1);
-      mbar_init(&s_empty[i], 128);
       mbar_init(&p_full[i], 128);
       mbar_init(&p_empty[i], 1);
-      mbar_init(&o_full[i], 1);
-      mbar_init(&o_empty[i], 128);
       mbar_init(&mask_full[i], 1);
       mbar_init(&mask_empty[i], 128 * G);
+    }
+    for (int i = 0; i < 4; ++i) {
+      mbar_init(&s_full[i], 1);
+      mbar_init(&s_empty[i], 128);
+      mbar_init(&o_full[i], 1);
     }
     fence_mbar_init();
     prefetch_tmap(&tmQ);
@@ -139,7 +143,7 @@ flash_core_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
   __syncthreads();
   tc_fence_after_sync();
   const uint32_t tmem_base = *tmem_slot;
-  // TMEM columns: S_g at g*128, O_g at 256 + g*DH.
+  // TMEM columns: score buffer pb of group g at g*256 + pb*128; its first DH columns later take P.V.
 
   const int T = p.nkt;
   // n counts key tiles over all work items of this CTA: every per-tile barrier completes one phase per n
@@ -159,10 +163,12 @@ flash_core_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
         const int bh = work / p.nqg;
         const int h = bh % p.H;
         const int b = bh / p.H;
-        mbar_wait(q_empty, (w & 1) ^ 1, 60);
-        mbar_arrive_expect_tx(q_full, G * Cfg::Q_BYTES);
+        const int qs = w & 1;
+        mbar_wait(&q_empty[qs], ((w >> 1) & 1) ^ 1, 60);
+        mbar_arrive_expect_tx(&q_full[qs], G * Cfg::Q_BYTES);
         for (int g = 0; g < G; ++g)
-          tma_load_3d(smem + Cfg::Q_OFF + g * 16384, &tmQ, q_full, p.q_col0 + h * DH, (qg * G + g) * 128, b);
+          tma_load_3d(smem + Cfg::Q_OFF + (qs * G + g) * Cfg::Q_BYTES, &tmQ, &q_full[qs], p.q_col0 + h * DH,
+                      (qg * G + g) * 128, b);
         const int bias_g = (b / p.bias_div) * p.H + h;
         for (int t = 0; t < T; ++t, ++n) {
           const int st = n % Cfg::STAGES;
@@ -190,38 +196,50 @@ flash_core_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
       // The groups run half a tile out of phase (group 1 starts late, see the softmax code), so that one is
       // in its ex2-bound second pass while the other does the ALU-bound first pass.  The requests of one
       // group are therefore served together: its next score tile, then its P.V.
-      auto issue_s = [&](int n, int g) {  // S_g = Q_g . K(n)^T
+      auto issue_s = [&](int n, int g, int qs) {  // S_g(n) = Q_g . K(n)^T into score buffer n & 1
         const int st = n % Cfg::STAGES;
+        const int pb = n & 1;
         mbar_wait(&kv_full[st], (n / Cfg::STAGES) & 1, 62);
-        mbar_wait(&s_empty[g], (n & 1) ^ 1, 63);
+        mbar_wait(&s_empty[g * 2 + pb], ((n >> 1) & 1) ^ 1, 63);
         tc_fence_after_sync();
         const uint32_t k_s = smem_u32(smem + Cfg::KV_OFF + st * Cfg::KV_BYTES);
-        const uint32_t q_s = smem_u32(smem + Cfg::Q_OFF + g * 16384);
+        const uint32_t q_s = smem_u32(smem + Cfg::Q_OFF + (qs * G + g) * Cfg::Q_BYTES);
 #pragma unroll
         for (int k = 0; k < DH / 16; ++k)
-          umma_bf16_ss(tmem_base + g * 128, make_desc_k(q_s + k * 32, SW64), make_desc_k(k_s + k * 32, SW64), idesc_s,
-                       k > 0);
-        umma_commit(&s_full[g]);
+          umma_bf16_ss(tmem_base + g * 256 + pb * 128, make_desc_k(q_s + k * 32, SW64), make_desc_k(k_s + k * 32, SW64),
+                       idesc_s, k > 0);
+        umma_commit(&s_full[g * 2 + pb]);
       };
       int n = 0, w = 0;
+      if ((int)blockIdx.x < p.total_work) {
+        mbar_wait(&q_full[0], 0, 64);
+        for (int g = 0; g < G; ++g) issue_s(0, g, 0);
+        if (T == 1) umma_commit(&q_empty[0]);
+      }
       for (int work = blockIdx.x; work < p.total_work; work += gridDim.x, ++w) {
-        mbar_wait(q_full, w & 1, 64);
-        for (int g = 0; g < G; ++g) issue_s(n, g);
+        const bool more = work + (int)gridDim.x < p.total_work;
         for (int t = 0; t < T; ++t, ++n) {
           const int st = n % Cfg::STAGES;
           const uint32_t v_s = smem_u32(smem + Cfg::KV_OFF + st * Cfg::KV_BYTES + Cfg::K_BYTES);
           for (int g = 0; g < G; ++g) {
-            if (t + 1 < T) issue_s(n + 1, g);
-            if (t + 1 == T && g == G - 1) umma_commit(q_empty);  // every S product of this item has been issued
+            // next score tile of this group: of this item, or the first one of the next item
+            if (t + 1 < T) {
+              issue_s(n + 1, g, w & 1);
+              if (t + 2 == T && g == G - 1) umma_commit(&q_empty[w & 1]);  // every S product of this item is issued
+            } else if (more) {
+              if (g == 0) mbar_wait(&q_full[(w + 1) & 1], ((w + 1) >> 1) & 1, 64);
+              issue_s(n + 1, g, (w + 1) & 1);
+              if (T == 1 && g == G - 1) umma_commit(&q_empty[(w + 1) & 1]);
+            }
             mbar_wait(&p_full[g], n & 1, 65);
-            mbar_wait(&o_empty[g], (n & 1) ^ 1, 66);
             tc_fence_after_sync();
             const uint32_t p_s = smem_u32(smem + Cfg::P_OFF + g * kOperandTile);
 #pragma unroll
             for (int k = 0; k < 8; ++k)
-              umma_bf16_ss(tmem_base + 256 + g * DH, make_desc_k_sw128(p_s + (k >> 2) * kOperandHalf + (k & 3) * 32),
+              umma_bf16_ss(tmem_base + g * 256 + (n & 1) * 128,
+                           make_desc_k_sw128(p_s + (k >> 2) * kOperandHalf + (k & 3) * 32),
                            make_desc_k_sw128(v_s + (k >> 2) * Cfg::V_HALF + (k & 3) * 32), idesc_o, k > 0);
-            umma_commit(&o_full[g]);
+            umma_commit(&o_full[g * 2 + (n & 1)]);
             umma_commit(&p_empty[g]);
           }
           umma_commit(&kv_empty[st]);

@@ -68,7 +68,8 @@ struct RowTile {
   uint4 v[RPT];
 
   // row_ptr(r) -> address of channel 0 of tile row r (elements of the z stream), or nullptr if absent.
-  template <bool F32, bool NORM, class RowPtr>
+  // LS: rows normalised in lock step (8 where the kernel has registers to spare, fewer otherwise).
+  template <bool F32, bool NORM, int LS = 8, class RowPtr>
   __device__ __forceinline__ void load(int pt, RowPtr row_ptr, const float (&gamma)[8], const float (&beta)[8],
                                        float eps) {
     const int c0 = (pt & 15) * 8;
@@ -86,25 +87,52 @@ struct RowTile {
           for (int i = 0; i < 8; ++i) x[q][i] = 0.f;
         }
       }
+      if (NORM) {
+        // LS rows at a time go through the two 16-lane reductions in lock step, so each shuffle step is LS
+        // independent exchanges instead of a serial chain per row.
 #pragma unroll
-      for (int q = 0; q < 8; ++q) {
-        if (NORM) {
-          float s = 0.f;
+        for (int qb = 0; qb < 8; qb += LS) {
+          float s[LS];
 #pragma unroll
-          for (int i = 0; i < 8; ++i) s += x[q][i];
-          const float mean = group16_sum(s) * (1.0f / kD);
-          float ss = 0.f;
+          for (int q = 0; q < LS; ++q) {
+            s[q] = 0.f;
 #pragma unroll
-          for (int i = 0; i < 8; ++i) {
-            x[q][i] -= mean;
-            ss = fmaf(x[q][i], x[q][i], ss);
+            for (int i = 0; i < 8; ++i) s[q] += x[qb + q][i];
           }
-          const float rstd = rsqrtf(group16_sum(ss) * (1.0f / kD) + eps);
 #pragma unroll
-          for (int i = 0; i < 8; ++i) x[q][i] = fmaf(x[q][i] * rstd, gamma[i], beta[i]);
+          for (int off = 8; off > 0; off >>= 1) {
+#pragma unroll
+            for (int q = 0; q < LS; ++q) s[q] += __shfl_xor_sync(0xffffffffu, s[q], off);
+          }
+#pragma unroll
+          for (int q = 0; q < LS; ++q) {
+            const float mean = s[q] * (1.0f / kD);
+            s[q] = 0.f;
+#pragma unroll
+            for (int i = 0; i < 8; ++i) {
+              x[qb + q][i] -= mean;
+              s[q] = fmaf(x[qb + q][i], x[qb + q][i], s[q]);
+            }
+          }
+#pragma unroll
+          for (int off = 8; off > 0; off >>= 1) {
+#pragma unroll
+            for (int q = 0; q < LS; ++q) s[q] += __shfl_xor_sync(0xffffffffu, s[q], off);
+          }
+#pragma unroll
+          for (int q = 0; q < LS; ++q) {
+            const float rstd = rsqrtf(s[q] * (1.0f / kD) + eps);
+#pragma unroll
+            for (int i = 0; i < 8; ++i) x[qb + q][i] = fmaf(x[qb + q][i] * rstd, gamma[i], beta[i]);
+            v[q0 + qb + q] = make_uint4(pack_bf16x2(x[qb + q][0], x[qb + q][1]), pack_bf16x2(x[qb + q][2], x[qb + q][3]),
+                                        pack_bf16x2(x[qb + q][4], x[qb + q][5]), pack_bf16x2(x[qb + q][6], x[qb + q][7]));
+          }
         }
-        v[q0 + q] = make_uint4(pack_bf16x2(x[q][0], x[q][1]), pack_bf16x2(x[q][2], x[q][3]),
-                               pack_bf16x2(x[q][4], x[q][5]), pack_bf16x2(x[q][6], x[q][7]));
+      } else {
+#pragma unroll
+        for (int q = 0; q < 8; ++q)
+          v[q0 + q] = make_uint4(pack_bf16x2(x[q][0], x[q][1]), pack_bf16x2(x[q][2], x[q][3]),
+                                 pack_bf16x2(x[q][4], x[q][5]), pack_bf16x2(x[q][6], x[q][7]));
       }
     }
   }

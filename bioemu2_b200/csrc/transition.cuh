@@ -156,7 +156,7 @@ transition_kernel(const __grid_constant__ CUtensorMap tmW1, const __grid_constan
         return (row0 + r) < p.rows ? static_cast<const uint8_t*>(p.x) + (row0 + r) * kD * zbytes<F32>() : nullptr;
       };
       if (p.use_norm)
-        regs.template load<F32, true>(pt, rp, gamma, beta, p.eps);
+        regs.template load<F32, true, 1>(pt, rp, gamma, beta, p.eps);
       else
         regs.template load<F32, false>(pt, rp, gamma, beta, p.eps);
     };

@@ -128,7 +128,7 @@ trimul_in_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant_
       const int line = tile / tiles_per_line;
       const int pos0 = (tile - line * tiles_per_line) << 7;
       const uint8_t* base = static_cast<const uint8_t*>(p.z) + line * line_stride;
-      regs.template load<F32, true>(
+      regs.template load<F32, true, 1>(
           pt,
           [&](int r) -> const void* {
             const int pos = pos0 + r;
@@ -403,7 +403,7 @@ trimul_out_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant
       const int line = tile / tiles_per_line;
       const int pos0 = (tile - line * tiles_per_line) << 7;
       const uint8_t* base = static_cast<const uint8_t*>(p.z) + line * p.z_line_stride + pos0 * p.z_pos_stride;
-      regs.template load<F32, true>(
+      regs.template load<F32, true, 1>(
           pt,
           [&](int r) -> const void* { return (pos0 + r) < p.n_pos ? base + r * p.z_pos_stride : nullptr; },
           gamma, beta, p.eps);
