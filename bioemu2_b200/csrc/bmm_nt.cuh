@@ -31,6 +31,9 @@ struct BmmParams {
   // (line < remap_m) is stored as row pos * remap_m + line.
   const void* residual;
   int remap_n, remap_m;
+  // Bulk output (fp32 C only): the scaled (+ bias) tile leaves through 16 KB staging tiles and the C tensor
+  // map, 1 = stored, 2 = added into C (the residual is C itself, which the epilogue then never reads).
+  int tma_c;
 };
 
 template <int BN>
@@ -42,13 +45,15 @@ struct BmmCfg {
   static constexpr uint32_t B_BYTES = BN * BK * 2;
   static constexpr uint32_t STAGE_BYTES = A_BYTES + B_BYTES;
   static constexpr uint32_t BAR_OFFSET = STAGES * STAGE_BYTES;
-  static constexpr uint32_t SMEM_BYTES = BAR_OFFSET + 256 + 1024;  // + barriers + alignment slack
+  static constexpr uint32_t OUT_OFFSET = BAR_OFFSET + 1024;        // two [128 rows][32 fp32] tiles for bulk output
+  static constexpr uint32_t SMEM_BYTES = OUT_OFFSET + 2 * 16384 + 1024;  // + alignment slack
   static constexpr int THREADS = 192;
 };
 
 template <int BN>
 __global__ void __launch_bounds__(192, 1)
-bmm_nt_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB, BmmParams p) {
+bmm_nt_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
+              const __grid_constant__ CUtensorMap tmC, BmmParams p) {
   using Cfg = BmmCfg<BN>;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
@@ -75,6 +80,7 @@ bmm_nt_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ C
     fence_mbar_init();
     prefetch_tmap(&tmA);
     prefetch_tmap(&tmB);
+    if (p.tma_c) prefetch_tmap(&tmC);
   }
   if (warp == 1) tmem_alloc(tmem_slot, 512);
   tc_fence_before_sync();
@@ -147,6 +153,56 @@ bmm_nt_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ C
       tc_fence_after_sync();
       const int row = tm * 128 + quarter * 32 + lane;
       const float scale = p.scale_ptr ? p.scale * p.scale_ptr[b] : p.scale;
+      if (p.tma_c) {
+        // 32 columns at a time into one of two swizzled staging tiles; warp 2's first lane sends each tile off.
+        const int r = quarter * 32 + lane;
+        const bool leader = threadIdx.x == 64;
+        int c1 = tm * 128, c2 = b;  // tensor map {column, row, batch}, or {column, line, pos} when remapped
+        if (p.remap_n > 0) {
+          c1 = (tm * 128) / p.remap_n;
+          c2 = tm * 128 - c1 * p.remap_n;
+        }
+        uint32_t va[32], vb[32];
+        tmem_ld_32x32(tmem_addr(tmem_base, quarter * 32, acc * BN), va);
+#pragma unroll
+        for (int c = 0; c < BN / 32; ++c) {
+          uint32_t(&v)[32] = (c & 1) ? vb : va;
+          uint8_t* stage = smem + Cfg::OUT_OFFSET + (c & 1) * 16384;
+          if (leader) tma_store_wait_read1();  // the store that last used this staging tile has read it
+          named_bar_sync(1, 128);
+          tmem_ld_wait();
+          if (c + 1 < BN / 32) {
+            tmem_ld_32x32(tmem_addr(tmem_base, quarter * 32, acc * BN + (c + 1) * 32), (c & 1) ? va : vb);
+          } else {
+            tc_fence_before_sync();
+            mbar_arrive(&acc_empty[acc]);
+          }
+          const int col0 = tn * BN + c * 32;
+#pragma unroll
+          for (int g = 0; g < 8; ++g) {
+            float4 x;
+            x.x = __uint_as_float(v[g * 4 + 0]) * scale;
+            x.y = __uint_as_float(v[g * 4 + 1]) * scale;
+            x.z = __uint_as_float(v[g * 4 + 2]) * scale;
+            x.w = __uint_as_float(v[g * 4 + 3]) * scale;
+            if (p.bias) {
+              const float4 bv = *reinterpret_cast<const float4*>(p.bias + col0 + g * 4);
+              x.x += bv.x; x.y += bv.y; x.z += bv.z; x.w += bv.w;
+            }
+            *reinterpret_cast<float4*>(stage + sw128_offset(r, g)) = x;
+          }
+          fence_proxy_async_smem();
+          named_bar_sync(1, 128);
+          if (leader && col0 < p.n_valid) {
+            if (p.tma_c == 2)
+              tma_reduce_add_3d(&tmC, stage, col0, c1, c2);
+            else
+              tma_store_3d(&tmC, stage, col0, c1, c2);
+            tma_store_commit();
+          }
+        }
+        continue;
+      }
       const size_t esz = p.out_f32 ? 4 : 2;
       uint8_t* cbase = static_cast<uint8_t*>(p.C) + (long long)b * p.c_batch_stride * esz;
       // 32 columns at a time; the next chunk's TMEM load and (when a residual is added) its residual row
@@ -215,6 +271,7 @@ bmm_nt_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ C
     }
   }
 
+  if (p.tma_c && threadIdx.x == 64) tma_store_wait0();
   tc_fence_before_sync();
   __syncthreads();
   if (warp == 1) {

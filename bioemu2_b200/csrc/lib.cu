@@ -71,14 +71,39 @@ static int launch_bmm(const BmmLaunch& a, cudaStream_t stream) {
   p.residual = a.residual;
   p.remap_n = a.remap_n;
   p.remap_m = a.remap_m > 0 ? a.remap_m : a.remap_n;
+  // Bulk output through the C tensor map where the layout allows it: fp32 C, whole 32-column groups, the
+  // residual (if any) being C itself, and for the transposed pair store lines that are whole row tiles.
+  p.tma_c = 0;
+  CUtensorMap tmC = tmA;
+  const int64_t c_batch = a.sc > 0 ? a.sc : a.ldc * int64_t(a.M);
+  if (a.out_f32 && a.opm_ntok == 0 && a.N % 32 == 0 && a.ldc % 4 == 0 && c_batch % 4 == 0 && aligned(a.C, 16) &&
+      (a.residual == nullptr || a.residual == a.C) && (a.bias == nullptr || aligned(a.bias, 16)) &&
+      (a.remap_n == 0 || (a.remap_n % 128 == 0 && a.batch == 1 && a.M == a.remap_n * p.remap_m))) {
+    uint64_t dims[3], str[2];
+    uint32_t box[3];
+    dims[0] = uint64_t(a.N);
+    box[0] = 32;
+    if (a.remap_n > 0) {  // {column, line, pos}: pair (line, pos) lives in row pos * remap_m + line
+      dims[1] = uint64_t(p.remap_m), dims[2] = uint64_t(a.remap_n);
+      str[0] = uint64_t(a.ldc) * 4, str[1] = uint64_t(a.ldc) * 4 * uint64_t(p.remap_m);
+      box[1] = 1, box[2] = 128;
+    } else {
+      dims[1] = uint64_t(a.M), dims[2] = uint64_t(a.batch);
+      str[0] = uint64_t(a.ldc) * 4, str[1] = uint64_t(c_batch) * 4;
+      box[1] = 128, box[2] = 1;
+    }
+    if (int e = make_tmap(&tmC, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, a.C, 3, dims, str, box, CU_TENSOR_MAP_SWIZZLE_128B))
+      return e;
+    p.tma_c = a.residual ? 2 : 1;
+  }
   const int total = p.tiles_m * p.tiles_n * a.batch;
   const int grid = total < sm_count() ? total : sm_count();
   if (BN == 256) {
     if (int e = set_smem(bmm_nt_kernel<256>, BmmCfg<256>::SMEM_BYTES)) return e;
-    bmm_nt_kernel<256><<<grid, 192, BmmCfg<256>::SMEM_BYTES, stream>>>(tmA, tmB, p);
+    bmm_nt_kernel<256><<<grid, 192, BmmCfg<256>::SMEM_BYTES, stream>>>(tmA, tmB, tmC, p);
   } else {
     if (int e = set_smem(bmm_nt_kernel<128>, BmmCfg<128>::SMEM_BYTES)) return e;
-    bmm_nt_kernel<128><<<grid, 192, BmmCfg<128>::SMEM_BYTES, stream>>>(tmA, tmB, p);
+    bmm_nt_kernel<128><<<grid, 192, BmmCfg<128>::SMEM_BYTES, stream>>>(tmA, tmB, tmC, p);
   }
   B200_CUDA(cudaGetLastError());
   return 0;
@@ -938,6 +963,19 @@ static int triatt_slab(const void* z, const uint8_t* mask, const void* ext_bias,
     const uint32_t box[2] = {64, 128};
     if (int e = make_tmap_bf16(&tmW, w->w_qkgv, 2, dims, str, box, CU_TENSOR_MAP_SWIZZLE_128B)) return e;
   }
+  CUtensorMap tmQKG, tmVT;  // [128 rows][64 values] boxes: pairs x channels of q|k|g, channels x keys of V^T
+  {
+    const uint64_t dims[3] = {384, uint64_t(pos), uint64_t(lines)};
+    const uint64_t str[2] = {768, uint64_t(pos) * 768};
+    const uint32_t box[3] = {64, 128, 1};
+    if (int e = make_tmap_bf16(&tmQKG, qkg, 3, dims, str, box, CU_TENSOR_MAP_SWIZZLE_128B)) return e;
+  }
+  {
+    const uint64_t dims[3] = {uint64_t(pos), uint64_t(kD), uint64_t(lines)};
+    const uint64_t str[2] = {uint64_t(pl.Nk) * 2, uint64_t(pl.Nk) * kD * 2};
+    const uint32_t box[3] = {64, 128, 1};
+    if (int e = make_tmap_bf16(&tmVT, vT, 3, dims, str, box, CU_TENSOR_MAP_SWIZZLE_128B)) return e;
+  }
   if (int e = set_smem(triatt_proj_kernel<true>, triatt_proj::SMEM_BYTES)) return e;
   if (int e = set_smem(triatt_proj_kernel<false>, triatt_proj::SMEM_BYTES)) return e;
   TriAttProjParams pp;
@@ -956,9 +994,9 @@ static int triatt_slab(const void* z, const uint8_t* mask, const void* ext_bias,
   pp.eps = 1e-5f;
   const int grid = pp.num_tiles < sm_count() ? pp.num_tiles : sm_count();
   if (f32)
-    triatt_proj_kernel<true><<<grid, triatt_proj::THREADS, triatt_proj::SMEM_BYTES, stream>>>(tmW, pp);
+    triatt_proj_kernel<true><<<grid, triatt_proj::THREADS, triatt_proj::SMEM_BYTES, stream>>>(tmW, tmQKG, tmVT, pp);
   else
-    triatt_proj_kernel<false><<<grid, triatt_proj::THREADS, triatt_proj::SMEM_BYTES, stream>>>(tmW, pp);
+    triatt_proj_kernel<false><<<grid, triatt_proj::THREADS, triatt_proj::SMEM_BYTES, stream>>>(tmW, tmQKG, tmVT, pp);
   B200_CUDA(cudaGetLastError());
   if (!ext_bias) {
     if (int e = launch_pair_bias(z, f32, w->ln_w, w->ln_b, w->w_b, tb, lines, pos, line_b, pos_b, (long long)pos * pl.Nk,

@@ -31,13 +31,15 @@ constexpr uint32_t W_OFF = 0;                        // Wq, Wk, Wg, Wv: 4 x 32 K
 constexpr uint32_t X_OFF = 4 * kOperandTile;         // 2 stages x 32 KB
 constexpr uint32_t GB_OFF = X_OFF + 2 * kOperandTile;  // gate bias, 512 B
 constexpr uint32_t BAR_OFF = GB_OFF + 512;
-constexpr uint32_t SMEM_BYTES = BAR_OFF + 128 + 1024;
+constexpr uint32_t STAGE_OFF = GB_OFF + 1024;        // two 16 KB output tiles [128 rows][128 B] for the TMA stores
+constexpr uint32_t SMEM_BYTES = STAGE_OFF + 2 * kOperandHalf + 1024;
 constexpr int THREADS = 416;
 }  // namespace triatt_proj
 
 template <bool F32>
 __global__ void __launch_bounds__(416, 1)
-triatt_proj_kernel(const __grid_constant__ CUtensorMap tmW, TriAttProjParams p) {
+triatt_proj_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUtensorMap tmQKG,
+                   const __grid_constant__ CUtensorMap tmVT, TriAttProjParams p) {
   using namespace triatt_proj;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
@@ -63,6 +65,8 @@ triatt_proj_kernel(const __grid_constant__ CUtensorMap tmW, TriAttProjParams p) 
     }
     fence_mbar_init();
     prefetch_tmap(&tmW);
+    prefetch_tmap(&tmQKG);
+    prefetch_tmap(&tmVT);
   }
   if (threadIdx.x < 128) gb_s[threadIdx.x] = p.g_bias[threadIdx.x];
   if (warp == 12) tmem_alloc(tmem_slot, 512);
@@ -134,65 +138,64 @@ triatt_proj_kernel(const __grid_constant__ CUtensorMap tmW, TriAttProjParams p) 
     for (int tile = blockIdx.x; tile < p.num_tiles; tile += gridDim.x, ++it) {
       const int line = tile / tiles_per_line;
       const int pos0 = (tile - line * tiles_per_line) << 7;
-      const bool valid = (pos0 + r) < p.n_pos;
-      __nv_bfloat16* row = p.qkg + ((long long)line * p.n_pos + pos0 + r) * 384;
-      // Both groups are read 32 columns at a time with the next chunk's TMEM load already in flight.
+      // The 512 accumulator columns leave as eight [128 rows][64 values] bf16 tiles through two swizzled
+      // staging tiles and TMA stores: q, k (4 tiles) and g + bias (2 tiles) with lane = pair into the pair-major
+      // rows, V^T (2 tiles) with lane = channel into the line's channel-major plane.  TMEM is read 32 columns
+      // at a time with the next chunk's load in flight.
       uint32_t va[32], vb[32];
-      auto pack8 = [](const uint32_t* v) {
-        return make_uint4(pack_bf16x2(__uint_as_float(v[0]), __uint_as_float(v[1])),
-                          pack_bf16x2(__uint_as_float(v[2]), __uint_as_float(v[3])),
-                          pack_bf16x2(__uint_as_float(v[4]), __uint_as_float(v[5])),
-                          pack_bf16x2(__uint_as_float(v[6]), __uint_as_float(v[7])));
-      };
-      // ---- group A: q, k
+      const bool leader = threadIdx.x == 0;
       mbar_wait(&acc_full[0], it & 1, 95);
       tc_fence_after_sync();
       tmem_ld_32x32(tmem_addr(tmem_base, warp * 32, 0), va);
 #pragma unroll
-      for (int c = 0; c < 8; ++c) {
+      for (int c = 0; c < 16; ++c) {
         uint32_t(&v)[32] = (c & 1) ? vb : va;
-        tmem_ld_wait();
-        if (c < 7) tmem_ld_32x32(tmem_addr(tmem_base, warp * 32, (c + 1) * 32), (c & 1) ? va : vb);
-        if (valid) {
-#pragma unroll
-          for (int g = 0; g < 4; ++g) *reinterpret_cast<uint4*>(row + c * 32 + g * 8) = pack8(&v[g * 8]);
+        uint8_t* stage = smem + STAGE_OFF + ((c >> 1) & 1) * kOperandHalf;
+        if ((c & 1) == 0) {  // the store that last used this staging tile has finished reading it
+          if (leader) tma_store_wait_read1();
+          named_bar_sync(1, 128);
         }
-      }
-      tc_fence_before_sync();
-      mbar_arrive(&acc_empty[0]);
-      // ---- group B: g (+ bias) in columns 256..383, V^T in 384..511
-      __nv_bfloat16* vrow = p.vT + ((long long)line * kD + r) * p.Nk + pos0;
-      mbar_wait(&acc_full[1], it & 1, 96);
-      tc_fence_after_sync();
-      tmem_ld_32x32(tmem_addr(tmem_base, warp * 32, 256), va);
-#pragma unroll
-      for (int c = 0; c < 8; ++c) {
-        uint32_t(&v)[32] = (c & 1) ? vb : va;
         tmem_ld_wait();
-        if (c < 7) tmem_ld_32x32(tmem_addr(tmem_base, warp * 32, 256 + (c + 1) * 32), (c & 1) ? va : vb);
-        if (c < 4) {
-          if (valid) {
-#pragma unroll
-            for (int g = 0; g < 4; ++g) {
-              float y[8];
-#pragma unroll
-              for (int e = 0; e < 8; ++e) y[e] = __uint_as_float(v[g * 8 + e]) + gb_s[c * 32 + g * 8 + e];
-              *reinterpret_cast<uint4*>(row + 256 + c * 32 + g * 8) = make_uint4(
-                  pack_bf16x2(y[0], y[1]), pack_bf16x2(y[2], y[3]), pack_bf16x2(y[4], y[5]), pack_bf16x2(y[6], y[7]));
-            }
-          }
+        if (c == 7) {  // q, k read: the next tile's group A products may start; g, V^T must have landed
+          tc_fence_before_sync();
+          mbar_arrive(&acc_empty[0]);
+          mbar_wait(&acc_full[1], it & 1, 96);
+          tc_fence_after_sync();
+        }
+        if (c < 15) {
+          tmem_ld_32x32(tmem_addr(tmem_base, warp * 32, (c + 1) * 32), (c & 1) ? va : vb);
         } else {
+          tc_fence_before_sync();
+          mbar_arrive(&acc_empty[1]);
+        }
 #pragma unroll
-          for (int g = 0; g < 4; ++g)
-            if (pos0 + (c - 4) * 32 + g * 8 < p.n_pos)
-              *reinterpret_cast<uint4*>(vrow + (c - 4) * 32 + g * 8) = pack8(&v[g * 8]);
+        for (int g = 0; g < 4; ++g) {
+          float y[8];
+#pragma unroll
+          for (int e = 0; e < 8; ++e) y[e] = __uint_as_float(v[g * 8 + e]);
+          if (c >= 8 && c < 12) {
+#pragma unroll
+            for (int e = 0; e < 8; ++e) y[e] += gb_s[(c - 8) * 32 + g * 8 + e];
+          }
+          *reinterpret_cast<uint4*>(stage + sw128_offset(r, (c & 1) * 4 + g)) = make_uint4(
+              pack_bf16x2(y[0], y[1]), pack_bf16x2(y[2], y[3]), pack_bf16x2(y[4], y[5]), pack_bf16x2(y[6], y[7]));
+        }
+        if (c & 1) {
+          fence_proxy_async_smem();
+          named_bar_sync(1, 128);
+          if (leader) {
+            if (c < 12)
+              tma_store_3d(&tmQKG, stage, (c >> 1) * 64, pos0, line);
+            else
+              tma_store_3d(&tmVT, stage, pos0 + ((c >> 1) - 6) * 64, 0, line);
+            tma_store_commit();
+          }
         }
       }
-      tc_fence_before_sync();
-      mbar_arrive(&acc_empty[1]);
     }
   }
 
+  if (threadIdx.x == 0) tma_store_wait0();
   tc_fence_before_sync();
   __syncthreads();
   if (warp == 12) {
