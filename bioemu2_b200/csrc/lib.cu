@@ -515,7 +515,7 @@ int b200_transition_fwd(const void* x, void* out, const void* w13, const void* w
   cudaStream_t stream = static_cast<cudaStream_t>(stream_);
   B200_CHECK_ARG(x && out && w13 && w3, "x/out/w13/w3 is NULL");
   B200_CHECK_ARG(!use_norm || (ln_w && ln_b), "use_norm needs ln_w and ln_b");
-  B200_CHECK_ARG(rows >= 0 && rows < (int64_t(1) << 31) * 128, "rows out of range");
+  B200_CHECK_ARG(rows >= 0 && rows < (int64_t(1) << 31), "rows out of range");
   B200_CHECK_ARG(x_dtype == B200_DTYPE_BF16 || x_dtype == B200_DTYPE_F32, "unknown x_dtype %d", x_dtype);
   B200_CHECK_ARG(aligned(x, 32) && aligned(out, 32) && aligned(w13, 16) && aligned(w3, 16),
                  "x/out must be 32-byte aligned, weights 16-byte aligned");
@@ -533,6 +533,16 @@ int b200_transition_fwd(const void* x, void* out, const void* w13, const void* w
     const uint32_t box[2] = {64, 128};
     if (int e = make_tmap_bf16(&tmW3, w3, 2, dims, str, box, CU_TENSOR_MAP_SWIZZLE_128B)) return e;
   }
+  const bool tr_f32 = x_dtype == B200_DTYPE_F32;
+  CUtensorMap tmO;  // output rows, [128 rows][64 B] boxes
+  {
+    const uint64_t dims[2] = {uint64_t(kD), uint64_t(rows)};
+    const uint64_t str[1] = {uint64_t(kD) * (tr_f32 ? 4 : 2)};
+    const uint32_t box[2] = {tr_f32 ? 16u : 32u, 128};
+    if (int e = make_tmap(&tmO, tr_f32 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, out, 2, dims, str,
+                          box, CU_TENSOR_MAP_SWIZZLE_64B))
+      return e;
+  }
   if (int e = set_smem(transition_kernel<true>, transition::SMEM_BYTES)) return e;
   if (int e = set_smem(transition_kernel<false>, transition::SMEM_BYTES)) return e;
   TransitionParams p;
@@ -547,9 +557,9 @@ int b200_transition_fwd(const void* x, void* out, const void* w13, const void* w
   p.eps = 1e-5f;
   const int grid = p.num_tiles < sm_count() ? p.num_tiles : sm_count();
   if (x_dtype == B200_DTYPE_F32)
-    transition_kernel<true><<<grid, transition::THREADS, transition::SMEM_BYTES, stream>>>(tmW1, tmW3, p);
+    transition_kernel<true><<<grid, transition::THREADS, transition::SMEM_BYTES, stream>>>(tmW1, tmW3, tmO, p);
   else
-    transition_kernel<false><<<grid, transition::THREADS, transition::SMEM_BYTES, stream>>>(tmW1, tmW3, p);
+    transition_kernel<false><<<grid, transition::THREADS, transition::SMEM_BYTES, stream>>>(tmW1, tmW3, tmO, p);
   B200_CUDA(cudaGetLastError());
   return B200_OK;
 }

@@ -71,7 +71,7 @@ struct RowTile {
   // LS: rows normalised in lock step (8 where the kernel has registers to spare, fewer otherwise).
   template <bool F32, bool NORM, int LS = 8, class RowPtr>
   __device__ __forceinline__ void load(int pt, RowPtr row_ptr, const float (&gamma)[8], const float (&beta)[8],
-                                       float eps) {
+                                       float eps, float raw_scale = 1.0f) {
     const int c0 = (pt & 15) * 8;
     const int rbase = pt >> 4;
 #pragma unroll
@@ -128,11 +128,14 @@ struct RowTile {
                                         pack_bf16x2(x[qb + q][4], x[qb + q][5]), pack_bf16x2(x[qb + q][6], x[qb + q][7]));
           }
         }
-      } else {
+      } else {  // no LayerNorm: the rows are only scaled by raw_scale (a power of two keeps them exact)
 #pragma unroll
-        for (int q = 0; q < 8; ++q)
+        for (int q = 0; q < 8; ++q) {
+#pragma unroll
+          for (int i = 0; i < 8; ++i) x[q][i] *= raw_scale;
           v[q0 + q] = make_uint4(pack_bf16x2(x[q][0], x[q][1]), pack_bf16x2(x[q][2], x[q][3]),
                                  pack_bf16x2(x[q][4], x[q][5]), pack_bf16x2(x[q][6], x[q][7]));
+        }
       }
     }
   }

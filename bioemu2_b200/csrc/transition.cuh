@@ -6,6 +6,11 @@
 // matching 64-wide slice of fc3 into the output accumulator (two of them, so the final store of a tile
 // overlaps the next tile's GEMMs).  The hidden activations never leave the SM.
 //
+// The GEMM1 input is halved (exactly), so with a' = fc1/2, b' = fc2/2 the SwiGLU product is
+// silu(a) b = 2 (u + u tanh(a')) with u = a' b': one MUFU and two FMA-pipe operations per hidden element; the
+// factor 2 is applied to the output accumulator.  The output leaves through swizzled [128 rows][64 B] staging
+// tiles and TMA: added into x in place when the residual is wanted and out aliases x, stored otherwise.
+//
 //   warps 0-3   SwiGLU epilogue of even chunks + final store of even tiles
 //   warps 4-7   SwiGLU epilogue of odd chunks  + final store of odd tiles
 //   warps 8-15  producers: load rows, LayerNorm, write the GEMM1 A operand
@@ -35,14 +40,15 @@ constexpr uint32_t W1_OFF = X_OFF + 2 * kOperandTile;    // 2 stages x 32 KB ([f
 constexpr uint32_t W3_OFF = W1_OFF + 2 * kOperandTile;   // 2 stages x 16 KB (fc3 slice, 128 rows x 64 K)
 constexpr uint32_t H_OFF = W3_OFF + 2 * kOperandHalf;    // 2 buffers x 16 KB (A of GEMM2, 128 rows x 64 K)
 constexpr uint32_t BAR_OFF = H_OFF + 2 * kOperandHalf;
-constexpr uint32_t SMEM_BYTES = BAR_OFF + 256 + 1024;
+constexpr uint32_t STAGE_OFF = BAR_OFF + 1024;           // per epilogue group two 8 KB output tiles
+constexpr uint32_t SMEM_BYTES = STAGE_OFF + 4 * 8192 + 1024;
 constexpr int THREADS = 576;
 }  // namespace transition
 
 template <bool F32>
 __global__ void __launch_bounds__(576, 1)
 transition_kernel(const __grid_constant__ CUtensorMap tmW1, const __grid_constant__ CUtensorMap tmW3,
-                  TransitionParams p) {
+                  const __grid_constant__ CUtensorMap tmO, TransitionParams p) {
   using namespace transition;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
@@ -82,6 +88,7 @@ transition_kernel(const __grid_constant__ CUtensorMap tmW1, const __grid_constan
     fence_mbar_init();
     prefetch_tmap(&tmW1);
     prefetch_tmap(&tmW3);
+    prefetch_tmap(&tmO);
   }
   if (warp == 16) tmem_alloc(tmem_slot, 512);
   tc_fence_before_sync();
@@ -148,7 +155,7 @@ transition_kernel(const __grid_constant__ CUtensorMap tmW1, const __grid_constan
     // ------------------------------------------------------------------ producers
     const int pt = threadIdx.x - 256;  // 0..255
     float gamma[8], beta[8];
-    load_gamma_beta(p.ln_w, p.ln_b, pt, gamma, beta);
+    load_gamma_beta(p.ln_w, p.ln_b, pt, gamma, beta, 0.5f);
     RowTile<256> regs;
     auto load_tile = [&](int tile) {
       const long long row0 = (long long)tile * 128;
@@ -158,7 +165,7 @@ transition_kernel(const __grid_constant__ CUtensorMap tmW1, const __grid_constan
       if (p.use_norm)
         regs.template load<F32, true, 1>(pt, rp, gamma, beta, p.eps);
       else
-        regs.template load<F32, false>(pt, rp, gamma, beta, p.eps);
+        regs.template load<F32, false>(pt, rp, gamma, beta, p.eps, 0.5f);
     };
     int it = 0;
     int tile = blockIdx.x;
@@ -199,9 +206,8 @@ transition_kernel(const __grid_constant__ CUtensorMap tmW1, const __grid_constan
             for (int e = 0; e < 4; ++e) {
               const int j0 = q * 8 + e * 2;
               const float a0 = __uint_as_float(av[j0]), a1 = __uint_as_float(av[j0 + 1]);
-              const float h0 = a0 * sigmoid_fast(a0) * __uint_as_float(bv[j0]);
-              const float h1 = a1 * sigmoid_fast(a1) * __uint_as_float(bv[j0 + 1]);
-              o[e] = pack_bf16x2(h0, h1);
+              const float u0 = a0 * __uint_as_float(bv[j0]), u1 = a1 * __uint_as_float(bv[j0 + 1]);
+              o[e] = pack_bf16x2(fmaf(u0, tanh_approx(a0), u0), fmaf(u1, tanh_approx(a1), u1));
             }
             *reinterpret_cast<uint4*>(hrow + sw128_offset(r, hh * 4 + q)) = make_uint4(o[0], o[1], o[2], o[3]);
           }
@@ -212,38 +218,70 @@ transition_kernel(const __grid_constant__ CUtensorMap tmW1, const __grid_constan
         mbar_arrive(&h_full[b]);
       }
       if ((it & 1) == grp) {
+        // final store of the tile: CPS columns (64 B) at a time, the next TMEM load in flight, through the
+        // group's two staging tiles
+        constexpr int CPS = F32 ? 16 : 32;
         const int o = it & 1;
+        const bool leader = r == 0;
+        const bool reduce = p.add_residual && p.out == p.x;
+        const bool read_res = p.add_residual && !reduce;
         mbar_wait(&out_full[o], (it >> 1) & 1, 41);
         tc_fence_after_sync();
         const long long row = (long long)tile * 128 + r;
         const bool valid = row < p.rows;
         const uint8_t* xrow = static_cast<const uint8_t*>(p.x) + row * kD * zbytes<F32>();
-        uint8_t* orow = static_cast<uint8_t*>(p.out) + row * kD * zbytes<F32>();
-#pragma unroll 1
-        for (int c = 0; c < 4; ++c) {
-          uint32_t v[32];
-          tmem_ld_32x32(tmem_addr(tmem_base, quarter * 32, 256 + o * 128 + c * 32), v);
+        const uint32_t o_addr = tmem_addr(tmem_base, quarter * 32, 256 + o * 128);
+        const uint32_t row_off = r * 64, row_xor = (r >> 1) & 3;
+        uint32_t va[CPS], vb[CPS];
+        if (F32) tmem_ld_32x16(o_addr, reinterpret_cast<uint32_t(&)[16]>(va));
+        else tmem_ld_32x32(o_addr, reinterpret_cast<uint32_t(&)[32]>(va));
+#pragma unroll
+        for (int k = 0; k < kD / CPS; ++k) {
+          uint32_t(&v)[CPS] = (k & 1) ? vb : va;
+          uint8_t* stage = smem + STAGE_OFF + (grp * 2 + (k & 1)) * 8192;
+          if (leader) tma_store_wait_read1();  // the store that last used this staging tile has read it
+          named_bar_sync(1 + grp, 128);
           tmem_ld_wait();
-          if (valid) {
+          if (k + 1 < kD / CPS) {
+            if (F32) tmem_ld_32x16(o_addr + (k + 1) * CPS, reinterpret_cast<uint32_t(&)[16]>((k & 1) ? va : vb));
+            else tmem_ld_32x32(o_addr + (k + 1) * CPS, reinterpret_cast<uint32_t(&)[32]>((k & 1) ? va : vb));
+          } else {
+            tc_fence_before_sync();
+            mbar_arrive(&out_empty[o]);
+          }
 #pragma unroll
-            for (int q = 0; q < 4; ++q) {
-              float zr[8];
-              if (p.add_residual) {
-                load8<F32>(xrow, c * 32 + q * 8, zr);
-              } else {
+          for (int q = 0; q < CPS / 8; ++q) {
+            float zr[8];
+            if (read_res && valid) {
+              load8<F32>(xrow, k * CPS + q * 8, zr);
+            } else {
 #pragma unroll
-                for (int e = 0; e < 8; ++e) zr[e] = 0.f;
-              }
+              for (int e = 0; e < 8; ++e) zr[e] = 0.f;
+            }
 #pragma unroll
-              for (int e = 0; e < 8; ++e) zr[e] += __uint_as_float(v[q * 8 + e]);
-              store8<F32>(orow, c * 32 + q * 8, zr);
+            for (int e = 0; e < 8; ++e) zr[e] = fmaf(2.0f, __uint_as_float(v[q * 8 + e]), zr[e]);
+            if (F32) {
+              *reinterpret_cast<float4*>(stage + row_off + (((q * 2) ^ row_xor) << 4)) = make_float4(zr[0], zr[1], zr[2], zr[3]);
+              *reinterpret_cast<float4*>(stage + row_off + (((q * 2 + 1) ^ row_xor) << 4)) =
+                  make_float4(zr[4], zr[5], zr[6], zr[7]);
+            } else {
+              *reinterpret_cast<uint4*>(stage + row_off + ((q ^ row_xor) << 4)) = make_uint4(
+                  pack_bf16x2(zr[0], zr[1]), pack_bf16x2(zr[2], zr[3]), pack_bf16x2(zr[4], zr[5]), pack_bf16x2(zr[6], zr[7]));
             }
           }
+          fence_proxy_async_smem();
+          named_bar_sync(1 + grp, 128);
+          if (leader) {
+            if (reduce)
+              tma_reduce_add_2d(&tmO, stage, k * CPS, tile * 128);
+            else
+              tma_store_2d(&tmO, stage, k * CPS, tile * 128);
+            tma_store_commit();
+          }
         }
-        tc_fence_before_sync();
-        mbar_arrive(&out_empty[o]);
       }
     }
+    if (r == 0) tma_store_wait0();
   }
 
   tc_fence_before_sync();
