@@ -11,11 +11,14 @@
 // factor 2 is applied to the output accumulator.  The output leaves through swizzled [128 rows][64 B] staging
 // tiles and TMA: added into x in place when the residual is wanted and out aliases x, stored otherwise.
 //
-//   warps 0-3   SwiGLU epilogue of even chunks + final store of even tiles
-//   warps 4-7   SwiGLU epilogue of odd chunks  + final store of odd tiles
-//   warps 8-15  producers: load rows, LayerNorm, write the GEMM1 A operand
-//   warp  16    MMA issuer
+//   warps 0-3   SwiGLU epilogue of even chunks
+//   warps 4-7   SwiGLU epilogue of odd chunks
+//   warps 8-15  producers: load rows, LayerNorm, write the GEMM1 A operand; they also send out the previous
+//               tile's output accumulator (warps 8-11 channels 0-63, warps 12-15 channels 64-127), so the
+//               SwiGLU groups never leave the chunk pipeline
+//   warp  16    GEMM1 issuer
 //   warp  17    TMA loader for the weight chunks
+//   warp  18    GEMM2 issuer
 #pragma once
 #include "row_tile.cuh"
 
@@ -42,11 +45,11 @@ constexpr uint32_t H_OFF = W3_OFF + 2 * kOperandHalf;    // 2 buffers x 16 KB (A
 constexpr uint32_t BAR_OFF = H_OFF + 2 * kOperandHalf;
 constexpr uint32_t STAGE_OFF = BAR_OFF + 1024;           // per epilogue group two 8 KB output tiles
 constexpr uint32_t SMEM_BYTES = STAGE_OFF + 4 * 8192 + 1024;
-constexpr int THREADS = 576;
+constexpr int THREADS = 608;
 }  // namespace transition
 
 template <bool F32>
-__global__ void __launch_bounds__(576, 1)
+__global__ void __launch_bounds__(608, 1)
 transition_kernel(const __grid_constant__ CUtensorMap tmW1, const __grid_constant__ CUtensorMap tmW3,
                   const __grid_constant__ CUtensorMap tmO, TransitionParams p) {
   using namespace transition;
@@ -83,7 +86,7 @@ transition_kernel(const __grid_constant__ CUtensorMap tmW1, const __grid_constan
       mbar_init(&h_full[i], 128);
       mbar_init(&h_empty[i], 1);
       mbar_init(&out_full[i], 1);
-      mbar_init(&out_empty[i], 128);
+      mbar_init(&out_empty[i], 256);
     }
     fence_mbar_init();
     prefetch_tmap(&tmW1);
@@ -117,10 +120,27 @@ transition_kernel(const __grid_constant__ CUtensorMap tmW1, const __grid_constan
       }
     }
   } else if (warp == 16) {
-    // ------------------------------------------------------------------ MMA issuer
+    // ------------------------------------------------------------------ GEMM1 issuer
     if (lane == 0) {
       constexpr uint32_t idesc = make_idesc_bf16(128, 128);
-      auto gemm2 = [&](int g) {  // consumes H[g&1] and the fc3 slice of chunk g
+      for (int g = 0; g < total_chunks; ++g) {
+        const int c = g & 7, b = g & 1, it = g >> 3, xs = it & 1;
+        if (c == 0) mbar_wait(&x_full[xs], (it >> 1) & 1, 35);
+        mbar_wait(&w1_full[b], (g >> 1) & 1, 36);
+        mbar_wait(&d1_empty[b], ((g >> 1) & 1) ^ 1, 37);
+        tc_fence_after_sync();
+        umma_k128(tmem_base + b * 128, smem_u32(smem + X_OFF + xs * kOperandTile),
+                  smem_u32(smem + W1_OFF + b * kOperandTile), idesc, false);
+        umma_commit(&w1_empty[b]);
+        umma_commit(&d1_full[b]);
+        if (c == 7) umma_commit(&x_empty[xs]);
+      }
+    }
+  } else if (warp == 18) {
+    // ------------------------------------------------------------------ GEMM2 issuer
+    if (lane == 0) {
+      constexpr uint32_t idesc = make_idesc_bf16(128, 128);
+      for (int g = 0; g < total_chunks; ++g) {  // consumes H[g&1] and the fc3 slice of chunk g
         const int c = g & 7, b = g & 1, o = (g >> 3) & 1;
         mbar_wait(&h_full[b], (g >> 1) & 1, 32);
         mbar_wait(&w3_full[b], (g >> 1) & 1, 33);
@@ -135,21 +155,7 @@ transition_kernel(const __grid_constant__ CUtensorMap tmW1, const __grid_constan
         umma_commit(&h_empty[b]);
         umma_commit(&w3_empty[b]);
         if (c == 7) umma_commit(&out_full[o]);
-      };
-      for (int g = 0; g < total_chunks; ++g) {
-        const int c = g & 7, b = g & 1, it = g >> 3, xs = it & 1;
-        if (c == 0) mbar_wait(&x_full[xs], (it >> 1) & 1, 35);
-        mbar_wait(&w1_full[b], (g >> 1) & 1, 36);
-        mbar_wait(&d1_empty[b], ((g >> 1) & 1) ^ 1, 37);
-        tc_fence_after_sync();
-        umma_k128(tmem_base + b * 128, smem_u32(smem + X_OFF + xs * kOperandTile),
-                  smem_u32(smem + W1_OFF + b * kOperandTile), idesc, false);
-        umma_commit(&w1_empty[b]);
-        umma_commit(&d1_full[b]);
-        if (c == 7) umma_commit(&x_empty[xs]);
-        if (g > 0) gemm2(g - 1);
       }
-      if (total_chunks > 0) gemm2(total_chunks - 1);
     }
   } else if (warp >= 8) {
     // ------------------------------------------------------------------ producers
@@ -167,6 +173,73 @@ transition_kernel(const __grid_constant__ CUtensorMap tmW1, const __grid_constan
       else
         regs.template load<F32, false>(pt, rp, gamma, beta, p.eps, 0.5f);
     };
+    // Output of tile number `ot` of this CTA (global tile index `otile`): CPS columns (64 B) at a time, the next
+    // TMEM load in flight, through this half-group's two staging tiles and TMA.
+    constexpr int CPS = F32 ? 16 : 32;
+    const int half = (warp - 8) >> 2;          // which 64 channels
+    const int quarter = warp & 3;
+    const int r = quarter * 32 + lane;         // pair row of the tile == TMEM lane
+    const bool leader = (pt & 127) == 0;
+    const bool reduce = p.add_residual && p.out == p.x;
+    const bool read_res = p.add_residual && !reduce;
+    const uint32_t row_off = r * 64, row_xor = (r >> 1) & 3;
+    auto store_out = [&](int ot, int otile) {
+      const int o = ot & 1;
+      mbar_wait(&out_full[o], (ot >> 1) & 1, 41);
+      tc_fence_after_sync();
+      const long long row = (long long)otile * 128 + r;
+      const bool valid = row < p.rows;
+      const uint8_t* xrow = static_cast<const uint8_t*>(p.x) + row * kD * zbytes<F32>();
+      const uint32_t o_addr = tmem_addr(tmem_base, quarter * 32, 256 + o * 128 + half * 64);
+      uint32_t va[CPS], vb[CPS];
+      if (F32) tmem_ld_32x16(o_addr, reinterpret_cast<uint32_t(&)[16]>(va));
+      else tmem_ld_32x32(o_addr, reinterpret_cast<uint32_t(&)[32]>(va));
+#pragma unroll
+      for (int k = 0; k < 64 / CPS; ++k) {
+        uint32_t(&v)[CPS] = (k & 1) ? vb : va;
+        uint8_t* stage = smem + STAGE_OFF + (half * 2 + (k & 1)) * 8192;
+        if (leader) tma_store_wait_read1();  // the store that last used this staging tile has read it
+        named_bar_sync(1 + half, 128);
+        tmem_ld_wait();
+        if (k + 1 < 64 / CPS) {
+          if (F32) tmem_ld_32x16(o_addr + (k + 1) * CPS, reinterpret_cast<uint32_t(&)[16]>((k & 1) ? va : vb));
+          else tmem_ld_32x32(o_addr + (k + 1) * CPS, reinterpret_cast<uint32_t(&)[32]>((k & 1) ? va : vb));
+        } else {
+          tc_fence_before_sync();
+          mbar_arrive(&out_empty[o]);
+        }
+        const int ch0 = half * 64 + k * CPS;
+#pragma unroll
+        for (int q = 0; q < CPS / 8; ++q) {
+          float zr[8];
+          if (read_res && valid) {
+            load8<F32>(xrow, ch0 + q * 8, zr);
+          } else {
+#pragma unroll
+            for (int e = 0; e < 8; ++e) zr[e] = 0.f;
+          }
+#pragma unroll
+          for (int e = 0; e < 8; ++e) zr[e] = fmaf(2.0f, __uint_as_float(v[q * 8 + e]), zr[e]);
+          if (F32) {
+            *reinterpret_cast<float4*>(stage + row_off + (((q * 2) ^ row_xor) << 4)) = make_float4(zr[0], zr[1], zr[2], zr[3]);
+            *reinterpret_cast<float4*>(stage + row_off + (((q * 2 + 1) ^ row_xor) << 4)) =
+                make_float4(zr[4], zr[5], zr[6], zr[7]);
+          } else {
+            *reinterpret_cast<uint4*>(stage + row_off + ((q ^ row_xor) << 4)) = make_uint4(
+                pack_bf16x2(zr[0], zr[1]), pack_bf16x2(zr[2], zr[3]), pack_bf16x2(zr[4], zr[5]), pack_bf16x2(zr[6], zr[7]));
+          }
+        }
+        fence_proxy_async_smem();
+        named_bar_sync(1 + half, 128);
+        if (leader) {
+          if (reduce)
+            tma_reduce_add_2d(&tmO, stage, ch0, otile * 128);
+          else
+            tma_store_2d(&tmO, stage, ch0, otile * 128);
+          tma_store_commit();
+        }
+      }
+    };
     int it = 0;
     int tile = blockIdx.x;
     if (tile < p.num_tiles) load_tile(tile);
@@ -178,9 +251,12 @@ transition_kernel(const __grid_constant__ CUtensorMap tmW1, const __grid_constan
       mbar_arrive(&x_full[s]);
       const int next = tile + gridDim.x;
       if (next < p.num_tiles) load_tile(next);
+      if (it > 0) store_out(it - 1, tile - gridDim.x);
     }
+    if (it > 0) store_out(it - 1, tile - gridDim.x);
+    if (leader) tma_store_wait0();
   } else {
-    // ------------------------------------------------------------------ SwiGLU + output epilogues
+    // ------------------------------------------------------------------ SwiGLU epilogues
     const int grp = warp >> 2;             // 0: even chunks / even tiles, 1: odd
     const int quarter = warp & 3;
     const int r = quarter * 32 + lane;     // pair row of the tile == TMEM lane
@@ -217,71 +293,7 @@ transition_kernel(const __grid_constant__ CUtensorMap tmW1, const __grid_constan
         mbar_arrive(&d1_empty[b]);
         mbar_arrive(&h_full[b]);
       }
-      if ((it & 1) == grp) {
-        // final store of the tile: CPS columns (64 B) at a time, the next TMEM load in flight, through the
-        // group's two staging tiles
-        constexpr int CPS = F32 ? 16 : 32;
-        const int o = it & 1;
-        const bool leader = r == 0;
-        const bool reduce = p.add_residual && p.out == p.x;
-        const bool read_res = p.add_residual && !reduce;
-        mbar_wait(&out_full[o], (it >> 1) & 1, 41);
-        tc_fence_after_sync();
-        const long long row = (long long)tile * 128 + r;
-        const bool valid = row < p.rows;
-        const uint8_t* xrow = static_cast<const uint8_t*>(p.x) + row * kD * zbytes<F32>();
-        const uint32_t o_addr = tmem_addr(tmem_base, quarter * 32, 256 + o * 128);
-        const uint32_t row_off = r * 64, row_xor = (r >> 1) & 3;
-        uint32_t va[CPS], vb[CPS];
-        if (F32) tmem_ld_32x16(o_addr, reinterpret_cast<uint32_t(&)[16]>(va));
-        else tmem_ld_32x32(o_addr, reinterpret_cast<uint32_t(&)[32]>(va));
-#pragma unroll
-        for (int k = 0; k < kD / CPS; ++k) {
-          uint32_t(&v)[CPS] = (k & 1) ? vb : va;
-          uint8_t* stage = smem + STAGE_OFF + (grp * 2 + (k & 1)) * 8192;
-          if (leader) tma_store_wait_read1();  // the store that last used this staging tile has read it
-          named_bar_sync(1 + grp, 128);
-          tmem_ld_wait();
-          if (k + 1 < kD / CPS) {
-            if (F32) tmem_ld_32x16(o_addr + (k + 1) * CPS, reinterpret_cast<uint32_t(&)[16]>((k & 1) ? va : vb));
-            else tmem_ld_32x32(o_addr + (k + 1) * CPS, reinterpret_cast<uint32_t(&)[32]>((k & 1) ? va : vb));
-          } else {
-            tc_fence_before_sync();
-            mbar_arrive(&out_empty[o]);
-          }
-#pragma unroll
-          for (int q = 0; q < CPS / 8; ++q) {
-            float zr[8];
-            if (read_res && valid) {
-              load8<F32>(xrow, k * CPS + q * 8, zr);
-            } else {
-#pragma unroll
-              for (int e = 0; e < 8; ++e) zr[e] = 0.f;
-            }
-#pragma unroll
-            for (int e = 0; e < 8; ++e) zr[e] = fmaf(2.0f, __uint_as_float(v[q * 8 + e]), zr[e]);
-            if (F32) {
-              *reinterpret_cast<float4*>(stage + row_off + (((q * 2) ^ row_xor) << 4)) = make_float4(zr[0], zr[1], zr[2], zr[3]);
-              *reinterpret_cast<float4*>(stage + row_off + (((q * 2 + 1) ^ row_xor) << 4)) =
-                  make_float4(zr[4], zr[5], zr[6], zr[7]);
-            } else {
-              *reinterpret_cast<uint4*>(stage + row_off + ((q ^ row_xor) << 4)) = make_uint4(
-                  pack_bf16x2(zr[0], zr[1]), pack_bf16x2(zr[2], zr[3]), pack_bf16x2(zr[4], zr[5]), pack_bf16x2(zr[6], zr[7]));
-            }
-          }
-          fence_proxy_async_smem();
-          named_bar_sync(1 + grp, 128);
-          if (leader) {
-            if (reduce)
-              tma_reduce_add_2d(&tmO, stage, k * CPS, tile * 128);
-            else
-              tma_store_2d(&tmO, stage, k * CPS, tile * 128);
-            tma_store_commit();
-          }
-        }
-      }
     }
-    if (r == 0) tma_store_wait0();
   }
 
   tc_fence_before_sync();
