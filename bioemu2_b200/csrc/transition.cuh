@@ -17,8 +17,9 @@
 //               tile's output accumulator (warps 8-11 channels 0-63, warps 12-15 channels 64-127), so the
 //               SwiGLU groups never leave the chunk pipeline
 //   warp  16    GEMM1 issuer
-//   warp  17    TMA loader for the weight chunks
+//   warp  17    TMA loader for the [fc1|fc2] chunks
 //   warp  18    GEMM2 issuer
+//   warp  19    TMA loader for the fc3 slices
 #pragma once
 #include "row_tile.cuh"
 
@@ -38,49 +39,52 @@ struct TransitionParams {
 
 namespace transition {
 constexpr int CHUNKS = 8;  // hidden 512 = 8 x 64
-constexpr uint32_t X_OFF = 0;                            // 2 stages x 32 KB (A of GEMM1)
-constexpr uint32_t W1_OFF = X_OFF + 2 * kOperandTile;    // 2 stages x 32 KB ([fc1|fc2] chunk, 128 rows x 128 K)
-constexpr uint32_t W3_OFF = W1_OFF + 2 * kOperandTile;   // 2 stages x 16 KB (fc3 slice, 128 rows x 64 K)
-constexpr uint32_t H_OFF = W3_OFF + 2 * kOperandHalf;    // 2 buffers x 16 KB (A of GEMM2, 128 rows x 64 K)
+constexpr int WS = 3;      // weight chunk stages: the chunk loads come from L2 and need two chunk times to land
+constexpr uint32_t X_OFF = 0;                            // 32 KB (A of GEMM1)
+constexpr uint32_t W1_OFF = X_OFF + kOperandTile;        // WS stages x 32 KB ([fc1|fc2] chunk, 128 rows x 128 K)
+constexpr uint32_t W3_OFF = W1_OFF + WS * kOperandTile;  // WS stages x 16 KB (fc3 slice, 128 rows x 64 K)
+constexpr uint32_t H_OFF = W3_OFF + WS * kOperandHalf;   // 2 buffers x 16 KB (A of GEMM2, 128 rows x 64 K)
 constexpr uint32_t BAR_OFF = H_OFF + 2 * kOperandHalf;
-constexpr uint32_t STAGE_OFF = BAR_OFF + 1024;           // per epilogue group two 8 KB output tiles
-constexpr uint32_t SMEM_BYTES = STAGE_OFF + 4 * 8192 + 1024;
-constexpr int THREADS = 608;
+constexpr uint32_t STAGE_OFF = BAR_OFF + 1024;           // per output half-group one 8 KB output tile
+constexpr uint32_t SMEM_BYTES = STAGE_OFF + 2 * 8192 + 1024;
+constexpr int THREADS = 640;
 }  // namespace transition
 
 template <bool F32>
-__global__ void __launch_bounds__(608, 1)
+__global__ void __launch_bounds__(640, 1)
 transition_kernel(const __grid_constant__ CUtensorMap tmW1, const __grid_constant__ CUtensorMap tmW3,
                   const __grid_constant__ CUtensorMap tmO, TransitionParams p) {
   using namespace transition;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem + BAR_OFF);
-  uint64_t* x_full = bars;            // [2] count 128
-  uint64_t* x_empty = bars + 2;       // [2] count 1 (commit)
-  uint64_t* w1_full = bars + 4;       // [2] TMA
-  uint64_t* w1_empty = bars + 6;      // [2] commit
-  uint64_t* w3_full = bars + 8;       // [2] TMA
-  uint64_t* w3_empty = bars + 10;     // [2] commit
-  uint64_t* d1_full = bars + 12;      // [2] commit
-  uint64_t* d1_empty = bars + 14;     // [2] count 128
-  uint64_t* h_full = bars + 16;       // [2] count 128
-  uint64_t* h_empty = bars + 18;      // [2] commit
-  uint64_t* out_full = bars + 20;     // [2] commit
-  uint64_t* out_empty = bars + 22;    // [2] count 128
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 24);
+  uint64_t* x_full = bars;            // count 256
+  uint64_t* x_empty = bars + 1;       // commit
+  uint64_t* w1_full = bars + 2;       // [WS] TMA
+  uint64_t* w1_empty = bars + 5;      // [WS] commit
+  uint64_t* w3_full = bars + 8;       // [WS] TMA
+  uint64_t* w3_empty = bars + 11;     // [WS] commit
+  uint64_t* d1_full = bars + 14;      // [2] commit
+  uint64_t* d1_empty = bars + 16;     // [2] count 128
+  uint64_t* h_full = bars + 18;       // [2] count 128
+  uint64_t* h_empty = bars + 20;      // [2] commit
+  uint64_t* out_full = bars + 22;     // [2] commit
+  uint64_t* out_empty = bars + 24;    // [2] count 256
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 26);
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
 
   if (threadIdx.x == 0) {
-    for (int i = 0; i < 2; ++i) {
-      mbar_init(&x_full[i], 256);
-      mbar_init(&x_empty[i], 1);
+    mbar_init(x_full, 256);
+    mbar_init(x_empty, 1);
+    for (int i = 0; i < WS; ++i) {
       mbar_init(&w1_full[i], 1);
       mbar_init(&w1_empty[i], 1);
       mbar_init(&w3_full[i], 1);
       mbar_init(&w3_empty[i], 1);
+    }
+    for (int i = 0; i < 2; ++i) {
       mbar_init(&d1_full[i], 1);
       mbar_init(&d1_empty[i], 128);
       mbar_init(&h_full[i], 128);
@@ -103,18 +107,26 @@ transition_kernel(const __grid_constant__ CUtensorMap tmW1, const __grid_constan
   int my_tiles = 0;
   for (int tile = blockIdx.x; tile < p.num_tiles; tile += gridDim.x) ++my_tiles;
   const int total_chunks = my_tiles * CHUNKS;
-  // A global chunk counter g = it*8 + c drives every ring of depth 2: stage g&1, use index g>>1.
+  // A global chunk counter g = it*8 + c drives the rings: depth 2 (stage g&1, use g>>1) for the TMEM and H
+  // buffers, depth WS (stage g%WS, use g/WS) for the weight chunks.
 
   if (warp == 17) {
-    // ------------------------------------------------------------------ weight loader (TMA)
+    // ------------------------------------------------------------------ [fc1|fc2] chunk loader (TMA)
     if (lane == 0) {
       for (int g = 0; g < total_chunks; ++g) {
-        const int c = g & 7, s = g & 1;
-        mbar_wait(&w1_empty[s], ((g >> 1) & 1) ^ 1, 30);
+        const int c = g & 7, s = g % WS;
+        mbar_wait(&w1_empty[s], ((g / WS) & 1) ^ 1, 30);
         mbar_arrive_expect_tx(&w1_full[s], kOperandTile);
         tma_load_2d(smem + W1_OFF + s * kOperandTile, &tmW1, &w1_full[s], 0, c * 128);
         tma_load_2d(smem + W1_OFF + s * kOperandTile + kOperandHalf, &tmW1, &w1_full[s], 64, c * 128);
-        mbar_wait(&w3_empty[s], ((g >> 1) & 1) ^ 1, 31);
+      }
+    }
+  } else if (warp == 19) {
+    // ------------------------------------------------------------------ fc3 slice loader (TMA)
+    if (lane == 0) {
+      for (int g = 0; g < total_chunks; ++g) {
+        const int c = g & 7, s = g % WS;
+        mbar_wait(&w3_empty[s], ((g / WS) & 1) ^ 1, 31);
         mbar_arrive_expect_tx(&w3_full[s], kOperandHalf);
         tma_load_2d(smem + W3_OFF + s * kOperandHalf, &tmW3, &w3_full[s], c * 64, 0);
       }
@@ -124,16 +136,15 @@ transition_kernel(const __grid_constant__ CUtensorMap tmW1, const __grid_constan
     if (lane == 0) {
       constexpr uint32_t idesc = make_idesc_bf16(128, 128);
       for (int g = 0; g < total_chunks; ++g) {
-        const int c = g & 7, b = g & 1, it = g >> 3, xs = it & 1;
-        if (c == 0) mbar_wait(&x_full[xs], (it >> 1) & 1, 35);
-        mbar_wait(&w1_full[b], (g >> 1) & 1, 36);
+        const int c = g & 7, b = g & 1, it = g >> 3, ws = g % WS;
+        if (c == 0) mbar_wait(x_full, it & 1, 35);
+        mbar_wait(&w1_full[ws], (g / WS) & 1, 36);
         mbar_wait(&d1_empty[b], ((g >> 1) & 1) ^ 1, 37);
         tc_fence_after_sync();
-        umma_k128(tmem_base + b * 128, smem_u32(smem + X_OFF + xs * kOperandTile),
-                  smem_u32(smem + W1_OFF + b * kOperandTile), idesc, false);
-        umma_commit(&w1_empty[b]);
+        umma_k128(tmem_base + b * 128, smem_u32(smem + X_OFF), smem_u32(smem + W1_OFF + ws * kOperandTile), idesc, false);
+        umma_commit(&w1_empty[ws]);
         umma_commit(&d1_full[b]);
-        if (c == 7) umma_commit(&x_empty[xs]);
+        if (c == 7) umma_commit(x_empty);
       }
     }
   } else if (warp == 18) {
@@ -141,19 +152,19 @@ transition_kernel(const __grid_constant__ CUtensorMap tmW1, const __grid_constan
     if (lane == 0) {
       constexpr uint32_t idesc = make_idesc_bf16(128, 128);
       for (int g = 0; g < total_chunks; ++g) {  // consumes H[g&1] and the fc3 slice of chunk g
-        const int c = g & 7, b = g & 1, o = (g >> 3) & 1;
+        const int c = g & 7, b = g & 1, o = (g >> 3) & 1, ws = g % WS;
         mbar_wait(&h_full[b], (g >> 1) & 1, 32);
-        mbar_wait(&w3_full[b], (g >> 1) & 1, 33);
+        mbar_wait(&w3_full[ws], (g / WS) & 1, 33);
         if (c == 0) mbar_wait(&out_empty[o], (((g >> 3) >> 1) & 1) ^ 1, 34);
         tc_fence_after_sync();
         const uint32_t h_s = smem_u32(smem + H_OFF + b * kOperandHalf);
-        const uint32_t w3_s = smem_u32(smem + W3_OFF + b * kOperandHalf);
+        const uint32_t w3_s = smem_u32(smem + W3_OFF + ws * kOperandHalf);
 #pragma unroll
         for (int k = 0; k < 4; ++k)
           umma_bf16_ss(tmem_base + 256 + o * 128, make_desc_k_sw128(h_s + k * 32), make_desc_k_sw128(w3_s + k * 32),
                        idesc, (c | k) != 0);
         umma_commit(&h_empty[b]);
-        umma_commit(&w3_empty[b]);
+        umma_commit(&w3_empty[ws]);
         if (c == 7) umma_commit(&out_full[o]);
       }
     }
@@ -174,7 +185,7 @@ transition_kernel(const __grid_constant__ CUtensorMap tmW1, const __grid_constan
         regs.template load<F32, false>(pt, rp, gamma, beta, p.eps, 0.5f);
     };
     // Output of tile number `ot` of this CTA (global tile index `otile`): CPS columns (64 B) at a time, the next
-    // TMEM load in flight, through this half-group's two staging tiles and TMA.
+    // TMEM load in flight, through this half-group's staging tile and TMA.
     constexpr int CPS = F32 ? 16 : 32;
     const int half = (warp - 8) >> 2;          // which 64 channels
     const int quarter = warp & 3;
@@ -197,8 +208,8 @@ transition_kernel(const __grid_constant__ CUtensorMap tmW1, const __grid_constan
 #pragma unroll
       for (int k = 0; k < 64 / CPS; ++k) {
         uint32_t(&v)[CPS] = (k & 1) ? vb : va;
-        uint8_t* stage = smem + STAGE_OFF + (half * 2 + (k & 1)) * 8192;
-        if (leader) tma_store_wait_read1();  // the store that last used this staging tile has read it
+        uint8_t* stage = smem + STAGE_OFF + half * 8192;
+        if (leader) tma_store_wait_read0();  // the previous store has read the staging tile
         named_bar_sync(1 + half, 128);
         tmem_ld_wait();
         if (k + 1 < 64 / CPS) {
@@ -244,11 +255,10 @@ transition_kernel(const __grid_constant__ CUtensorMap tmW1, const __grid_constan
     int tile = blockIdx.x;
     if (tile < p.num_tiles) load_tile(tile);
     for (; tile < p.num_tiles; tile += gridDim.x, ++it) {
-      const int s = it & 1;
-      mbar_wait(&x_empty[s], ((it >> 1) & 1) ^ 1, 38);
-      regs.store_operand(pt, smem + X_OFF + s * kOperandTile);
+      mbar_wait(x_empty, (it & 1) ^ 1, 38);
+      regs.store_operand(pt, smem + X_OFF);
       fence_proxy_async_smem();
-      mbar_arrive(&x_full[s]);
+      mbar_arrive(x_full);
       const int next = tile + gridDim.x;
       if (next < p.num_tiles) load_tile(next);
       if (it > 0) store_out(it - 1, tile - gridDim.x);
