@@ -72,9 +72,7 @@ __device__ __forceinline__ uint64_t make_desc_k(uint32_t addr, bool sw64) {
 }
 
 __device__ __forceinline__ float max8(const float* v, float m) {
-  const float a = fmaxf(fmaxf(v[0], v[1]), fmaxf(v[2], v[3]));
-  const float b = fmaxf(fmaxf(v[4], v[5]), fmaxf(v[6], v[7]));
-  return fmaxf(m, fmaxf(a, b));
+  return max3(max3(v[0], v[1], v[2]), max3(v[3], v[4], v[5]), max3(v[6], v[7], m));
 }
 
 template <int DH, int G>
