@@ -8,15 +8,19 @@
 // Q and the bias arrive pre-multiplied by log2(e) (Q also by 1/sqrt(dh)), so the kernel works in base 2.
 //
 // One work item = (batch b, head h, G consecutive tiles of 128 queries); a persistent CTA walks work items.
-// G "softmax groups" of four warps each own one query tile and share the K / V^T tiles of the item:
-//   softmax warps  one thread per query row; S tile from TMEM, bias tile from shared memory (TMA, 128-byte
-//                  swizzle), online max/sum in registers, P written as a bf16 MMA operand; the output
-//                  accumulator lives in registers and takes each key tile's P.V from TMEM.  Two groups
-//                  put two warps on every scheduler, which is what hides the TMEM / shared-memory / ex2
-//                  latencies of the one-thread-per-row softmax.
+// G "softmax groups" of eight warps each own one query tile and share the K / V^T tiles of the item:
+//   softmax warps  two threads per query row (one per 64-column half of a score tile), so a thread holds its
+//                  whole share of a score tile in registers: one TMEM read per key tile, online max/sum (row
+//                  maximum exchanged through shared memory once per key tile), P written back to TMEM as
+//                  packed bf16; the output accumulator lives in registers (half the head dim per thread) and
+//                  takes each key tile's P.V from TMEM.  Two groups put four softmax warps on every scheduler.
 //   loader warp    TMA: Q tiles once per item (two slots, so the next item's arrive early), K and V^T through a
 //                  ring, one bias tile per group
-//   MMA warp       S_g = Q_g.K^T into one of the group's two TMEM score buffers, alternating per key tile, so
+//   MMA warp       S_g = Q_g.K^T + bias tile into one of the group's two TMEM score buffers (the bias is added by
+//                  the tensor core: eight 128 x 16 x 16 products of the bias tile's 16-column blocks, as the A
+//                  operand, with a 16 x 16 identity, each onto its own 16 accumulator columns, so the softmax
+//                  threads never touch the bias); O_g = P_g.V with P read from TMEM, where the softmax threads leave it
+//                  (packed bf16, in the first 64 columns of the score buffer it was computed from), alternating per key tile, so
 //                  the next scores are ready when a softmax pass ends; P_g.V lands in the first DH columns of
 //                  the score buffer its P came from (dead by then).  The tile stream runs on across work
 //                  items: the first scores of the next item are issued during the last tile of this one.
@@ -57,12 +61,14 @@ struct FlashCfg {
   static constexpr uint32_t KV_BYTES = K_BYTES + V_BYTES;
   static constexpr uint32_t Q_OFF = 0;                   // [2 slots][G] query tiles
   static constexpr uint32_t KV_OFF = 2 * G * Q_BYTES;
-  static constexpr uint32_t BIAS_OFF = KV_OFF + STAGES * KV_BYTES;   // G tiles x 32 KB
-  static constexpr uint32_t P_OFF = BIAS_OFF + G * kOperandTile;     // G tiles x 32 KB
-  static constexpr uint32_t MASK_OFF = P_OFF + G * kOperandTile;     // 2 x MAX_T x 8 words
-  static constexpr uint32_t BAR_OFF = MASK_OFF + 2 * MAX_T * 32;
+  static constexpr uint32_t BIAS_OFF = KV_OFF + STAGES * KV_BYTES;   // [G][2 slots] tiles x 32 KB
+  static constexpr uint32_t MASK_OFF = BIAS_OFF + 2 * G * kOperandTile;  // 2 x MAX_T x 8 words
+  static constexpr uint32_t XCH_OFF = MASK_OFF + 2 * MAX_T * 32;  // per group 768 floats: row max / row sum exchange
+  // 16 x 16 identity (bf16) as an unswizzled K-major operand: two 16-byte K chunks of 16 rows each.
+  static constexpr uint32_t IDENT_OFF = XCH_OFF + G * 3072;
+  static constexpr uint32_t BAR_OFF = IDENT_OFF + 512;
   static constexpr uint32_t SMEM_BYTES = BAR_OFF + 384 + 1024;
-  static constexpr int THREADS = 128 * G + 128;        // G softmax warpgroups + one for loader / MMA (2 idle warps)
+  static constexpr int THREADS = 256 * G + 128;        // G softmax groups of 8 warps + loader / MMA / mask (+1 idle) warps
   static constexpr int SOFTMAX_REGS = 0;  // setmaxnreg targets when three warpgroups share the file
   static constexpr int OTHER_REGS = 40;
 };
@@ -76,7 +82,7 @@ __device__ __forceinline__ float max8(const float* v, float m) {
 }
 
 template <int DH, int G>
-__global__ void __launch_bounds__(128 * G + 128, 1)
+__global__ void __launch_bounds__(256 * G + 128, 1)
 flash_core_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
                   const __grid_constant__ CUtensorMap tmV, const __grid_constant__ CUtensorMap tmBias,
                   FlashParams p) {
@@ -90,16 +96,15 @@ flash_core_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
   uint64_t* q_empty = bars + 2;       // [2] commit
   uint64_t* kv_full = bars + 4;       // [3] TMA
   uint64_t* kv_empty = bars + 7;      // [3] commit
-  uint64_t* bias_full = bars + 10;    // [G] TMA
-  uint64_t* bias_empty = bars + 12;   // [G] count 128
-  uint64_t* s_full = bars + 14;       // [G][2 buffers] commit
-  uint64_t* s_empty = bars + 18;      // [G][2] count 128: the P.V result in the buffer has been read
-  uint64_t* p_full = bars + 22;       // [G] count 128
-  uint64_t* p_empty = bars + 24;      // [G] commit
-  uint64_t* o_full = bars + 26;       // [G][2] commit
-  uint64_t* mask_full = bars + 30;    // [2] count 1 (mask warp)
-  uint64_t* mask_empty = bars + 32;   // [2] count 128*G
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 34);
+  uint64_t* bias_full = bars + 10;    // [G][2 slots] TMA
+  uint64_t* bias_empty = bars + 14;   // [G][2] commit
+  uint64_t* s_full = bars + 18;       // [G][2 buffers] commit
+  uint64_t* s_empty = bars + 22;      // [G][2] count 256: the P.V result in the buffer has been read
+  uint64_t* p_full = bars + 26;       // [G] count 256
+  uint64_t* o_full = bars + 28;       // [G][2] commit
+  uint64_t* mask_full = bars + 32;    // [2] count 1 (mask warp)
+  uint64_t* mask_empty = bars + 34;   // [2] count 256*G
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 36);
   // Key-validity bits of a work item's mask row, two buffers of MAX_T x 8 words:
   //   word t*8 + w      bit j <=> key t*128 + 32*w + j exists and is unmasked
   //   word t*8 + 4 + w  bit j <=> key t*128 + 32*w + j exists
@@ -107,8 +112,8 @@ flash_core_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
-  constexpr int kLoaderWarp = 4 * G;
-  constexpr int kMmaWarp = 4 * G + 1;
+  constexpr int kLoaderWarp = 8 * G;
+  constexpr int kMmaWarp = 8 * G + 1;
 
   if (threadIdx.x == 0) {
     for (int i = 0; i < 3; ++i) {
@@ -118,16 +123,15 @@ flash_core_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
     for (int i = 0; i < 2; ++i) {
       mbar_init(&q_full[i], 1);
       mbar_init(&q_empty[i], 1);
-      mbar_init(&bias_full[i], 1);
-      mbar_init(&bias_empty[i], 128);
-      mbar_init(&p_full[i], 128);
-      mbar_init(&p_empty[i], 1);
+      mbar_init(&p_full[i], 256);
       mbar_init(&mask_full[i], 1);
-      mbar_init(&mask_empty[i], 128 * G);
+      mbar_init(&mask_empty[i], 256 * G);
     }
     for (int i = 0; i < 4; ++i) {
+      mbar_init(&bias_full[i], 1);
+      mbar_init(&bias_empty[i], 1);
       mbar_init(&s_full[i], 1);
-      mbar_init(&s_empty[i], 128);
+      mbar_init(&s_empty[i], 256);
       mbar_init(&o_full[i], 1);
     }
     fence_mbar_init();
@@ -136,12 +140,20 @@ flash_core_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
     prefetch_tmap(&tmV);
     prefetch_tmap(&tmBias);
   }
+  if (threadIdx.x < 32) {  // identity: 16-byte unit u = (K chunk c, row i) holds K indices 8c .. 8c+7 of row i
+    const int c = threadIdx.x >> 4, i = threadIdx.x & 15;
+    uint32_t wds[4] = {0, 0, 0, 0};
+    if ((i >> 3) == c) wds[(i & 7) >> 1] = (i & 1) ? 0x3F800000u : 0x00003F80u;
+    *reinterpret_cast<uint4*>(smem + Cfg::IDENT_OFF + c * 256 + i * 16) = make_uint4(wds[0], wds[1], wds[2], wds[3]);
+  }
+  fence_proxy_async_smem();
   if (warp == kMmaWarp) tmem_alloc(tmem_slot, 512);
   tc_fence_before_sync();
   __syncthreads();
   tc_fence_after_sync();
   const uint32_t tmem_base = *tmem_slot;
-  // TMEM columns: score buffer pb of group g at g*256 + pb*128; its first DH columns later take P.V.
+  // TMEM columns: score buffer pb of group g at g*256 + pb*128; its first 64 columns later take P (packed bf16),
+  // columns 64 .. 64+DH the P.V product.
 
   const int T = p.nkt;
   // n counts key tiles over all work items of this CTA: every per-tile barrier completes one phase per n
@@ -177,11 +189,12 @@ flash_core_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
           tma_load_3d(base + Cfg::K_BYTES, &tmV, &kv_full[st], t * 128, p.v_row0 + h * DH, b);
           tma_load_3d(base + Cfg::K_BYTES + Cfg::V_HALF, &tmV, &kv_full[st], t * 128 + 64, p.v_row0 + h * DH, b);
           for (int g = 0; g < G; ++g) {
-            mbar_wait(&bias_empty[g], (n & 1) ^ 1, 72);
-            uint8_t* bb = smem + Cfg::BIAS_OFF + g * kOperandTile;
-            mbar_arrive_expect_tx(&bias_full[g], kOperandTile);
-            tma_load_3d(bb, &tmBias, &bias_full[g], t * 128, (qg * G + g) * 128, bias_g);
-            tma_load_3d(bb + kOperandHalf, &tmBias, &bias_full[g], t * 128 + 64, (qg * G + g) * 128, bias_g);
+            const int bs = g * 2 + (n & 1);
+            mbar_wait(&bias_empty[bs], ((n >> 1) & 1) ^ 1, 72);
+            uint8_t* bb = smem + Cfg::BIAS_OFF + bs * kOperandTile;
+            mbar_arrive_expect_tx(&bias_full[bs], kOperandTile);
+            tma_load_3d(bb, &tmBias, &bias_full[bs], t * 128, (qg * G + g) * 128, bias_g);
+            tma_load_3d(bb + kOperandHalf, &tmBias, &bias_full[bs], t * 128 + 64, (qg * G + g) * 128, bias_g);
           }
         }
       }
@@ -191,22 +204,35 @@ flash_core_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
     if (lane == 0) {
       constexpr uint32_t idesc_s = make_idesc_bf16(128, 128);
       constexpr uint32_t idesc_o = make_idesc_bf16(128, DH);
-      // The groups run half a tile out of phase (group 1 starts late, see the softmax code), so that one is
-      // in its ex2-bound second pass while the other does the ALU-bound first pass.  The requests of one
-      // group are therefore served together: its next score tile, then its P.V.
+      constexpr uint32_t idesc_b = make_idesc_bf16(128, 16);
+      // The groups run half a tile out of phase (group 1 starts late, see the softmax code).  The requests of
+      // one group are served together: its next score tile, then its P.V.  (One issuing thread per group was
+      // measured slower.)  The operand descriptors are stepped by adding to their low words, which keeps this
+      // thread's instruction count per MMA small: it shares its scheduler with four busy softmax warps.
+      const uint32_t smem_base = smem_u32(smem);
+      const uint32_t z_lo = desc_lo(smem_base + Cfg::IDENT_OFF, 256);
       auto issue_s = [&](int n, int g, int qs) {  // S_g(n) = Q_g . K(n)^T into score buffer n & 1
         const int st = n % Cfg::STAGES;
         const int pb = n & 1;
         mbar_wait(&kv_full[st], (n / Cfg::STAGES) & 1, 62);
         mbar_wait(&s_empty[g * 2 + pb], ((n >> 1) & 1) ^ 1, 63);
         tc_fence_after_sync();
-        const uint32_t k_s = smem_u32(smem + Cfg::KV_OFF + st * Cfg::KV_BYTES);
-        const uint32_t q_s = smem_u32(smem + Cfg::Q_OFF + (qs * G + g) * Cfg::Q_BYTES);
+        const uint32_t k_lo = desc_lo(smem_base + Cfg::KV_OFF + st * Cfg::KV_BYTES);
+        const uint32_t q_lo = desc_lo(smem_base + Cfg::Q_OFF + (qs * G + g) * Cfg::Q_BYTES);
+        constexpr uint32_t qk_hi = SW64 ? kDescHiSw64 : kDescHiSw128;
 #pragma unroll
         for (int k = 0; k < DH / 16; ++k)
-          umma_bf16_ss(tmem_base + g * 256 + pb * 128, make_desc_k(q_s + k * 32, SW64), make_desc_k(k_s + k * 32, SW64),
-                       idesc_s, k > 0);
+          umma_bf16_ss2(tmem_base + g * 256 + pb * 128, q_lo + 2 * k, qk_hi, k_lo + 2 * k, qk_hi, idesc_s, k > 0);
+        // + bias tile: K step k adds bias[:, 16k .. 16k+15] into the same columns of the accumulator
+        mbar_wait(&bias_full[g * 2 + pb], (n >> 1) & 1, 68);
+        tc_fence_after_sync();
+        const uint32_t b_lo = desc_lo(smem_base + Cfg::BIAS_OFF + (g * 2 + pb) * kOperandTile);
+#pragma unroll
+        for (int k = 0; k < 8; ++k)  // 128 x 16 x 16: bias columns 16k.. times the 16 x 16 identity, onto the same columns
+          umma_bf16_ss2(tmem_base + g * 256 + pb * 128 + 16 * k, b_lo + (k >> 2) * (kOperandHalf >> 4) + (k & 3) * 2,
+                        kDescHiSw128, z_lo, desc_hi_noswizzle(128), idesc_b, true);
         umma_commit(&s_full[g * 2 + pb]);
+        umma_commit(&bias_empty[g * 2 + pb]);
       };
       int n = 0, w = 0;
       if ((int)blockIdx.x < p.total_work) {
@@ -218,7 +244,7 @@ flash_core_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
         const bool more = work + (int)gridDim.x < p.total_work;
         for (int t = 0; t < T; ++t, ++n) {
           const int st = n % Cfg::STAGES;
-          const uint32_t v_s = smem_u32(smem + Cfg::KV_OFF + st * Cfg::KV_BYTES + Cfg::K_BYTES);
+          const uint32_t v_lo = desc_lo(smem_base + Cfg::KV_OFF + st * Cfg::KV_BYTES + Cfg::K_BYTES);
           for (int g = 0; g < G; ++g) {
             // next score tile of this group: of this item, or the first one of the next item
             if (t + 1 < T) {
@@ -231,14 +257,12 @@ flash_core_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
             }
             mbar_wait(&p_full[g], n & 1, 65);
             tc_fence_after_sync();
-            const uint32_t p_s = smem_u32(smem + Cfg::P_OFF + g * kOperandTile);
+            const uint32_t buf = tmem_base + g * 256 + (n & 1) * 128;
 #pragma unroll
-            for (int k = 0; k < 8; ++k)
-              umma_bf16_ss(tmem_base + g * 256 + (n & 1) * 128,
-                           make_desc_k_sw128(p_s + (k >> 2) * kOperandHalf + (k & 3) * 32),
-                           make_desc_k_sw128(v_s + (k >> 2) * Cfg::V_HALF + (k & 3) * 32), idesc_o, k > 0);
+            for (int k = 0; k < 8; ++k)  // A = P from TMEM: 16 keys = 8 packed columns per K step
+              umma_bf16_ts2(buf + 64, buf + k * 8, v_lo + (k >> 2) * (Cfg::V_HALF >> 4) + (k & 3) * 2, kDescHiSw128, idesc_o,
+                            k > 0);
             umma_commit(&o_full[g * 2 + (n & 1)]);
-            umma_commit(&p_empty[g]);
           }
           umma_commit(&kv_empty[st]);
         }

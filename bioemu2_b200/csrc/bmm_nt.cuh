@@ -126,11 +126,10 @@ bmm_nt_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ C
           tc_fence_after_sync();
           const uint32_t sa = smem_u32(smem + stage * Cfg::STAGE_BYTES);
           const uint32_t sb = sa + Cfg::A_BYTES;
+          const uint32_t a_lo = desc_lo(sa), b_lo = desc_lo(sb);
 #pragma unroll
-          for (int k = 0; k < 4; ++k) {
-            umma_bf16_ss(d_tmem, make_desc_k_sw128(sa + k * 32), make_desc_k_sw128(sb + k * 32), idesc,
-                         (kb | k) != 0);
-          }
+          for (int k = 0; k < 4; ++k)
+            umma_bf16_ss2(d_tmem, a_lo + 2 * k, kDescHiSw128, b_lo + 2 * k, kDescHiSw128, idesc, (kb | k) != 0);
           umma_commit(&empty[stage]);
           if (++stage == Cfg::STAGES) {
             stage = 0;

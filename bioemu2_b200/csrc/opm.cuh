@@ -88,10 +88,10 @@ opm_proj_kernel(const __grid_constant__ CUtensorMap tmW, OpmProjParams p) {
         mbar_wait(&acc_empty[s], ((it >> 1) & 1) ^ 1, 52);
         tc_fence_after_sync();
         const uint32_t x_s = smem_u32(smem + X_OFF + s * kOperandHalf);
+        const uint32_t x_lo = desc_lo(x_s), w_lo = desc_lo(w_s);
 #pragma unroll
         for (int k = 0; k < 4; ++k)
-          umma_bf16_ss(tmem_base + s * 64, make_desc_k_sw128(x_s + k * 32), make_desc_k_sw128(w_s + k * 32), idesc,
-                       k > 0);
+          umma_bf16_ss2(tmem_base + s * 64, x_lo + 2 * k, kDescHiSw128, w_lo + 2 * k, kDescHiSw128, idesc, k > 0);
         umma_commit(&x_empty[s]);
         umma_commit(&acc_full[s]);
       }

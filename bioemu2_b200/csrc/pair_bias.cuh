@@ -79,10 +79,11 @@ pair_bias_kernel(const __grid_constant__ CUtensorMap tmW, PairBiasParams p) {
         mbar_wait(&acc_empty[s], ((it >> 1) & 1) ^ 1, 82);
         tc_fence_after_sync();
         const uint32_t x_s = smem_u32(smem + X_OFF + s * kOperandTile);
+        const uint32_t x_lo = desc_lo(x_s), w_lo = desc_lo(w_s);
 #pragma unroll
         for (int k = 0; k < 8; ++k)
-          umma_bf16_ss(tmem_base + s * 16, make_desc_k_sw128(x_s + (k >> 2) * kOperandHalf + (k & 3) * 32),
-                       make_desc_k_sw128(w_s + (k >> 2) * 2048 + (k & 3) * 32), idesc, k > 0);
+          umma_bf16_ss2(tmem_base + s * 16, x_lo + (k >> 2) * (kOperandHalf >> 4) + (k & 3) * 2, kDescHiSw128,
+                        w_lo + (k >> 2) * (2048 >> 4) + (k & 3) * 2, kDescHiSw128, idesc, k > 0);
         umma_commit(&x_empty[s]);
         umma_commit(&acc_full[s]);
       }

@@ -165,11 +165,11 @@ __device__ __forceinline__ void load_gamma_beta(const float* w, const float* b, 
 // Issue the 8 K-steps of a 128 x N x 128 product: A and B operand tiles are 128-swizzled halves.
 __device__ __forceinline__ void umma_k128(uint32_t d_tmem, uint32_t a_smem, uint32_t b_smem, uint32_t idesc,
                                           bool accumulate_first) {
+  const uint32_t a_lo = desc_lo(a_smem), b_lo = desc_lo(b_smem);  // one add per operand per step in the loop
 #pragma unroll
   for (int k = 0; k < 8; ++k) {
-    const uint32_t off = (k >> 2) * kOperandHalf + (k & 3) * 32;
-    umma_bf16_ss(d_tmem, make_desc_k_sw128(a_smem + off), make_desc_k_sw128(b_smem + off), idesc,
-                 (accumulate_first || k > 0) ? 1u : 0u);
+    const uint32_t off = (k >> 2) * (kOperandHalf >> 4) + (k & 3) * 2;
+    umma_bf16_ss2(d_tmem, a_lo + off, kDescHiSw128, b_lo + off, kDescHiSw128, idesc, (accumulate_first || k > 0) ? 1u : 0u);
   }
 }
 

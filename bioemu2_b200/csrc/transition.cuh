@@ -159,10 +159,10 @@ transition_kernel(const __grid_constant__ CUtensorMap tmW1, const __grid_constan
         tc_fence_after_sync();
         const uint32_t h_s = smem_u32(smem + H_OFF + b * kOperandHalf);
         const uint32_t w3_s = smem_u32(smem + W3_OFF + ws * kOperandHalf);
+        const uint32_t h_lo = desc_lo(h_s), w3_lo = desc_lo(w3_s);
 #pragma unroll
         for (int k = 0; k < 4; ++k)
-          umma_bf16_ss(tmem_base + 256 + o * 128, make_desc_k_sw128(h_s + k * 32), make_desc_k_sw128(w3_s + k * 32),
-                       idesc, (c | k) != 0);
+          umma_bf16_ss2(tmem_base + 256 + o * 128, h_lo + 2 * k, kDescHiSw128, w3_lo + 2 * k, kDescHiSw128, idesc, (c | k) != 0);
         umma_commit(&h_empty[b]);
         umma_commit(&w3_empty[ws]);
         if (c == 7) umma_commit(&out_full[o]);
