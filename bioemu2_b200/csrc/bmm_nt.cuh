@@ -31,8 +31,9 @@ struct BmmParams {
   // (line < remap_m) is stored as row pos * remap_m + line.
   const void* residual;
   int remap_n, remap_m;
-  // Bulk output (fp32 C only): the scaled (+ bias) tile leaves through 16 KB staging tiles and the C tensor
-  // map, 1 = stored, 2 = added into C (the residual is C itself, which the epilogue then never reads).
+  // Bulk output: the scaled (+ bias) tile leaves through 16 KB staging tiles ([128 rows][128 B]: 32 fp32 or 64
+  // bf16 columns) and the C tensor map, 1 = stored, 2 = added into C (the residual is C itself, which the
+  // epilogue then never reads).
   int tma_c;
 };
 
@@ -45,7 +46,7 @@ struct BmmCfg {
   static constexpr uint32_t B_BYTES = BN * BK * 2;
   static constexpr uint32_t STAGE_BYTES = A_BYTES + B_BYTES;
   static constexpr uint32_t BAR_OFFSET = STAGES * STAGE_BYTES;
-  static constexpr uint32_t OUT_OFFSET = BAR_OFFSET + 1024;        // two [128 rows][32 fp32] tiles for bulk output
+  static constexpr uint32_t OUT_OFFSET = BAR_OFFSET + 1024;        // two [128 rows][128 B] tiles for bulk output
   static constexpr uint32_t SMEM_BYTES = OUT_OFFSET + 2 * 16384 + 1024;  // + alignment slack
   static constexpr int THREADS = 192;
 };
@@ -161,14 +162,18 @@ bmm_nt_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ C
           c1 = (tm * 128) / p.remap_n;
           c2 = tm * 128 - c1 * p.remap_n;
         }
+        const int cps = p.out_f32 ? 1 : 2;  // 32-column chunks per staging tile
         uint32_t va[32], vb[32];
         tmem_ld_32x32(tmem_addr(tmem_base, quarter * 32, acc * BN), va);
 #pragma unroll
         for (int c = 0; c < BN / 32; ++c) {
           uint32_t(&v)[32] = (c & 1) ? vb : va;
-          uint8_t* stage = smem + Cfg::OUT_OFFSET + (c & 1) * 16384;
-          if (leader) tma_store_wait_read1();  // the store that last used this staging tile has read it
-          named_bar_sync(1, 128);
+          const int st = p.out_f32 ? c : (c >> 1);  // staging tile number within the output tile
+          uint8_t* stage = smem + Cfg::OUT_OFFSET + (st & 1) * 16384;
+          if (p.out_f32 || (c & 1) == 0) {
+            if (leader) tma_store_wait_read1();  // the store that last used this staging tile has read it
+            named_bar_sync(1, 128);
+          }
           tmem_ld_wait();
           if (c + 1 < BN / 32) {
             tmem_ld_32x32(tmem_addr(tmem_base, quarter * 32, acc * BN + (c + 1) * 32), (c & 1) ? va : vb);
@@ -177,27 +182,45 @@ bmm_nt_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ C
             mbar_arrive(&acc_empty[acc]);
           }
           const int col0 = tn * BN + c * 32;
+          if (p.out_f32) {
 #pragma unroll
-          for (int g = 0; g < 8; ++g) {
-            float4 x;
-            x.x = __uint_as_float(v[g * 4 + 0]) * scale;
-            x.y = __uint_as_float(v[g * 4 + 1]) * scale;
-            x.z = __uint_as_float(v[g * 4 + 2]) * scale;
-            x.w = __uint_as_float(v[g * 4 + 3]) * scale;
-            if (p.bias) {
-              const float4 bv = *reinterpret_cast<const float4*>(p.bias + col0 + g * 4);
-              x.x += bv.x; x.y += bv.y; x.z += bv.z; x.w += bv.w;
+            for (int g = 0; g < 8; ++g) {
+              float4 x;
+              x.x = __uint_as_float(v[g * 4 + 0]) * scale;
+              x.y = __uint_as_float(v[g * 4 + 1]) * scale;
+              x.z = __uint_as_float(v[g * 4 + 2]) * scale;
+              x.w = __uint_as_float(v[g * 4 + 3]) * scale;
+              if (p.bias) {
+                const float4 bv = *reinterpret_cast<const float4*>(p.bias + col0 + g * 4);
+                x.x += bv.x; x.y += bv.y; x.z += bv.z; x.w += bv.w;
+              }
+              *reinterpret_cast<float4*>(stage + sw128_offset(r, g)) = x;
             }
-            *reinterpret_cast<float4*>(stage + sw128_offset(r, g)) = x;
+          } else {
+#pragma unroll
+            for (int g = 0; g < 4; ++g) {
+              float x[8];
+#pragma unroll
+              for (int e = 0; e < 8; ++e) x[e] = __uint_as_float(v[g * 8 + e]) * scale;
+              if (p.bias) {
+#pragma unroll
+                for (int e = 0; e < 8; ++e) x[e] += p.bias[col0 + g * 8 + e];
+              }
+              *reinterpret_cast<uint4*>(stage + sw128_offset(r, (c & 1) * 4 + g)) = make_uint4(
+                  pack_bf16x2(x[0], x[1]), pack_bf16x2(x[2], x[3]), pack_bf16x2(x[4], x[5]), pack_bf16x2(x[6], x[7]));
+            }
           }
-          fence_proxy_async_smem();
-          named_bar_sync(1, 128);
-          if (leader && col0 < p.n_valid) {
-            if (p.tma_c == 2)
-              tma_reduce_add_3d(&tmC, stage, col0, c1, c2);
-            else
-              tma_store_3d(&tmC, stage, col0, c1, c2);
-            tma_store_commit();
+          if (p.out_f32 || (c & 1) == 1) {
+            const int tcol0 = tn * BN + st * 32 * cps;
+            fence_proxy_async_smem();
+            named_bar_sync(1, 128);
+            if (leader && tcol0 < p.n_valid) {
+              if (p.tma_c == 2)
+                tma_reduce_add_3d(&tmC, stage, tcol0, c1, c2);
+              else
+                tma_store_3d(&tmC, stage, tcol0, c1, c2);
+              tma_store_commit();
+            }
           }
         }
         continue;

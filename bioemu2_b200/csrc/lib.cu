@@ -71,28 +71,31 @@ static int launch_bmm(const BmmLaunch& a, cudaStream_t stream) {
   p.residual = a.residual;
   p.remap_n = a.remap_n;
   p.remap_m = a.remap_m > 0 ? a.remap_m : a.remap_n;
-  // Bulk output through the C tensor map where the layout allows it: fp32 C, whole 32-column groups, the
+  // Bulk output through the C tensor map where the layout allows it: whole 128-byte column groups, the
   // residual (if any) being C itself, and for the transposed pair store lines that are whole row tiles.
   p.tma_c = 0;
   CUtensorMap tmC = tmA;
   const int64_t c_batch = a.sc > 0 ? a.sc : a.ldc * int64_t(a.M);
-  if (a.out_f32 && a.opm_ntok == 0 && a.N % 32 == 0 && a.ldc % 4 == 0 && c_batch % 4 == 0 && aligned(a.C, 16) &&
+  const int c_esz = a.out_f32 ? 4 : 2;
+  const int c_cols = 128 / c_esz;  // columns of one staging tile
+  if (a.opm_ntok == 0 && a.N % c_cols == 0 && (a.ldc * c_esz) % 16 == 0 && (c_batch * c_esz) % 16 == 0 && aligned(a.C, 16) &&
       (a.residual == nullptr || a.residual == a.C) && (a.bias == nullptr || aligned(a.bias, 16)) &&
       (a.remap_n == 0 || (a.remap_n % 128 == 0 && a.batch == 1 && a.M == a.remap_n * p.remap_m))) {
     uint64_t dims[3], str[2];
     uint32_t box[3];
     dims[0] = uint64_t(a.N);
-    box[0] = 32;
+    box[0] = uint32_t(c_cols);
     if (a.remap_n > 0) {  // {column, line, pos}: pair (line, pos) lives in row pos * remap_m + line
       dims[1] = uint64_t(p.remap_m), dims[2] = uint64_t(a.remap_n);
-      str[0] = uint64_t(a.ldc) * 4, str[1] = uint64_t(a.ldc) * 4 * uint64_t(p.remap_m);
+      str[0] = uint64_t(a.ldc) * c_esz, str[1] = uint64_t(a.ldc) * c_esz * uint64_t(p.remap_m);
       box[1] = 1, box[2] = 128;
     } else {
       dims[1] = uint64_t(a.M), dims[2] = uint64_t(a.batch);
-      str[0] = uint64_t(a.ldc) * 4, str[1] = uint64_t(c_batch) * 4;
+      str[0] = uint64_t(a.ldc) * c_esz, str[1] = uint64_t(c_batch) * c_esz;
       box[1] = 128, box[2] = 1;
     }
-    if (int e = make_tmap(&tmC, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, a.C, 3, dims, str, box, CU_TENSOR_MAP_SWIZZLE_128B))
+    if (int e = make_tmap(&tmC, a.out_f32 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, a.C, 3, dims,
+                          str, box, CU_TENSOR_MAP_SWIZZLE_128B))
       return e;
     p.tma_c = a.residual ? 2 : 1;
   }
