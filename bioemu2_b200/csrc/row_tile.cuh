@@ -68,7 +68,8 @@ struct RowTile {
   uint4 v[RPT];
 
   // row_ptr(r) -> address of channel 0 of tile row r (elements of the z stream), or nullptr if absent.
-  // LS: rows normalised in lock step (8 where the kernel has registers to spare, fewer otherwise).
+  // LS: rows normalised in lock step by the one-pass packed form (8 where the kernel has registers to spare);
+  // LS = 1 selects the register-tight two-pass form.
   template <bool F32, bool NORM, int LS = 8, class RowPtr>
   __device__ __forceinline__ void load(int pt, RowPtr row_ptr, const float (&gamma)[8], const float (&beta)[8],
                                        float eps, float raw_scale = 1.0f) {
@@ -87,45 +88,73 @@ struct RowTile {
           for (int i = 0; i < 8; ++i) x[q][i] = 0.f;
         }
       }
-      if (NORM) {
-        // LS rows at a time go through the two 16-lane reductions in lock step, so each shuffle step is LS
-        // independent exchanges instead of a serial chain per row.
+      if (NORM && LS == 1) {
+        // Register-tight form for kernels compiled at 96 registers: rows one after the other, two-pass variance.
+#pragma unroll
+        for (int q = 0; q < 8; ++q) {
+          float sm = 0.f;
+#pragma unroll
+          for (int i = 0; i < 8; ++i) sm += x[q][i];
+          const float mean = group16_sum(sm) * (1.0f / kD);
+          float ss = 0.f;
+#pragma unroll
+          for (int i = 0; i < 8; ++i) {
+            x[q][i] -= mean;
+            ss = fmaf(x[q][i], x[q][i], ss);
+          }
+          const float rstd = rsqrtf(group16_sum(ss) * (1.0f / kD) + eps);
+#pragma unroll
+          for (int i = 0; i < 8; ++i) x[q][i] = fmaf(x[q][i] * rstd, gamma[i], beta[i]);
+          v[q0 + q] = make_uint4(pack_bf16x2(x[q][0], x[q][1]), pack_bf16x2(x[q][2], x[q][3]),
+                                 pack_bf16x2(x[q][4], x[q][5]), pack_bf16x2(x[q][6], x[q][7]));
+        }
+      } else if (NORM) {
+        // One pass: row sum and sum of squares together (packed fp32x2 arithmetic, one 16-lane butterfly for the
+        // pair), then y = x * (rstd * gamma) + (beta - mean * rstd * gamma).  LS rows go through the butterfly
+        // in lock step.  (Sum of squares minus squared mean in fp32: the relative error of the variance is
+        // about 1e-7 * (1 + mean^2 / var), far below bf16 resolution for any realistic row.)
 #pragma unroll
         for (int qb = 0; qb < 8; qb += LS) {
-          float s[LS];
+          float s1[LS], s2[LS];
 #pragma unroll
           for (int q = 0; q < LS; ++q) {
-            s[q] = 0.f;
-#pragma unroll
-            for (int i = 0; i < 8; ++i) s[q] += x[qb + q][i];
+            const float* xr = x[qb + q];
+            float a0 = xr[0], a1 = xr[1], b0, b1;
+            add_f32x2(a0, a1, xr[2], xr[3]);
+            add_f32x2(a0, a1, xr[4], xr[5]);
+            add_f32x2(a0, a1, xr[6], xr[7]);
+            mul_f32x2(b0 = xr[0], b1 = xr[1], xr[0], xr[1]);
+            fma_f32x2(b0, b1, xr[2], xr[3], xr[2], xr[3], b0, b1);
+            fma_f32x2(b0, b1, xr[4], xr[5], xr[4], xr[5], b0, b1);
+            fma_f32x2(b0, b1, xr[6], xr[7], xr[6], xr[7], b0, b1);
+            s1[q] = a0 + a1;
+            s2[q] = b0 + b1;
           }
 #pragma unroll
           for (int off = 8; off > 0; off >>= 1) {
 #pragma unroll
-            for (int q = 0; q < LS; ++q) s[q] += __shfl_xor_sync(0xffffffffu, s[q], off);
-          }
-#pragma unroll
-          for (int q = 0; q < LS; ++q) {
-            const float mean = s[q] * (1.0f / kD);
-            s[q] = 0.f;
-#pragma unroll
-            for (int i = 0; i < 8; ++i) {
-              x[qb + q][i] -= mean;
-              s[q] = fmaf(x[qb + q][i], x[qb + q][i], s[q]);
+            for (int q = 0; q < LS; ++q) {
+              const float o1 = __shfl_xor_sync(0xffffffffu, s1[q], off);
+              const float o2 = __shfl_xor_sync(0xffffffffu, s2[q], off);
+              add_f32x2(s1[q], s2[q], o1, o2);
             }
           }
 #pragma unroll
-          for (int off = 8; off > 0; off >>= 1) {
-#pragma unroll
-            for (int q = 0; q < LS; ++q) s[q] += __shfl_xor_sync(0xffffffffu, s[q], off);
-          }
-#pragma unroll
           for (int q = 0; q < LS; ++q) {
-            const float rstd = rsqrtf(s[q] * (1.0f / kD) + eps);
+            float* xr = x[qb + q];
+            const float mean = s1[q] * (1.0f / kD);
+            const float var = fmaxf(fmaf(-mean, mean, s2[q] * (1.0f / kD)), 0.f);
+            const float rstd = rsqrtf(var + eps);
+            const float nmr = -mean * rstd;
 #pragma unroll
-            for (int i = 0; i < 8; ++i) x[qb + q][i] = fmaf(x[qb + q][i] * rstd, gamma[i], beta[i]);
-            v[q0 + qb + q] = make_uint4(pack_bf16x2(x[qb + q][0], x[qb + q][1]), pack_bf16x2(x[qb + q][2], x[qb + q][3]),
-                                        pack_bf16x2(x[qb + q][4], x[qb + q][5]), pack_bf16x2(x[qb + q][6], x[qb + q][7]));
+            for (int i = 0; i < 8; i += 2) {
+              float g0 = gamma[i], g1 = gamma[i + 1], b0, b1;
+              fma_f32x2(b0, b1, g0, g1, nmr, nmr, beta[i], beta[i + 1]);  // beta - mean * rstd * gamma
+              mul_f32x2(g0, g1, rstd, rstd);                              // rstd * gamma
+              fma_f32x2(xr[i], xr[i + 1], xr[i], xr[i + 1], g0, g1, b0, b1);
+            }
+            v[q0 + qb + q] = make_uint4(pack_bf16x2(xr[0], xr[1]), pack_bf16x2(xr[2], xr[3]), pack_bf16x2(xr[4], xr[5]),
+                                        pack_bf16x2(xr[6], xr[7]));
           }
         }
       } else {  // no LayerNorm: the rows are only scaled by raw_scale (a power of two keeps them exact)
