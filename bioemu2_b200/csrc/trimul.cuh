@@ -43,13 +43,17 @@ constexpr uint32_t BAR_OFF = MASK_OFF + 4 * 128;
 constexpr uint32_t FLAG_OFF = BAR_OFF + 96;          // 4 stages x 4 "every pair of this quarter valid" bytes
 constexpr uint32_t STAGE_OFF = MASK_OFF + 1024;      // per epilogue group a 16 KB tile [128 channels][64 pairs]
 constexpr uint32_t SMEM_BYTES = STAGE_OFF + 2 * kOperandHalf + 1024;
-constexpr int THREADS = 544;  // warps 0-3 epilogue of a, 4-7 epilogue of b, 8-15 producers, 16 control
+constexpr int THREADS = 512;  // warps 0-3 epilogue of a, 4-7 epilogue of b (their first threads issue the MMAs), 8-15 producers
 }  // namespace trimul_in
 
 // The LayerNorm output is halved (exactly) before the projections, so the accumulators hold p/2 and g/2
 // and the gate is p * sigmoid(g) = p/2 + p/2 * tanh(g/2): one MUFU and one FMA per element.
+// 512 threads, not 544: a 17th warp would round the register allocation up to 640 threads and cap every
+// thread at 96 registers, which the LayerNorm producers spill at.  So there is no control warp: the first
+// thread of each epilogue group issues the two products of its own half (whose accumulators it has just
+// drained), and shared stage x is released when both have committed.
 template <bool F32>
-__global__ void __launch_bounds__(544, 1)
+__global__ void __launch_bounds__(512, 1)
 trimul_in_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUtensorMap tmA,
                  const __grid_constant__ CUtensorMap tmB, TriMulInParams p) {
   using namespace trimul_in;
@@ -72,7 +76,7 @@ trimul_in_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant_
     mbar_init(w_full, 1);
     for (int i = 0; i < 2; ++i) {
       mbar_init(&x_full[i], 256);
-      mbar_init(&x_empty[i], 1);
+      mbar_init(&x_empty[i], 2);
       mbar_init(&acc_full[i], 1);
       mbar_init(&acc_empty[i], 128);
     }
@@ -81,41 +85,13 @@ trimul_in_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant_
     prefetch_tmap(&tmA);
     prefetch_tmap(&tmB);
   }
-  if (warp == 16) tmem_alloc(tmem_slot, 512);
+  if (warp == 0) tmem_alloc(tmem_slot, 512);
   tc_fence_before_sync();
   __syncthreads();
   tc_fence_after_sync();
   const uint32_t tmem_base = *tmem_slot;
 
-  if (warp == 16) {
-    // ------------------------------------------------------------------ control
-    if (lane == 0) {
-      mbar_arrive_expect_tx(w_full, 4 * kOperandTile);
-      for (int mt = 0; mt < 4; ++mt)
-        for (int h = 0; h < 2; ++h)
-          tma_load_2d(smem + W_OFF + mt * kOperandTile + h * kOperandHalf, &tmW, w_full, h * 64, mt * 128);
-      mbar_wait(w_full, 0, 10);
-      constexpr uint32_t idesc = make_idesc_bf16(128, 128);
-      const uint32_t w_s = smem_u32(smem + W_OFF);
-      int it = 0;
-      for (int tile = blockIdx.x; tile < p.num_tiles; tile += gridDim.x, ++it) {
-        const int s = it & 1;
-        mbar_wait(&x_full[s], (it >> 1) & 1, 11);
-        tc_fence_after_sync();
-        const uint32_t x_s = smem_u32(smem + X_OFF + s * kOperandTile);
-        for (int half = 0; half < 2; ++half) {
-          mbar_wait(&acc_empty[half], (it & 1) ^ 1, 12);
-          tc_fence_after_sync();
-          for (int m2 = 0; m2 < 2; ++m2) {
-            const int mt = half * 2 + m2;
-            umma_k128(tmem_base + mt * 128, w_s + mt * kOperandTile, x_s, idesc, false);
-          }
-          umma_commit(&acc_full[half]);
-        }
-        umma_commit(&x_empty[s]);
-      }
-    }
-  } else if (warp >= 8) {
+  if (warp >= 8) {
     // ------------------------------------------------------------------ producers
     const int pt = threadIdx.x - 256;  // 0..255
     float gamma[8], beta[8];
@@ -128,7 +104,7 @@ trimul_in_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant_
       const int line = tile / tiles_per_line;
       const int pos0 = (tile - line * tiles_per_line) << 7;
       const uint8_t* base = static_cast<const uint8_t*>(p.z) + line * line_stride;
-      regs.template load<F32, true, 1>(
+      regs.template load<F32, true, 8>(
           pt,
           [&](int r) -> const void* {
             const int pos = pos0 + r;
@@ -169,11 +145,37 @@ trimul_in_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant_
     const CUtensorMap* tmOut = half ? &tmB : &tmA;
     const uint32_t p_addr = tmem_addr(tmem_base, (warp & 3) * 32, (half * 2) * 128);
     const uint32_t g_addr = p_addr + 128;
+    const bool issuer = (threadIdx.x & 127) == 0;  // first thread of the group
+    constexpr uint32_t idesc = make_idesc_bf16(128, 128);
+    const uint32_t w_s = smem_u32(smem + W_OFF);
+    if (issuer) {
+      if (half == 0) {
+        mbar_arrive_expect_tx(w_full, 4 * kOperandTile);
+        for (int mt = 0; mt < 4; ++mt)
+          for (int h = 0; h < 2; ++h)
+            tma_load_2d(smem + W_OFF + mt * kOperandTile + h * kOperandHalf, &tmW, w_full, h * 64, mt * 128);
+      }
+      mbar_wait(w_full, 0, 10);
+    }
     int it = 0;
     for (int tile = blockIdx.x; tile < p.num_tiles; tile += gridDim.x, ++it) {
       const int line = tile / tiles_per_line;
       const int pos0 = (tile - line * tiles_per_line) << 7;
       const uint32_t* msk = reinterpret_cast<const uint32_t*>(mask_s + (it & 3) * 128);
+      if (issuer) {  // this half's products for the tile: p and g projections against operand stage it & 1
+        const int s = it & 1;
+        mbar_wait(&x_full[s], (it >> 1) & 1, 11);
+        mbar_wait(&acc_empty[half], (it & 1) ^ 1, 12);  // the whole group has drained the previous tile
+        tc_fence_after_sync();
+        const uint32_t x_s = smem_u32(smem + X_OFF + s * kOperandTile);
+        for (int m2 = 0; m2 < 2; ++m2) {
+          const int mt = half * 2 + m2;
+          umma_k128(tmem_base + mt * 128, w_s + mt * kOperandTile, x_s, idesc, false);
+        }
+        umma_commit(&acc_full[half]);
+        umma_commit(&x_empty[s]);
+      }
+      __syncwarp();
       mbar_wait(&acc_full[half], it & 1, 14);
       tc_fence_after_sync();
       // every pair of the tile unmasked?  (tiles away from the padding are, and then no select is needed)
@@ -228,7 +230,7 @@ trimul_in_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant_
 
   tc_fence_before_sync();
   __syncthreads();
-  if (warp == 16) {
+  if (warp == 0) {
     __syncwarp();
     tmem_dealloc(tmem_base, 512);
   }
