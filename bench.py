@@ -427,7 +427,11 @@ def run_b200(args) -> None:
                           "launched alone on N rows x 4 heads x 32",
                 "bound": "tensor", "achieved": ach, "peak": pk["bf16_tflops"], "unit": "TFLOP/s",
                 "frac": ach / pk["bf16_tflops"], "peak_source": pk["source"] + " burst (kernel timed alone)",
-                "algorithmic_flops_per_launch": core_flops, "ms_per_launch": t["attention_core"], "traffic": None,
+                "algorithmic_flops_per_launch": core_flops, "ms_per_launch": t["attention_core"],
+                # dram__bytes_read.sum + dram__bytes_write.sum of one launch at N=512 (ncu capture summarised in
+                # profiles/flash_core_triatt_n512.md); the operands scale with N^2, so other sizes are scaled from it
+                "traffic": 323.5e6 * (N / 512.0) ** 2,
+                "traffic_source": "ncu capture at N=512 (271.1 MB read + 52.4 MB written), scaled by (N/512)^2",
                 "note": "head dim 32 makes the core ex2-bound, not tensor-bound: N^3*4 exponentials at 16/clk/SM "
                         f"take {ex2_floor_ms:.3f} ms at the sampled clock; the tensor work alone would take "
                         f"{core_flops / (pk['bf16_tflops'] * 1e12) * 1e3:.3f} ms" if ex2_floor_ms else "",
