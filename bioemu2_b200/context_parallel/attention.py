@@ -99,15 +99,43 @@ def cp_triangle_attention_(z_loc: Tensor, mask_loc: Tensor, tri_packed, grid: CP
         raise ValueError("blocks must tile a square pair tensor: pad the token axis to shard_multiple(R, C)")
     tb_loc = local.tri_bias(z_loc, tri_packed, ending)
     bias_full = _assemble_bias(grid.all_gather(tb_loc, grid.group), grid, n, ending)
+    # A line (a row for the starting node, a column for the ending node) needs its whole length, which is spread
+    # over the row (column) group.  The group splits its lines evenly: two all-to-alls move each rank's share of
+    # whole lines in and the updates back out, so the attention work per rank is 1 / (R * C) of the total.  When
+    # the lines do not divide by the group size every rank of the group computes all of them (all-gather form).
     if not ending:
-        slab = torch.cat(grid.all_gather(z_loc, grid.row_group), dim=1)          # [n_r, N, 128]
-        mslab = torch.cat(grid.all_gather(mask_loc, grid.row_group), dim=1)
+        g, gs = grid.row_group, grid.cols
+        if gs > 1 and n_r % gs == 0:
+            share = n_r // gs
+
+            def lines_in(x):  # [n_r, n_c, ...] -> this rank's lines at full length [share, N, ...]
+                got = grid.all_to_all(x.reshape(gs, share, *x.shape[1:]).contiguous(), g)   # [src c, share, n_c, ...]
+                return got.transpose(0, 1).reshape(share, gs * n_c, *x.shape[2:]).contiguous()
+
+            upd = local.tri_slab(lines_in(z_loc), lines_in(mask_loc), bias_full, tri_packed, False)  # [share, N, 128]
+            back = grid.all_to_all(upd.reshape(share, gs, n_c, upd.shape[-1]).transpose(0, 1).contiguous(), g)
+            z_loc += back.reshape(n_r, n_c, upd.shape[-1])
+            return z_loc
+        slab = torch.cat(grid.all_gather(z_loc, g), dim=1)          # [n_r, N, 128]
+        mslab = torch.cat(grid.all_gather(mask_loc, g), dim=1)
         upd = local.tri_slab(slab, mslab, bias_full, tri_packed, False)
         c0, c1 = grid.coords.my_cols(n)
         z_loc += upd[:, c0:c1]
     else:
-        slab = torch.cat(grid.all_gather(z_loc, grid.col_group), dim=0)          # [N, n_c, 128]
-        mslab = torch.cat(grid.all_gather(mask_loc, grid.col_group), dim=0)
+        g, gs = grid.col_group, grid.rows
+        if gs > 1 and n_c % gs == 0:
+            share = n_c // gs
+
+            def lines_in(x):  # [n_r, n_c, ...] -> this rank's columns at full height [N, share, ...]
+                send = x.reshape(n_r, gs, share, *x.shape[2:]).transpose(0, 1).contiguous()   # [dst r, n_r, share, ...]
+                return grid.all_to_all(send, g).reshape(gs * n_r, share, *x.shape[2:])
+
+            upd = local.tri_slab(lines_in(z_loc), lines_in(mask_loc), bias_full, tri_packed, True)   # [N, share, 128]
+            back = grid.all_to_all(upd.reshape(gs, n_r, share, upd.shape[-1]).contiguous(), g)      # [src r, n_r, share, 128]
+            z_loc += back.transpose(0, 1).reshape(n_r, n_c, upd.shape[-1])
+            return z_loc
+        slab = torch.cat(grid.all_gather(z_loc, g), dim=0)          # [N, n_c, 128]
+        mslab = torch.cat(grid.all_gather(mask_loc, g), dim=0)
         upd = local.tri_slab(slab, mslab, bias_full, tri_packed, True)
         r0, r1 = grid.coords.my_rows(n)
         z_loc += upd[r0:r1]

@@ -123,6 +123,21 @@ class CPGrid:
         dist.reduce_scatter_tensor(out.view(-1), chunks.view(-1), group=group)
         return out
 
+    @staticmethod
+    def all_to_all(x: Tensor, group) -> Tensor:
+        """``x[g, ...]`` (contiguous, ``g`` = group size): chunk ``i`` goes to group rank ``i``; returns the chunks
+        received, in group-rank order."""
+        n = dist.get_world_size(group)
+        if n == 1:
+            return x
+        assert x.shape[0] == n and x.is_contiguous()
+        if dist.get_backend(group) == "gloo":  # gloo has no all-to-all: gather everything and keep what is addressed here
+            me = dist.get_rank(group)
+            return torch.stack([t[me] for t in CPGrid.all_gather(x, group)])
+        out = torch.empty_like(x)
+        dist.all_to_all_single(out, x, group=group)
+        return out
+
     # ------------------------------------------------------------------ host-side sharding helpers (tests, setup)
     def shard_pair(self, z: Tensor) -> Tensor:
         """This rank's block of a full pair tensor ``z[B, N, N, ...]`` (N already padded)."""
