@@ -264,11 +264,11 @@ constexpr uint32_t LN_OFF = A2_OFF + kOperandTile;     // gamma_out[128], beta_o
 constexpr uint32_t BAR_OFF = LN_OFF + 1024;
 constexpr uint32_t STAGE_OFF = LN_OFF + 2048;          // 2 x 16 KB output tiles [128 pairs][128 B of channels]
 constexpr uint32_t SMEM_BYTES = STAGE_OFF + 2 * kOperandHalf + 1024;
-constexpr int THREADS = 544;  // warps 0-3 epilogue, 4-7 t transformers, 8-15 z producers, 16 control
+constexpr int THREADS = 512;  // warps 0-3 epilogue (thread 0 also issues the TMA loads and MMAs), 4-7 t transformers, 8-15 z producers
 }  // namespace trimul_out
 
 template <bool F32>
-__global__ void __launch_bounds__(544, 1)
+__global__ void __launch_bounds__(512, 1)
 trimul_out_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUtensorMap tmT,
                   const __grid_constant__ CUtensorMap tmO, TriMulOutParams p) {
   using namespace trimul_out;
@@ -309,54 +309,13 @@ trimul_out_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant
     ln_s[threadIdx.x] = p.ln_out_w[threadIdx.x];
     ln_s[128 + threadIdx.x] = p.ln_out_b[threadIdx.x];
   }
-  if (warp == 16) tmem_alloc(tmem_slot, 512);
+  if (warp == 0) tmem_alloc(tmem_slot, 512);
   tc_fence_before_sync();
   __syncthreads();
   tc_fence_after_sync();
   const uint32_t tmem_base = *tmem_slot;
 
-  if (warp == 16) {
-    // ------------------------------------------------------------------ control: TMA + MMA
-    if (lane == 0) {
-      mbar_arrive_expect_tx(w_full, 2 * kOperandTile);
-      for (int mt = 0; mt < 2; ++mt)
-        for (int h = 0; h < 2; ++h)
-          tma_load_2d(smem + W_OFF + mt * kOperandTile + h * kOperandHalf, &tmW, w_full, h * 64, mt * 128);
-      auto issue_t = [&](int tile, int s) {
-        const int line = tile / tiles_per_line;
-        const int pos0 = (tile - line * tiles_per_line) << 7;
-        mbar_arrive_expect_tx(&t_full[s], kOperandTile);
-        tma_load_3d(smem + T_OFF + s * kOperandTile, &tmT, &t_full[s], pos0, line, 0);
-      };
-      // prologue: first two t tiles in flight
-      int tile = blockIdx.x;
-      if (tile < p.num_tiles) issue_t(tile, 0);
-      if (tile + (int)gridDim.x < p.num_tiles) issue_t(tile + gridDim.x, 1);
-      mbar_wait(w_full, 0, 20);
-      constexpr uint32_t idesc = make_idesc_bf16(128, 128);
-      const uint32_t w_s = smem_u32(smem + W_OFF);
-      const uint32_t a1_s = smem_u32(smem + A1_OFF);
-      const uint32_t a2_s = smem_u32(smem + A2_OFF);
-      int it = 0;
-      for (; tile < p.num_tiles; tile += gridDim.x, ++it) {
-        const int acc = it & 1;
-        mbar_wait(&acc_empty[acc], ((it >> 1) & 1) ^ 1, 21);
-        mbar_wait(a1_full, it & 1, 22);
-        mbar_wait(a2_full, it & 1, 23);
-        tc_fence_after_sync();
-        umma_k128(tmem_base + acc * 256, a1_s, w_s, idesc, false);                       // p_out(LN_out(t))
-        umma_k128(tmem_base + acc * 256 + 128, a2_s, w_s + kOperandTile, idesc, false);  // g_out(LN_in(z))
-        umma_commit(a_empty);
-        umma_commit(&acc_full[acc]);
-        // refill the raw-t stage this tile used, once the transformers have released it
-        const int next2 = tile + 2 * gridDim.x;
-        if (next2 < p.num_tiles) {
-          mbar_wait(&t_empty[it & 1], (it >> 1) & 1, 24);
-          issue_t(next2, it & 1);
-        }
-      }
-    }
-  } else if (warp >= 4 && warp < 8) {
+  if (warp >= 4 && warp < 8) {
     // ------------------------------------------------------------------ t transformers
     // thread j owns pair column j of the raw tile [d][j]; LayerNorm over d, written as row j of A1.
     const int j = threadIdx.x - 128;
@@ -405,7 +364,7 @@ trimul_out_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant
       const int line = tile / tiles_per_line;
       const int pos0 = (tile - line * tiles_per_line) << 7;
       const uint8_t* base = static_cast<const uint8_t*>(p.z) + line * p.z_line_stride + pos0 * p.z_pos_stride;
-      regs.template load<F32, true, 1>(
+      regs.template load<F32, true, 8>(
           pt,
           [&](int r) -> const void* { return (pos0 + r) < p.n_pos ? base + r * p.z_pos_stride : nullptr; },
           gamma, beta, p.eps);
@@ -431,8 +390,51 @@ trimul_out_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant
     const int r = warp * 32 + lane;   // pair row of the tile == TMEM lane
     const bool reduce = p.add_residual && p.out == p.z;
     const bool read_res = p.add_residual && !reduce;
-    int it = 0;
-    for (int tile = blockIdx.x; tile < p.num_tiles; tile += gridDim.x, ++it) {
+    // There is no control warp (a 17th warp would cap every thread at 96 registers): thread 0 issues the TMA
+    // loads of the weights and the raw t tiles and, in step i, the two products of tile i; the four warps then
+    // drain tile i - 1, whose products ran while tile i's operands were being written.
+    constexpr uint32_t idesc = make_idesc_bf16(128, 128);
+    const uint32_t w_s = smem_u32(smem + W_OFF);
+    const uint32_t a1_s = smem_u32(smem + A1_OFF);
+    const uint32_t a2_s = smem_u32(smem + A2_OFF);
+    auto issue_t = [&](int tile, int s) {
+      const int line = tile / tiles_per_line;
+      const int pos0 = (tile - line * tiles_per_line) << 7;
+      mbar_arrive_expect_tx(&t_full[s], kOperandTile);
+      tma_load_3d(smem + T_OFF + s * kOperandTile, &tmT, &t_full[s], pos0, line, 0);
+    };
+    int my_tiles = 0;
+    for (int tile = blockIdx.x; tile < p.num_tiles; tile += gridDim.x) ++my_tiles;
+    if (threadIdx.x == 0) {
+      mbar_arrive_expect_tx(w_full, 2 * kOperandTile);
+      for (int mt = 0; mt < 2; ++mt)
+        for (int h = 0; h < 2; ++h)
+          tma_load_2d(smem + W_OFF + mt * kOperandTile + h * kOperandHalf, &tmW, w_full, h * 64, mt * 128);
+      if (my_tiles > 0) issue_t(blockIdx.x, 0);          // first two t tiles in flight
+      if (my_tiles > 1) issue_t(blockIdx.x + gridDim.x, 1);
+      mbar_wait(w_full, 0, 20);
+    }
+    __syncwarp();
+    for (int step = 0; step <= my_tiles; ++step) {
+      if (threadIdx.x == 0 && step < my_tiles) {
+        const int acc = step & 1;
+        mbar_wait(&acc_empty[acc], ((step >> 1) & 1) ^ 1, 21);
+        mbar_wait(a1_full, step & 1, 22);
+        mbar_wait(a2_full, step & 1, 23);
+        tc_fence_after_sync();
+        umma_k128(tmem_base + acc * 256, a1_s, w_s, idesc, false);                       // p_out(LN_out(t))
+        umma_k128(tmem_base + acc * 256 + 128, a2_s, w_s + kOperandTile, idesc, false);  // g_out(LN_in(z))
+        umma_commit(a_empty);
+        umma_commit(&acc_full[acc]);
+        if (step + 2 < my_tiles) {  // refill the raw-t stage this tile used, once the transformers have released it
+          mbar_wait(&t_empty[step & 1], (step >> 1) & 1, 24);
+          issue_t(blockIdx.x + (step + 2) * gridDim.x, step & 1);
+        }
+      }
+      __syncwarp();
+      if (step == 0) continue;
+      const int it = step - 1;
+      const int tile = blockIdx.x + it * gridDim.x;
       const int line = tile / tiles_per_line;
       const int pos0 = (tile - line * tiles_per_line) << 7;
       const int acc = it & 1;
@@ -503,7 +505,7 @@ trimul_out_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant
 
   tc_fence_before_sync();
   __syncthreads();
-  if (warp == 16) {
+  if (warp == 0) {
     __syncwarp();
     tmem_dealloc(tmem_base, 512);
   }
