@@ -1,21 +1,30 @@
 """Benchmark of the pair-representation trunk on B200.
 
     python bench.py [--gpus N] [--steps K] [--warmup W] [--impl b200|reference] [--tokens 512] [--blocks 48]
-                    [--block pairformer|pairmixer]
+                    [--block pairformer|pairmixer] [--cp RxC] [--replicas] [--probe NAME]
 
 A "step" is one forward of the 48-block Pairformer trunk over one pair tensor z[1, N, N, 128] and single
 track s[1, N, 384] (fp32 residual streams, bf16 tensor-core arithmetic), N = 512 with the last 37 tokens
 padded -- the configuration the headline metric (trunk ms/forward and pair-cells/s) is quoted on.  The
 block is the benchmark's composite one (--block pairformer); --block pairmixer runs the reference trunk's
-own attention-free block.  Inputs are synthetic
-(seeded N(0,1)), weights random-init (Kaiming-uniform linears, LayerNorm 1/0).
+own attention-free block.  Inputs are synthetic (seeded N(0,1)), weights random-init (Kaiming-uniform
+linears, LayerNorm 1/0).
 
-One JSON line is printed by rank 0.  `value` is pair cells per second (N^2 / forward time, summed over
-ranks), timed with CUDA events with z resident in HBM; `e2e` is the same through the public module call
-with pinned HOST buffers, host->device and device->host copies inside the timed region; `roofline`
-describes the dominant kernel; `cpu_baseline` is the CPU oracle timed on this host's cores on a bounded
-sample.  With --gpus N > 1 (torchrun) every rank runs the same workload on its own pair tensor
-(independent systems, no data-path collective): weak scaling.
+One JSON line is printed by rank 0.
+
+* 1 GPU: `value` is pair cells per second (N^2 / forward time), timed with CUDA events with z resident in HBM;
+  `e2e` is the same through the public module call with pinned HOST buffers, host->device and device->host copies
+  inside the timed region; `roofline` describes the dominant kernel; `parity` compares block 0 of the trunk, run on
+  the bench's own inputs, with the CPU oracle; `cpu_baseline` is the CPU oracle timed on this host's cores on a
+  bounded sample; `torch_gpu_baseline` is the same oracle code run on this GPU under bf16 autocast (plain torch
+  kernels), outside the timed region; `ops` holds per-op times, including the outer product mean (1024 x 384 MSA)
+  and the N = 1536 / 3072 sizes.
+* N > 1 GPUs (torchrun): the SAME workload with ONE pair tensor tiled over an R x C grid (1x2, 2x2, 2x4) -- context
+  parallelism with NCCL row / column collectives, strong scaling; `cp_parity_rel` is the sharded result against the
+  single-GPU modules on a small case run first, `cp_config3` times triangle multiplication out/in + triangle attention
+  start/end at N = 1536 on the same grid.  --replicas keeps the older mode (every rank its own pair tensor, no
+  collective, weak scaling).
+* --probe NAME runs one kernel family alone a few times (for profiler captures) and prints its time.
 """
 from __future__ import annotations
 
@@ -35,6 +44,8 @@ import torch  # noqa: E402
 
 METRIC = "pairformer_trunk_pair_cells_per_s"
 UNIT = "pair-cells/s"
+GRIDS = {1: (1, 1), 2: (1, 2), 4: (2, 2), 8: (2, 4)}
+PROBES = ("attention_core", "triatt", "trimul", "transition", "apb", "opm")
 
 
 def parse_args():
@@ -50,11 +61,16 @@ def parse_args():
                          "pair transition, single-track pair-bias attention, single transition); "
                          "pairmixer: the reference trunk's own block (no attention)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-extras", action="store_true",
+                    help="skip the outer-product-mean, N=1536/3072 and torch-on-GPU legs of the 1-GPU run")
     ap.add_argument("--no-graph", action="store_true",
                     help="launch the kernels of the HBM-resident step one by one instead of replaying a CUDA graph")
     ap.add_argument("--cp", default=None, metavar="RxC",
-                    help="context-parallel mode: ONE pair tensor tiled over an RxC grid of the --gpus ranks (strong "
-                         "scaling) running the PairMixer blocks; the default without --cp is independent replicas")
+                    help="grid for the context-parallel run (default: 1x2, 2x2, 2x4 for 2, 4, 8 ranks)")
+    ap.add_argument("--replicas", action="store_true",
+                    help="with --gpus N > 1: N independent replicas (weak scaling) instead of context parallelism")
+    ap.add_argument("--probe", default=None, choices=PROBES,
+                    help="run one kernel family alone (--steps launches after --warmup) and print its time")
     return ap.parse_args()
 
 
@@ -94,6 +110,18 @@ def workload(tokens: int, blocks: int, kind: str, seed: int = 2):
     return w, s, z, tok
 
 
+def opm_workload():
+    """Outer product mean on m[1, 1024, 384, 64] bf16 with a random 10 % of the MSA rows masked, seed 1."""
+    import helpers as H
+
+    g = torch.Generator().manual_seed(1)
+    w = H.opm_weights(g, perturbed=False)
+    m = torch.randn(1, 1024, 384, 64, generator=g).bfloat16()
+    rows = torch.rand(1, 1024, generator=g) > 0.1
+    mask = rows[:, :, None].expand(1, 1024, 384).contiguous()
+    return w, m, mask
+
+
 def block_flops(N: int, kind: str) -> dict:
     P = float(N) * N
     f = {
@@ -110,7 +138,7 @@ def block_flops(N: int, kind: str) -> dict:
     return f
 
 
-def config_dict(args, impl_note: str) -> dict:
+def config_dict(args, impl_note: str, parallelism: str) -> dict:
     what = ("triangle multiplication out/in, triangle attention start/end (4x32), pair transition, single-track "
             "pair-bias attention (16x24), single transition" if args.block == "pairformer"
             else "triangle multiplication out/in + pair transition (the reference trunk's own block)")
@@ -124,50 +152,49 @@ def config_dict(args, impl_note: str) -> dict:
         "arithmetic": "bf16 tensor cores, fp32 accumulate",
         "cache": "inputs larger than L2: z is 134 MB fp32 at N=512 and every kernel streams >=200 MB of scratch",
         "launch": "eager" if args.no_graph else "CUDA graph replay of the step (value); eager launches (e2e)",
-        "parallelism": f"{args.gpus} independent replicas" if args.gpus > 1 else "single GPU",
+        "parallelism": parallelism,
         "note": impl_note,
     }
 
 
 # ----------------------------------------------------------------------------------------- CPU oracle legs
-def cpu_block_fn(tokens: int, kind: str):
-    """Returns a closure running ONE block of the trunk with the CPU oracle, and the core count used."""
+def oracle_block_fn(tokens: int, kind: str, device: str = "cpu"):
+    """A closure running ONE block of the trunk (block 0 of the seed-2 workload) with the oracle, on `device`."""
     from oracle import pair_ops as O
 
-    cores = os.cpu_count() or 1
-    torch.set_num_threads(cores)
-    g = torch.Generator().manual_seed(2)
-    w = block_weights(g, kind)
-    z = torch.randn(1, tokens, tokens, 128, generator=g)
-    s = torch.randn(1, tokens, 384, generator=g)
-    tok = torch.ones(1, tokens, dtype=torch.bool)
-    tok[0, tokens - pad_tokens(tokens):] = False
+    w, s, z, tok = workload(tokens, 1, kind, seed=2)
+    w = {k[len("layers.0."):]: v.to(device) for k, v in w.items()}
+    s, z, tok = s.to(device), z.to(device), tok.to(device)
     pm = tok[:, :, None] & tok[:, None, :]
     if kind == "pairmixer":
-        return (lambda: O.pairmixer_layer(z, pm, w)), cores
-    return (lambda: O.pairformer_block(s, z, tok, w, row_chunk=32)), cores
+        return lambda: (s, O.pairmixer_layer(z, pm, w))
+    return lambda: O.pairformer_block(s, z, tok, w, row_chunk=32)
 
 
-def time_cpu_oracle(tokens: int, kind: str, reps: int = 1):
-    fn, cores = cpu_block_fn(tokens, kind)
-    times = []
+def time_oracle(fn, reps: int, sync=None):
+    """Median of `reps` runs after one warm-up; returns (seconds, last result)."""
+    times, out = [], None
     with torch.no_grad():
-        for _ in range(reps + 1):
+        for i in range(reps + 1):
             t0 = time.perf_counter()
-            fn()
-            times.append(time.perf_counter() - t0)
-    times = sorted(times[1:])
-    return times[len(times) // 2], cores
+            out = fn()
+            if sync:
+                sync()
+            if i > 0:
+                times.append(time.perf_counter() - t0)
+    times.sort()
+    return times[len(times) // 2], out
 
 
 def run_reference(args) -> None:
-    """--impl reference: the CPU port of the reference path, each step a bounded sample (one block)."""
-    rank = int(os.environ.get("RANK", "0"))
-    if rank != 0:
+    """--impl reference: the CPU port of the reference path on all host cores, each step a bounded sample (one block
+    of the trunk at the same N); rank 0 alone runs it."""
+    if int(os.environ.get("RANK", "0")) != 0:
         return
-    fn, cores = cpu_block_fn(args.tokens, args.block)
-    steps = max(1, min(args.steps, 3))
-    warm = min(args.warmup, 1)
+    cores = os.cpu_count() or 1
+    torch.set_num_threads(cores)
+    fn = oracle_block_fn(args.tokens, args.block)
+    steps, warm = max(1, args.steps), max(0, args.warmup)
     with torch.no_grad():
         for _ in range(warm):
             fn()
@@ -177,15 +204,16 @@ def run_reference(args) -> None:
         dt = (time.perf_counter() - t0) / steps
     fwd = dt * args.blocks
     value = args.tokens ** 2 / fwd
-    sample = (f"1 of {args.blocks} blocks per step at N={args.tokens} (fp32 torch on CPU, {dt:.2f} s/block), "
-              f"forward time = {args.blocks} x block time")
+    sample = (f"each step = 1 of the {args.blocks} blocks at N={args.tokens} (fp32 torch on CPU, {dt:.2f} s/block, mean of "
+              f"{steps} steps after {warm} warm-up); forward time = {args.blocks} x block time")
     note = "CPU port of the reference modules (oracle/pair_ops.py)"
     if args.block == "pairformer":
         note += "; triangle attention is not in the reference and is timed from the oracle's own statement of it"
     line = {
         "impl": "reference", "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": args.gpus, "steps": steps,
-        "warmup": warm, "ms_per_step": fwd * 1e3, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
-        "dtype": "f32", "data": "synthetic", "config": config_dict(args, note),
+        "warmup": warm, "ms_per_step": fwd * 1e3, "higher_is_better": True,
+        "scaling": "weak" if (args.replicas or args.gpus == 1) else "strong", "vs_baseline": None,
+        "dtype": "f32", "data": "synthetic", "config": config_dict(args, note, f"CPU, {cores} threads"),
         "cpu_baseline": {"value": value, "unit": UNIT, "cores": cores, "kind": "port", "sample": sample},
         "e2e": {"value": value, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
     }
@@ -236,7 +264,7 @@ class ClockSampler:
                 "reasons": reasons, "samples": len(sm)}
 
 
-# ----------------------------------------------------------------------------------------- GPU arm
+# ----------------------------------------------------------------------------------------- GPU helpers
 def peaks() -> dict:
     path = os.path.join(ROOT, "MEASURED_PEAKS.json")
     if os.path.exists(path):
@@ -284,6 +312,78 @@ def attention_core_probe(N: int, dev):
     return launch, keep
 
 
+def pair_ops_at(N: int, dev, seed: int = 3):
+    """The four pair ops of one block (seed-3 weights, full mask) on a fresh z[1, N, N, 128]: the workload of the
+    N = 1536 configuration.  Returns (modules, z, mask)."""
+    import bioemu2_b200 as b
+    import helpers as H
+
+    g = torch.Generator().manual_seed(seed)
+    mods = {}
+    for name, mode in (("trimul_out", "outgoing"), ("trimul_in", "incoming")):
+        m = b.TriangleMultiplication(128, mode).eval()
+        m.load_state_dict(H.trimul_weights(g, perturbed=False), strict=True)
+        mods[name] = m.to(dev)
+    for name, ending in (("triatt_start", False), ("triatt_end", True)):
+        m = b.TriangleAttention(ending=ending).eval()
+        m.load_state_dict(H.triatt_weights(g, perturbed=False), strict=True)
+        mods[name] = m.to(dev)
+    gd = torch.Generator(device=dev).manual_seed(seed)
+    z = torch.randn(1, N, N, 128, device=dev, generator=gd)
+    mask = torch.ones(1, N, N, dtype=torch.uint8, device=dev)
+    return mods, z, mask
+
+
+def run_probe(args) -> None:
+    """One kernel family alone, for profiler captures: --warmup launches, then --steps timed ones."""
+    import bioemu2_b200 as b
+
+    torch.cuda.set_device(0)
+    dev = torch.device("cuda", 0)
+    N = args.tokens
+    with torch.no_grad():
+        if args.probe == "attention_core":
+            fn, keep = attention_core_probe(N, dev)
+        elif args.probe in ("triatt", "trimul"):
+            mods, z, mask = pair_ops_at(N, dev)
+            key = "triatt_start" if args.probe == "triatt" else "trimul_out"
+            fn = lambda: mods[key].forward_residual_(z, mask)  # noqa: E731
+        elif args.probe == "transition":
+            w, s, z, tok = workload(N, 1, "pairformer")
+            blk = b.PairformerBlock().eval()
+            blk.load_state_dict({k[len("layers.0."):]: v for k, v in w.items()}, strict=True)
+            blk.to(dev)
+            zd = z.to(dev)
+            fn = lambda: blk.transition_z.forward_residual_(zd)  # noqa: E731
+        elif args.probe == "apb":
+            w, s, z, tok = workload(N, 1, "pairformer")
+            blk = b.PairformerBlock().eval()
+            blk.load_state_dict({k[len("layers.0."):]: v for k, v in w.items()}, strict=True)
+            blk.to(dev)
+            sd, zd, td = s.to(dev), z.to(dev), tok.to(dev)
+            fn = lambda: blk.attention(sd, zd, td)  # noqa: E731
+        else:
+            w, m, mask = opm_workload()
+            mod = b.OuterProductMean(64, 32, 128).eval()
+            mod.load_state_dict(w, strict=True)
+            mod.to(dev)
+            md, kd = m.to(dev), mask.to(dev)
+            fn = lambda: mod(md, kd)  # noqa: E731
+        for _ in range(args.warmup):
+            fn()
+        ms = event_time_ms(fn, args.steps)
+        status = b._lib.device_status()
+    print(json.dumps({"probe": args.probe, "tokens": N, "ms_per_call": ms, "device_status": status}), flush=True)
+
+
+def parity_stats(actual: torch.Tensor, expected: torch.Tensor) -> dict:
+    a, e = actual.detach().double().cpu(), expected.detach().double().cpu()
+    d = (a - e).abs()
+    return {"rel_max": float(d.max() / e.abs().max().clamp_min(1e-30)),
+            "elementwise_ok": bool((d <= 2e-2 + 2e-2 * e.abs()).all()), "nan": bool(torch.isnan(a).any())}
+
+
+# ----------------------------------------------------------------------------------------- 1 GPU (or replicas)
 def run_b200(args) -> None:
     import torch.distributed as dist
 
@@ -344,7 +444,10 @@ def run_b200(args) -> None:
         sampler = ClockSampler(local)
         if rank == 0:
             sampler.start()
-        for _ in range(max(args.warmup, 3)):
+        n0 = b._lib.launch_count()
+        step_resident()
+        launches_per_step = b._lib.launch_count() - n0
+        for _ in range(max(args.warmup, 3) - 1):
             step_resident()
         barrier()
         timed_step = step_resident
@@ -398,6 +501,16 @@ def run_b200(args) -> None:
             core, keep = attention_core_probe(N, dev)
             t["attention_core"] = event_time_ms(core, it)
             del keep
+        # block 0 of the trunk on the bench's own inputs, kept for the parity check against the oracle below
+        if composite:
+            s_blk, z_blk = L0(s_dev, z_dev, tok_dev)
+        else:
+            s_blk, z_blk = L0(s_dev, z_dev, mask8)
+        s_blk, z_blk = s_blk.cpu(), z_blk.cpu()
+        del zt, st
+        extras = {}
+        if rank == 0 and world == 1 and not args.no_extras:
+            extras = extra_ops(args, dev, b)
         status = b._lib.device_status()
 
     if world > 1:
@@ -418,20 +531,27 @@ def run_b200(args) -> None:
         ops["trimul_hbm_gbs"] = 3072.0 * P / (t_tm * 1e-3) / 1e9
         ops["trimul_frac_of_hbm"] = ops["trimul_hbm_gbs"] / pk["hbm_gbs"]
         ops["trunk_tflops"] = tf(args.blocks * fl["block"], ms)
+        ops.update(extras.get("ops", {}))
         if composite:
             core_flops = 4.0 * N ** 3 * 128
             ach = tf(core_flops, t["attention_core"])
             ex2_floor_ms = (float(N) ** 3 * 4) / (16.0 * 148 * (clocks["sm_mhz"] or 1965) * 1e6) * 1e3 if clocks else None
+            # q, k, g (N^2 x 384 bf16), V^T (N^2 x 128 bf16) read once, the gated output (N^2 x 128 bf16) written once,
+            # the 4-head bias (4 N^2 bf16) read from L2
+            core_bytes = P * (384 + 128 + 128) * 2 + 4 * P * 2
             roofline = {
                 "kernel": "flash_core_kernel<32,2> (triangle-attention core: QK^T + bias tile + online softmax + PV), "
                           "launched alone on N rows x 4 heads x 32",
                 "bound": "tensor", "achieved": ach, "peak": pk["bf16_tflops"], "unit": "TFLOP/s",
                 "frac": ach / pk["bf16_tflops"], "peak_source": pk["source"] + " burst (kernel timed alone)",
-                "algorithmic_flops_per_launch": core_flops, "ms_per_launch": t["attention_core"],
+                "algorithmic_flops_per_launch": core_flops, "algorithmic_bytes_per_launch": core_bytes,
+                "ms_per_launch": t["attention_core"],
                 # dram__bytes_read.sum + dram__bytes_write.sum of one launch at N=512 (ncu capture summarised in
                 # profiles/flash_core_triatt_n512.md); the operands scale with N^2, so other sizes are scaled from it
                 "traffic": 323.5e6 * (N / 512.0) ** 2,
-                "traffic_source": "ncu capture at N=512 (271.1 MB read + 52.4 MB written), scaled by (N/512)^2",
+                "traffic_source": "ncu capture at N=512 (271.1 MB read + 52.4 MB written), scaled by (N/512)^2; the "
+                                  "algorithmic bytes of the launch are 337.6 MB at N=512 (four 67.1 MB operands read, one "
+                                  "67.1 MB result written, 2.1 MB of bias), so the kernel moves no byte twice",
                 "note": "head dim 32 makes the core ex2-bound, not tensor-bound: N^3*4 exponentials at 16/clk/SM "
                         f"take {ex2_floor_ms:.3f} ms at the sampled clock; the tensor work alone would take "
                         f"{core_flops / (pk['bf16_tflops'] * 1e12) * 1e3:.3f} ms" if ex2_floor_ms else "",
@@ -443,111 +563,300 @@ def run_b200(args) -> None:
                 "frac": ops["transition_z_frac_of_bf16_burst"], "peak_source": pk["source"] + " burst (kernel timed alone)",
                 "algorithmic_flops_per_launch": fl["transition_z"], "ms_per_launch": t["transition_z"], "traffic": None,
             }
-        launches_per_block = 25 if composite else 7
         h2d = z_host.numel() * 4 + s_host.numel() * 4 + (tok.numel() if composite else pair_mask.numel())
+        par = f"{world} independent replicas (weak scaling, no data-path collective)" if world > 1 else "single GPU"
         line = {
             "metric": METRIC, "value": world * cells / (ms * 1e-3), "unit": UNIT, "n_gpus": world, "steps": args.steps,
             "warmup": max(args.warmup, 3), "ms_per_step": ms, "higher_is_better": True, "scaling": "weak",
             "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
-            "config": config_dict(args, "hand-written sm_100a kernels through the C ABI (libb200pair.so)"),
+            "config": config_dict(args, "hand-written sm_100a kernels through the C ABI (libb200pair.so)", par),
             "clocks": clocks,
             "e2e": {"value": world * cells / (e2e_ms * 1e-3), "unit": UNIT, "ms_per_step": e2e_ms,
                     "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": z_host.numel() * 4 + s_host.numel() * 4},
-            "gpu_launches": args.steps * args.blocks * launches_per_block,
+            "gpu_launches": int(args.steps * launches_per_step),
+            "gpu_launches_per_step": int(launches_per_step),
             "roofline": roofline, "ops": ops, "device_status": status,
         }
+        for k in ("torch_gpu_baseline", "larger_sizes"):
+            if k in extras:
+                line[k] = extras[k]
         if not args.no_cpu_baseline and world == 1:
-            t_block, cores = time_cpu_oracle(N, args.block)
+            cores = os.cpu_count() or 1
+            torch.set_num_threads(cores)
+            t_block, (s_ref, z_ref) = time_oracle(oracle_block_fn(N, args.block), 3)
             line["cpu_baseline"] = {
                 "value": cells / (t_block * args.blocks), "unit": UNIT, "cores": cores, "kind": "port",
-                "sample": f"1 of {args.blocks} blocks at N={N} timed once after 1 warm-up ({t_block:.2f} s/block), "
+                "sample": f"1 of {args.blocks} blocks at N={N}, median of 3 after 1 warm-up ({t_block:.2f} s/block), "
                           f"forward = {args.blocks} x block",
+            }
+            pz, ps = parity_stats(z_blk, z_ref), parity_stats(s_blk, s_ref)
+            line["parity"] = {
+                "what": f"block 0 of the trunk on the bench inputs (N={N}, all cells) against the fp32 CPU oracle",
+                "rel_max": max(pz["rel_max"], ps["rel_max"]), "rel_max_z": pz["rel_max"], "rel_max_s": ps["rel_max"],
+                "elementwise_ok": pz["elementwise_ok"] and ps["elementwise_ok"] and not (pz["nan"] or ps["nan"]),
+                "bar": "|d| <= 2e-2 + 2e-2 |ref| for every element, and rel_max <= 2e-2",
             }
         print(json.dumps(line), flush=True)
     if world > 1:
         dist.destroy_process_group()
 
 
+def extra_ops(args, dev, b) -> dict:
+    """The legs of the 1-GPU run outside the headline: outer product mean (1024 x 384 MSA), the N = 1536 pair ops, a
+    two-block trunk at N = 1536 and a one-block trunk at N = 3072 (scaled to 48 blocks, stated as such), and the
+    oracle's torch code on this GPU under bf16 autocast as the same-box GPU baseline."""
+    out = {"ops": {}}
+    ops = out["ops"]
+    pk = peaks()
+    # outer product mean
+    w, m, mask = opm_workload()
+    mod = b.OuterProductMean(64, 32, 128).eval()
+    mod.load_state_dict(w, strict=True)
+    mod.to(dev)
+    md, kd = m.to(dev), mask.to(dev)
+    mod(md, kd)
+    ops["opm_c1_ms"] = event_time_ms(lambda: mod(md, kd), 20)
+    opm_flops = 2.0 * 1024 * 384 ** 2 * 32 ** 2 + 2.0 * 384 ** 2 * 1024 * 128 + 2.0 * 1024 * 384 * 64 * 64
+    ops["opm_c1_tflops"] = opm_flops / (ops["opm_c1_ms"] * 1e-3) / 1e12
+    ops["opm_c1_frac_of_bf16_burst"] = ops["opm_c1_tflops"] / pk["bf16_tflops"]
+    del mod, md, kd
+    # N = 1536 pair ops (one block's triangle multiplication out/in + triangle attention start/end)
+    mods, z, mask = pair_ops_at(1536, dev)
+    z0 = z.clone()
+    for k in ("trimul_out", "trimul_in", "triatt_start", "triatt_end"):
+        z.copy_(z0)
+        mods[k].forward_residual_(z, mask)
+        ops[k + "_n1536_ms"] = event_time_ms(lambda: mods[k].forward_residual_(z, mask), 5)
+
+    def config3():
+        z.copy_(z0)
+        for k in ("trimul_out", "trimul_in", "triatt_start", "triatt_end"):
+            mods[k].forward_residual_(z, mask)
+
+    ops["config3_n1536_ms"] = event_time_ms(config3, 5)
+    del mods, z, z0, mask
+    torch.cuda.empty_cache()
+    # larger trunks, fewer blocks
+    larger = {}
+    for n_tok, n_blk in ((1536, 2), (3072, 1)):
+        wl, s, zz, tok = workload(n_tok, n_blk, args.block, seed=2)
+        trunk = (b.PairformerModule(384, 128, n_blk) if args.block == "pairformer" else b.PairMixerModule(384, 128, n_blk)).eval()
+        trunk.load_state_dict(wl, strict=True)
+        trunk.to(dev)
+        sd, zd, td = s.to(dev), zz.to(dev), tok.to(dev)
+        pm8 = (td[:, :, None] & td[:, None, :]).to(torch.uint8)
+        zw, sw = torch.empty_like(zd), torch.empty_like(sd)
+
+        def step():
+            zw.copy_(zd)
+            sw.copy_(sd)
+            for layer in trunk.layers:
+                if args.block == "pairformer":
+                    layer.forward_(sw, zw, td, pm8)
+                else:
+                    layer.forward_(zw, pm8)
+
+        step()
+        ms = event_time_ms(step, 3)
+        larger[f"N{n_tok}"] = {
+            "blocks_timed": n_blk, "ms_per_block": ms / n_blk, "ms_per_forward_48_blocks_extrapolated": ms / n_blk * 48,
+            "pair_cells_per_s_extrapolated": n_tok ** 2 / (ms / n_blk * 48 * 1e-3),
+            "trunk_tflops": block_flops(n_tok, args.block)["block"] * n_blk / (ms * 1e-3) / 1e12,
+        }
+        del trunk, sd, zd, td, pm8, zw, sw
+        b.functional.release_workspaces()
+        torch.cuda.empty_cache()
+    out["larger_sizes"] = larger
+    # the oracle's plain torch code on this GPU under bf16 autocast (cuBLAS / eager kernels)
+    try:
+        fn = oracle_block_fn(args.tokens, args.block, device=str(dev))
+
+        def run():
+            with torch.autocast("cuda", dtype=torch.bfloat16):
+                return fn()
+
+        t_blk, _ = time_oracle(run, 3, sync=torch.cuda.synchronize)
+        out["torch_gpu_baseline"] = {
+            "what": "the oracle's un-fused torch code (the reference's `full`/`vanilla`/einsum formulation) on this GPU "
+                    "under torch.autocast(bfloat16): cuBLAS and eager kernels, one block, outside the timed region",
+            "ms_per_block": t_blk * 1e3, "ms_per_forward_extrapolated": t_blk * 1e3 * args.blocks,
+            "value": args.tokens ** 2 / (t_blk * args.blocks), "unit": UNIT,
+        }
+    except Exception as exc:  # an out-of-memory or missing kernel here must not cost the headline
+        out["torch_gpu_baseline"] = {"unavailable": f"{type(exc).__name__}: {exc}"[:200]}
+    torch.cuda.empty_cache()
+    return out
+
+
+# ----------------------------------------------------------------------------------------- context parallel
 def run_cp(args) -> None:
-    """One pair tensor sharded over an RxC grid: triangle multiplication exchanges b-operands (all-gather over the
-    column / row group) and fp32 partial sums (reduce-scatter); everything else is local to the block."""
+    """ONE pair tensor tiled over an R x C grid of the ranks (strong scaling): the same 48-block trunk on the same
+    seeded inputs as the 1-GPU run, every rank holding its block of z and its rows of s."""
     import torch.distributed as dist
 
     import bioemu2_b200 as b
-    from bioemu2_b200.context_parallel import CPGrid, CPPairMixerModule, kernel_shard_multiple
+    from bioemu2_b200.context_parallel import (CPGrid, CPPairformerModule, CPPairMixerModule, CPTriangleAttention,
+                                               CPTriangleMultiplication, kernel_shard_multiple)
 
-    rows, cols = (int(v) for v in args.cp.lower().split("x"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
     rank = int(os.environ.get("RANK", "0"))
     local = int(os.environ.get("LOCAL_RANK", "0"))
+    rows, cols = (int(v) for v in args.cp.lower().split("x")) if args.cp else GRIDS.get(world, (1, world))
     if rows * cols != world:
-        raise SystemExit(f"--cp {args.cp} needs {rows * cols} ranks, got {world}")
+        raise SystemExit(f"grid {rows}x{cols} needs {rows * cols} ranks, got {world}")
     torch.cuda.set_device(local)
     dev = torch.device("cuda", local)
     os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
     os.environ.setdefault("MASTER_PORT", "29511")
     dist.init_process_group("nccl", rank=rank, world_size=world, device_id=dev)
     N = args.tokens
-    if N % kernel_shard_multiple(rows, cols):
-        raise SystemExit(f"--tokens must be a multiple of {kernel_shard_multiple(rows, cols)} for a {args.cp} grid")
+    mult = kernel_shard_multiple(rows, cols)
+    if N % mult:
+        raise SystemExit(f"--tokens must be a multiple of {mult} for a {rows}x{cols} grid")
     grid = CPGrid(rows, cols)
-    torch.manual_seed(2)  # same seed on every rank: replicated weights
-    tri = args.block == "pairformer"  # BASELINE config 3: triangle multiplication out/in + triangle attention start/end
-    if tri:
-        from bioemu2_b200.context_parallel import CPTriangleAttention, CPTriangleMultiplication
+    composite = args.block == "pairformer"
 
-        blocks = [b.PairformerBlock().eval().to(dev) for _ in range(args.blocks)]
-        ops = []
-        for blk in blocks:
-            ops += [CPTriangleMultiplication(blk.tri_mul_out, grid), CPTriangleMultiplication(blk.tri_mul_in, grid),
-                    CPTriangleAttention(blk.tri_att_start, grid), CPTriangleAttention(blk.tri_att_end, grid)]
+    def shard_inputs(s, z, tok):
+        n = z.shape[1]
+        (r0, r1), (c0, c1) = grid.coords.my_rows(n), grid.coords.my_cols(n)
+        return s[:, r0:r1].contiguous(), z[:, r0:r1, c0:c1].contiguous(), tok[:, r0:r1].contiguous(), tok[:, c0:c1].contiguous()
 
-        def cp(zz, mm):
-            for op in ops:
-                op(zz, mm)
-    else:
-        serial = b.PairMixerModule(384, 128, args.blocks).eval().to(dev)
-        cp = CPPairMixerModule(serial, grid)
-    (r0, r1), (c0, c1) = grid.coords.my_rows(N), grid.coords.my_cols(N)
-    g = torch.Generator(device=dev).manual_seed(100 + rank)
-    z0 = torch.randn(1, r1 - r0, c1 - c0, 128, device=dev, generator=g)
-    z = torch.empty_like(z0)
-    mask = torch.ones(1, r1 - r0, c1 - c0, dtype=torch.uint8, device=dev)
+    def build(n_tok, n_blk, seed):
+        w, s, z, tok = workload(n_tok, n_blk, args.block, seed=seed)  # same seed on every rank: replicated weights
+        serial = (b.PairformerModule(384, 128, n_blk) if composite else b.PairMixerModule(384, 128, n_blk)).eval()
+        serial.load_state_dict(w, strict=True)
+        serial.to(dev)
+        cp = CPPairformerModule(serial, grid) if composite else CPPairMixerModule(serial, grid)
+        return serial, cp, s, z, tok
 
-    def step():
-        z.copy_(z0)
-        cp(z, mask)
+    def run_sharded(cp, s_blk, z_blk, tr, tc):
+        if composite:
+            return cp.forward_(s_blk, z_blk, tr, tc)
+        pm = (tr[:, :, None] & tc[:, None, :]).to(torch.uint8)
+        return s_blk, cp(z_blk, pm)
 
     with torch.no_grad():
+        # -- correctness first: two blocks at N = 256, sharded against the single-GPU modules, on every rank
+        serial, cp, s, z, tok = build(256, 2, seed=5)
+        s_l, z_l, tr, tc = (t.to(dev) for t in shard_inputs(s, z, tok))
+        s_cp, z_cp = run_sharded(cp, s_l.clone(), z_l.clone(), tr, tc)
+        td = tok.to(dev)
+        if composite:
+            s_ref, z_ref = serial(s.to(dev), z.to(dev), td)
+        else:
+            s_ref, z_ref = serial(s.to(dev), z.to(dev), (td[:, :, None] & td[:, None, :]))
+        s_ref_l, z_ref_l, _, _ = shard_inputs(s_ref, z_ref, td)
+        rel = max(float((z_cp - z_ref_l).abs().max() / z_ref.abs().max()),
+                  float((s_cp - s_ref_l).abs().max() / s_ref.abs().max()))
+        rel_t = torch.tensor([rel], device=dev, dtype=torch.float64)
+        dist.all_reduce(rel_t, op=dist.ReduceOp.MAX)
+        cp_parity_rel = float(rel_t[0])
+        del serial, cp, s_cp, z_cp, s_ref, z_ref
+        torch.cuda.empty_cache()
+
+        # -- the headline workload, sharded
+        serial, cp, s, z, tok = build(N, args.blocks, seed=2)
+        s_h, z_h, tr_h, tc_h = shard_inputs(s, z, tok)
+        s_pin, z_pin = s_h.pin_memory(), z_h.pin_memory()
+        s_out_pin, z_out_pin = torch.empty_like(s_h).pin_memory(), torch.empty_like(z_h).pin_memory()
+        s_d, z_d, tr, tc = s_h.to(dev), z_h.to(dev), tr_h.to(dev), tc_h.to(dev)
+        s_w, z_w = torch.empty_like(s_d), torch.empty_like(z_d)
+
+        def step_resident():
+            s_w.copy_(s_d)
+            z_w.copy_(z_d)
+            run_sharded(cp, s_w, z_w, tr, tc)
+
+        def step_e2e():
+            sd = s_pin.to(dev, non_blocking=True)
+            zd = z_pin.to(dev, non_blocking=True)
+            so, zo = run_sharded(cp, sd, zd, tr, tc)
+            s_out_pin.copy_(so, non_blocking=True)
+            z_out_pin.copy_(zo, non_blocking=True)
+            torch.cuda.current_stream().synchronize()
+
+        def barrier():
+            dist.barrier()
+            torch.cuda.synchronize()
+
         sampler = ClockSampler(local)
         if rank == 0:
             sampler.start()
-        for _ in range(max(args.warmup, 3)):
-            step()
-        dist.barrier()
+        n0 = b._lib.launch_count()
+        step_resident()
+        launches_per_step = b._lib.launch_count() - n0
+        for _ in range(max(args.warmup, 3) - 1):
+            step_resident()
+        barrier()
+        ms = event_time_ms(step_resident, args.steps)
+        barrier()
+        step_e2e()
+        barrier()
+        t0 = time.perf_counter()
+        for _ in range(args.steps):
+            step_e2e()
         torch.cuda.synchronize()
-        ms = event_time_ms(step, args.steps)
-        dist.barrier()
-        torch.cuda.synchronize()
+        e2e_ms = (time.perf_counter() - t0) * 1e3 / args.steps
+        barrier()
         clocks = sampler.stop() if rank == 0 else None
+        del serial, cp, s_d, z_d, s_w, z_w
+        torch.cuda.empty_cache()
+
+        # -- triangle multiplication out/in + triangle attention start/end at N = 1536, full mask, seed 3
+        n3 = 1536
+        cfg3 = None
+        if composite and n3 % mult == 0:
+            mods, _, _ = pair_ops_at(8, dev)  # weights only (seed 3, same on every rank); z is built per block below
+            ops3 = [CPTriangleMultiplication(mods["trimul_out"], grid), CPTriangleMultiplication(mods["trimul_in"], grid),
+                    CPTriangleAttention(mods["triatt_start"], grid), CPTriangleAttention(mods["triatt_end"], grid)]
+            (r0, r1), (c0, c1) = grid.coords.my_rows(n3), grid.coords.my_cols(n3)
+            gd = torch.Generator(device=dev).manual_seed(300 + rank)
+            z3 = torch.randn(1, r1 - r0, c1 - c0, 128, device=dev, generator=gd)
+            z3w = torch.empty_like(z3)
+            m3 = torch.ones(1, r1 - r0, c1 - c0, dtype=torch.uint8, device=dev)
+
+            def step3():
+                z3w.copy_(z3)
+                for op in ops3:
+                    op(z3w, m3)
+
+            step3()
+            step3()
+            barrier()
+            ms3 = event_time_ms(step3, 5)
+            barrier()
+            t3 = torch.tensor([ms3], device=dev, dtype=torch.float64)
+            dist.all_reduce(t3, op=dist.ReduceOp.MAX)
+            cfg3 = {"grid": f"{rows}x{cols}", "tokens": n3, "ms": float(t3[0]),
+                    "what": "triangle multiplication out/in + triangle attention start/end, one block, full mask, seed 3"}
         status = b._lib.device_status()
-    tt = torch.tensor([ms], device=dev, dtype=torch.float64)
+
+    tt = torch.tensor([ms, e2e_ms], device=dev, dtype=torch.float64)
     dist.all_reduce(tt, op=dist.ReduceOp.MAX)
-    ms = float(tt[0])
+    ms, e2e_ms = float(tt[0]), float(tt[1])
+    st = torch.tensor([status], device=dev, dtype=torch.int64)
+    dist.all_reduce(st, op=dist.ReduceOp.MAX)
     if rank == 0:
-        fl = block_flops(N, "pairmixer")
-        if tri:
-            fl["block"] = 2 * fl["trimul"] + 2 * block_flops(N, "pairformer")["triatt"]
+        fl = block_flops(N, args.block)
+        per_rank_in = s_h.numel() * 4 + z_h.numel() * 4
         line = {
             "metric": METRIC, "value": N * N / (ms * 1e-3), "unit": UNIT, "n_gpus": world, "steps": args.steps,
             "warmup": max(args.warmup, 3), "ms_per_step": ms, "higher_is_better": True, "scaling": "strong",
             "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
-            "config": {"workload": f"context-parallel {'triangle multiplication out/in + triangle attention start/end' if tri else 'PairMixer trunk'}, {args.blocks} blocks, N={N}, one pair tensor tiled "
-                                   f"{rows}x{cols} (block {r1 - r0}x{c1 - c0}), full mask", "grid": args.cp, "tokens": N,
-                       "blocks": args.blocks, "z_stream": "fp32",
-                       "exchange": "all-gather of the b operand + fp32 reduce-scatter of partial sums per direction (NCCL)"},
-            "clocks": clocks, "gpu_launches": args.steps * args.blocks * (2 * (3 + rows + cols) + 1),
-            "ops": {"trunk_tflops_aggregate": args.blocks * fl["block"] / (ms * 1e-3) / 1e12}, "device_status": status,
+            "config": config_dict(args, "hand-written sm_100a kernels through the C ABI (libb200pair.so); NCCL collectives "
+                                        "over the grid's row and column groups, eager launches",
+                                  f"context parallel: one pair tensor tiled {rows}x{cols} "
+                                  f"(block {z_h.shape[1]}x{z_h.shape[2]}), single track row-sharded"),
+            "clocks": clocks,
+            "e2e": {"value": N * N / (e2e_ms * 1e-3), "unit": UNIT, "ms_per_step": e2e_ms,
+                    "h2d_bytes_per_step": world * per_rank_in, "d2h_bytes_per_step": world * per_rank_in},
+            "gpu_launches": int(args.steps * launches_per_step), "gpu_launches_per_step": int(launches_per_step),
+            "cp_parity_rel": cp_parity_rel,
+            "cp_parity": "2 blocks at N=256 (seed 5, 18 tokens padded): sharded result against the single-GPU modules "
+                         "on the same inputs, max over ranks of max|d| / max|ref| over every cell",
+            "cp_config3": cfg3,
+            "ops": {"trunk_tflops_aggregate": args.blocks * fl["block"] / (ms * 1e-3) / 1e12},
+            "device_status": int(st[0]),
         }
         print(json.dumps(line), flush=True)
     dist.destroy_process_group()
@@ -555,9 +864,12 @@ def run_cp(args) -> None:
 
 def main():
     args = parse_args()
+    world = int(os.environ.get("WORLD_SIZE", "1"))
     if args.impl == "reference":
         run_reference(args)
-    elif args.cp:
+    elif args.probe:
+        run_probe(args)
+    elif world > 1 and not args.replicas:
         run_cp(args)
     else:
         run_b200(args)

@@ -6,7 +6,7 @@ from __future__ import annotations
 
 import ctypes
 import os
-from ctypes import POINTER, Structure, c_char_p, c_float, c_int, c_int64, c_size_t, c_uint8, c_void_p
+from ctypes import POINTER, Structure, c_char_p, c_float, c_int, c_int64, c_size_t, c_ulonglong, c_void_p
 
 HERE = os.path.dirname(os.path.abspath(__file__))
 # BIOEMU2_B200_LIB points at an alternative build of the same library (profiling or experimental builds).
@@ -66,6 +66,8 @@ SIGNATURES = {
     "b200_last_error": (c_char_p, []),
     "b200_check_device": (c_int, []),
     "b200_device_status": (c_int, [POINTER(c_int)]),
+    "b200_peek_status": (c_int, [POINTER(c_int)]),
+    "b200_launch_count": (c_ulonglong, []),
     "b200_layernorm_fwd": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_int, c_float, c_void_p]),
     "b200_bmm_nt_bf16": (c_int, [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int64, c_int64,
                                  c_int64, c_int64, c_int64, c_int64, c_float, c_void_p]),
@@ -128,6 +130,18 @@ def last_error() -> str:
     return (lib.b200_last_error() or b"").decode()
 
 
+class DeviceWaitError(RuntimeError):
+    """A kernel gave up one of its bounded waits: its results, and those of the kernels queued behind it, are invalid."""
+
+
+def decode_status(word: int) -> str:
+    """Readable form of the device status word: low byte = kind (1: a bounded wait ran out), bits 8.. = wait site."""
+    if word == 0:
+        return "ok"
+    kind = {1: "bounded wait ran out"}.get(word & 0xFF, f"unknown kind {word & 0xFF}")
+    return f"{kind} at wait site {word >> 8} (status {word:#x})"
+
+
 def check(status: int) -> None:
     """Turn a status code into the exception the reference modules would raise."""
     if status == OK:
@@ -135,10 +149,33 @@ def check(status: int) -> None:
     msg = last_error()
     if status in (ERR_INVALID_ARGUMENT, ERR_WORKSPACE):
         raise ValueError(f"b200pair: {msg}")
+    if status == ERR_DEVICE_WAIT:
+        raise DeviceWaitError(f"b200pair: {msg}")
     raise RuntimeError(f"b200pair (status {status}): {msg}")
 
 
 def device_status() -> int:
+    """Synchronises the device, reads and clears the status word."""
     out = c_int(0)
     check(lib.b200_device_status(ctypes.byref(out)))
     return out.value
+
+
+def peek_status() -> int:
+    """The status word as written by kernels that have finished; no synchronisation."""
+    out = c_int(0)
+    check(lib.b200_peek_status(ctypes.byref(out)))
+    return out.value
+
+
+def raise_if_device_wait() -> None:
+    """Poll at a natural synchronisation point (end of a forward, before a collective or a device-to-host copy):
+    raises ``DeviceWaitError`` when a finished kernel reported a wait that ran out.  Costs one host memory read."""
+    word = peek_status()
+    if word != 0:
+        raise DeviceWaitError(f"b200pair: {decode_status(word)}; results since then are invalid "
+                              "(device_status() clears the condition)")
+
+
+def launch_count() -> int:
+    return int(lib.b200_launch_count())

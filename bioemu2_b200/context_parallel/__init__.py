@@ -6,6 +6,7 @@ from .modules import (
     CPAttentionPairBias,
     CPOuterProductMean,
     CPPairformerBlock,
+    CPPairformerModule,
     CPPairMixerLayer,
     CPPairMixerModule,
     CPTransition,
@@ -16,7 +17,7 @@ from .trimul import cp_triangle_multiplication_
 
 __all__ = [
     "CPGrid", "GridCoords", "kernel_shard_multiple", "pad_amount", "shard_multiple", "shard_range",
-    "CPAttentionPairBias", "CPOuterProductMean", "CPPairformerBlock", "CPPairMixerLayer", "CPPairMixerModule", "CPTransition",
+    "CPAttentionPairBias", "CPOuterProductMean", "CPPairformerBlock", "CPPairformerModule", "CPPairMixerLayer", "CPPairMixerModule", "CPTransition",
     "CPTriangleAttention", "CPTriangleMultiplication", "cp_attention_pair_bias", "cp_outer_product_mean",
     "cp_triangle_attention_", "cp_triangle_multiplication_",
 ]

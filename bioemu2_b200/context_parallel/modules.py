@@ -173,13 +173,43 @@ class CPPairformerBlock(nn.Module):
         self.attention = CPAttentionPairBias(serial.attention, grid)
         self.transition_s = CPTransition(serial.transition_s, grid)
 
-    def forward(self, s, z, mask_rows, mask_cols):
-        pm = (mask_rows[:, :, None] & mask_cols[:, None, :]).to(torch.uint8)
-        self.tri_mul_out(z, pm)
-        self.tri_mul_in(z, pm)
-        self.tri_att_start(z, pm)
-        self.tri_att_end(z, pm)
+    def forward_(self, s, z, mask_rows, pair_mask_u8):
+        """In place on the local blocks, with the pair mask of the block already built (one byte per pair)."""
+        self.tri_mul_out(z, pair_mask_u8)
+        self.tri_mul_in(z, pair_mask_u8)
+        self.tri_att_start(z, pair_mask_u8)
+        self.tri_att_end(z, pair_mask_u8)
         self.transition_z.forward_residual_(z)
         s += self.attention(s, z, mask_rows)
         self.transition_s.forward_residual_(s)
         return s, z
+
+    def forward(self, s, z, mask_rows, mask_cols):
+        pm = (mask_rows[:, :, None] & mask_cols[:, None, :]).to(torch.uint8)
+        return self.forward_(s, z, mask_rows, pm)
+
+
+class CPPairformerModule(nn.Module):
+    """A stack of composite blocks on sharded inputs; adopts a loaded serial ``PairformerModule``.
+
+    ``forward(s_rows, z_block, token_mask_rows, token_mask_cols)`` returns updated copies; ``forward_`` updates the
+    given blocks in place.  A kernel-side failure (a bounded wait that ran out) is raised at the end of the stack.
+    """
+
+    def __init__(self, serial, grid: CPGrid) -> None:
+        super().__init__()
+        self.grid = grid
+        self.layers = nn.ModuleList(CPPairformerBlock(layer, grid) for layer in serial.layers)
+
+    def forward_(self, s, z, mask_rows, mask_cols):
+        from .. import _lib
+
+        pm = (mask_rows[:, :, None] & mask_cols[:, None, :]).to(torch.uint8)
+        with torch.no_grad():
+            for layer in self.layers:
+                layer.forward_(s, z, mask_rows, pm)
+        _lib.raise_if_device_wait()
+        return s, z
+
+    def forward(self, s, z, mask_rows, mask_cols):
+        return self.forward_(s.clone(), z.clone(), mask_rows, mask_cols)

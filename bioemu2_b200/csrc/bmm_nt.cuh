@@ -190,7 +190,7 @@ bmm_nt_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ C
               x.y = __uint_as_float(v[g * 4 + 1]) * scale;
               x.z = __uint_as_float(v[g * 4 + 2]) * scale;
               x.w = __uint_as_float(v[g * 4 + 3]) * scale;
-              if (p.bias) {
+              if (p.bias && col0 + g * 4 < p.n_valid) {  // n_valid % 8 == 0: a group of four is inside or outside
                 const float4 bv = *reinterpret_cast<const float4*>(p.bias + col0 + g * 4);
                 x.x += bv.x; x.y += bv.y; x.z += bv.z; x.w += bv.w;
               }
@@ -202,7 +202,7 @@ bmm_nt_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ C
               float x[8];
 #pragma unroll
               for (int e = 0; e < 8; ++e) x[e] = __uint_as_float(v[g * 8 + e]) * scale;
-              if (p.bias) {
+              if (p.bias && col0 + g * 8 < p.n_valid) {
 #pragma unroll
                 for (int e = 0; e < 8; ++e) x[e] += p.bias[col0 + g * 8 + e];
               }

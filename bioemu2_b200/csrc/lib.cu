@@ -19,8 +19,7 @@ namespace b200 {
 
 template <class Kernel>
 static int set_smem(Kernel k, uint32_t bytes) {
-  B200_CUDA(cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, int(bytes)));
-  return 0;
+  return set_smem_once(reinterpret_cast<const void*>(k), bytes);
 }
 
 struct BmmLaunch {
@@ -108,7 +107,7 @@ static int launch_bmm(const BmmLaunch& a, cudaStream_t stream) {
     if (int e = set_smem(bmm_nt_kernel<128>, BmmCfg<128>::SMEM_BYTES)) return e;
     bmm_nt_kernel<128><<<grid, 192, BmmCfg<128>::SMEM_BYTES, stream>>>(tmA, tmB, tmC, p);
   }
-  B200_CUDA(cudaGetLastError());
+  B200_AFTER_LAUNCH();
   return 0;
 }
 
@@ -123,7 +122,7 @@ static int launch_rows_to_bf16(const void* x, bool f32, __nv_bfloat16* y, const 
     layernorm_rows_kernel<true><<<int(blocks), warps * 32, 0, stream>>>(x, y, w, b, rows, cols, 1e-5f, normalize, silu);
   else
     layernorm_rows_kernel<false><<<int(blocks), warps * 32, 0, stream>>>(x, y, w, b, rows, cols, 1e-5f, normalize, silu);
-  B200_CUDA(cudaGetLastError());
+  B200_AFTER_LAUNCH();
   return 0;
 }
 
@@ -175,7 +174,7 @@ static int launch_flash_t(const FlashLaunch& a, cudaStream_t stream) {
   if (int e = set_smem(flash_core_kernel<DH, G>, Cfg::SMEM_BYTES)) return e;
   const int grid = p.total_work < sm_count() ? p.total_work : sm_count();
   flash_core_kernel<DH, G><<<grid, Cfg::THREADS, Cfg::SMEM_BYTES, stream>>>(tmQ, tmQ, tmV, tmB, p);
-  B200_CUDA(cudaGetLastError());
+  B200_AFTER_LAUNCH();
   return 0;
 }
 
@@ -213,7 +212,7 @@ static int launch_pair_bias(const void* z, bool f32, const float* ln_w, const fl
     pair_bias_kernel<true><<<grid, pair_bias::THREADS, pair_bias::SMEM_BYTES, stream>>>(tmW, p);
   else
     pair_bias_kernel<false><<<grid, pair_bias::THREADS, pair_bias::SMEM_BYTES, stream>>>(tmW, p);
-  B200_CUDA(cudaGetLastError());
+  B200_AFTER_LAUNCH();
   return 0;
 }
 
@@ -227,10 +226,12 @@ int b200_version(void) { return 100; }
 
 const char* b200_last_error(void) { return g_last_error; }
 
-int b200_check_device(void) {
+// Compute capability check only (cached per thread); *dev_out receives the current device ordinal.
+static int check_arch(int* dev_out) {
   static thread_local int cached_dev = -1;
   int dev = 0;
   B200_CUDA(cudaGetDevice(&dev));
+  if (dev_out) *dev_out = dev;
   if (dev == cached_dev) return B200_OK;
   int major = 0;
   B200_CUDA(cudaDeviceGetAttribute(&major, cudaDevAttrComputeCapabilityMajor, dev));
@@ -241,6 +242,49 @@ int b200_check_device(void) {
   return B200_OK;
 }
 
+// Host-visible copy of the device status word, one per device ordinal: 64 bytes of pinned, mapped host memory
+// that a kernel writes when one of its bounded waits runs out.  Set up by the first ordinary call on a device.
+static int* g_host_status[64] = {nullptr};
+
+static int ensure_host_status(int dev) {
+  static std::mutex mu;
+  std::lock_guard<std::mutex> lock(mu);
+  if (g_host_status[dev]) return B200_OK;
+  int* hp = nullptr;
+  B200_CUDA(cudaHostAlloc(reinterpret_cast<void**>(&hp), 64, cudaHostAllocMapped | cudaHostAllocPortable));
+  *hp = 0;
+  int* dp = nullptr;
+  B200_CUDA(cudaHostGetDevicePointer(reinterpret_cast<void**>(&dp), hp, 0));
+  B200_CUDA(cudaMemcpyToSymbol(g_host_status_ptr, &dp, sizeof(dp)));
+  g_host_status[dev] = hp;
+  return B200_OK;
+}
+
+int b200_check_device(void) {
+  int dev = 0;
+  if (int e = check_arch(&dev)) return e;
+  if (dev < 0 || dev >= 64) return B200_OK;
+  if (!g_host_status[dev])
+    if (int e = ensure_host_status(dev)) return e;
+  const int st = *reinterpret_cast<volatile int*>(g_host_status[dev]);
+  if (st != 0)
+    return fail(B200_ERR_DEVICE_WAIT,
+                "an earlier kernel on device %d gave up a bounded wait (status %#x, wait site %d): its results and "
+                "those of the kernels after it are invalid; b200_device_status() reads and clears the status",
+                dev, st, st >> 8);
+  return B200_OK;
+}
+
+int b200_peek_status(int* status) {
+  B200_CHECK_ARG(status != nullptr, "status is NULL");
+  int dev = 0;
+  B200_CUDA(cudaGetDevice(&dev));
+  *status = (dev >= 0 && dev < 64 && g_host_status[dev]) ? *reinterpret_cast<volatile int*>(g_host_status[dev]) : 0;
+  return B200_OK;
+}
+
+unsigned long long b200_launch_count(void) { return g_launch_count.load(std::memory_order_relaxed); }
+
 int b200_device_status(int* status) {
   B200_CHECK_ARG(status != nullptr, "status is NULL");
   B200_CUDA(cudaDeviceSynchronize());
@@ -250,6 +294,9 @@ int b200_device_status(int* status) {
     const int zero = 0;
     B200_CUDA(cudaMemcpyToSymbol(g_dev_status, &zero, sizeof(int)));
   }
+  int dev = 0;
+  B200_CUDA(cudaGetDevice(&dev));
+  if (dev >= 0 && dev < 64 && g_host_status[dev]) *reinterpret_cast<volatile int*>(g_host_status[dev]) = 0;
   *status = v;
   return B200_OK;
 }
@@ -268,7 +315,7 @@ int b200_layernorm_fwd(const void* x, void* y, const float* w, const float* b, i
   if (blocks > cap) blocks = cap;
   layernorm_rows_kernel<false><<<int(blocks), warps * 32, 0, static_cast<cudaStream_t>(stream)>>>(
       x, static_cast<__nv_bfloat16*>(y), w, b, rows, cols, eps, 1, 0);
-  B200_CUDA(cudaGetLastError());
+  B200_AFTER_LAUNCH();
   return B200_OK;
 }
 
@@ -343,7 +390,7 @@ static int launch_trimul_project(const void* z, const uint8_t* mask, __nv_bfloat
     trimul_in_kernel<true><<<grid, trimul_in::THREADS, trimul_in::SMEM_BYTES, stream>>>(tmWin, tmA, tmB, pi);
   else
     trimul_in_kernel<false><<<grid, trimul_in::THREADS, trimul_in::SMEM_BYTES, stream>>>(tmWin, tmA, tmB, pi);
-  B200_CUDA(cudaGetLastError());
+  B200_AFTER_LAUNCH();
   return 0;
 }
 
@@ -398,7 +445,7 @@ static int launch_trimul_output(const void* z, void* out, const __nv_bfloat16* t
     trimul_out_kernel<true><<<grid, trimul_out::THREADS, trimul_out::SMEM_BYTES, stream>>>(tmWout, tmT, tmO, po);
   else
     trimul_out_kernel<false><<<grid, trimul_out::THREADS, trimul_out::SMEM_BYTES, stream>>>(tmWout, tmT, tmO, po);
-  B200_CUDA(cudaGetLastError());
+  B200_AFTER_LAUNCH();
   return 0;
 }
 
@@ -407,10 +454,10 @@ static bool trimul_weights_ok(const b200_trimul_weights* w) {
          aligned(w->w_out, 16);
 }
 
-int b200_trimul_fwd(const void* z, const uint8_t* mask, void* out, const b200_trimul_weights* w, int B, int N,
-                    int incoming, int add_residual, int z_dtype, void* workspace, size_t workspace_bytes,
-                    b200_stream_t stream_) {
-  if (int e = b200_check_device()) return e;
+// Argument checks and the three launches of triangle multiplication; the callers have checked the device.
+static int trimul_fwd_impl(const void* z, const uint8_t* mask, void* out, const b200_trimul_weights* w, int B, int N,
+                           int incoming, int add_residual, int z_dtype, void* workspace, size_t workspace_bytes,
+                           b200_stream_t stream_) {
   cudaStream_t stream = static_cast<cudaStream_t>(stream_);
   B200_CHECK_ARG(z && mask && out && w, "z/mask/out/w is NULL");
   B200_CHECK_ARG(trimul_weights_ok(w), "a weight pointer is NULL or not 16-byte aligned");
@@ -444,6 +491,13 @@ int b200_trimul_fwd(const void* z, const uint8_t* mask, void* out, const b200_tr
     if (int e = launch_trimul_output(zb, ob, t_buf, w, gout, add_residual != 0, f32, stream)) return e;
   }
   return B200_OK;
+}
+
+int b200_trimul_fwd(const void* z, const uint8_t* mask, void* out, const b200_trimul_weights* w, int B, int N,
+                    int incoming, int add_residual, int z_dtype, void* workspace, size_t workspace_bytes,
+                    b200_stream_t stream) {
+  if (int e = b200_check_device()) return e;
+  return trimul_fwd_impl(z, mask, out, w, B, N, incoming, add_residual, z_dtype, workspace, workspace_bytes, stream);
 }
 
 // Staged form for sharded callers: the projection and output stages on a rectangular slab, the contraction
@@ -563,7 +617,7 @@ int b200_transition_fwd(const void* x, void* out, const void* w13, const void* w
     transition_kernel<true><<<grid, transition::THREADS, transition::SMEM_BYTES, stream>>>(tmW1, tmW3, tmO, p);
   else
     transition_kernel<false><<<grid, transition::THREADS, transition::SMEM_BYTES, stream>>>(tmW1, tmW3, tmO, p);
-  B200_CUDA(cudaGetLastError());
+  B200_AFTER_LAUNCH();
   return B200_OK;
 }
 
@@ -580,7 +634,9 @@ static void* g_trimul_static_ptr[64] = {nullptr};
 
 int b200_trimul_fwd_static(const void* z, const uint8_t* mask, void* out, const b200_trimul_weights* w, int B, int N,
                            int incoming, int add_residual, int z_dtype, b200_stream_t stream) {
-  if (int e = b200_check_device()) return e;
+  // Only the compute-capability check: the ordinary entry points also set up a pinned status word on their first
+  // call, which is an allocation this entry point promises not to make.
+  if (int e = check_arch(nullptr)) return e;
   B200_CHECK_ARG(N > 0 && N <= B200_STATIC_TRIMUL_MAX_N,
                  "b200_trimul_fwd_static handles N <= %d (got %d); use b200_trimul_fwd with a caller workspace",
                  B200_STATIC_TRIMUL_MAX_N, N);
@@ -593,7 +649,7 @@ int b200_trimul_fwd_static(const void* z, const uint8_t* mask, void* out, const 
     g_trimul_static_ptr[dev] = ptr;
   }
   uintptr_t base = (reinterpret_cast<uintptr_t>(g_trimul_static_ptr[dev]) + 1023) & ~uintptr_t(1023);
-  return b200_trimul_fwd(z, mask, out, w, B, N, incoming, add_residual, z_dtype, reinterpret_cast<void*>(base),
+  return trimul_fwd_impl(z, mask, out, w, B, N, incoming, add_residual, z_dtype, reinterpret_cast<void*>(base),
                          b200_trimul_workspace_bytes(N), stream);
 }
 
@@ -678,11 +734,11 @@ static int opm_run(const void* m, const uint8_t* mask, int mask_ndim, void* out,
       opm_proj_kernel<true><<<grid, opm_proj::THREADS, opm_proj::SMEM_BYTES, stream>>>(tmW, pp);
     else
       opm_proj_kernel<false><<<grid, opm_proj::THREADS, opm_proj::SMEM_BYTES, stream>>>(tmW, pp);
-    B200_CUDA(cudaGetLastError());
+    B200_AFTER_LAUNCH();
     const float* scale_ptr = ext_scale;
     if (mask_ndim == 3 && !ext_scale) {
       opm_inv_row_count_kernel<<<1, 1024, 0, stream>>>(pp.mask, S, N, inv);
-      B200_CUDA(cudaGetLastError());
+      B200_AFTER_LAUNCH();
       scale_ptr = inv;
     }
     for (int i0 = 0; i0 < N; i0 += CI) {
@@ -1010,7 +1066,7 @@ static int triatt_slab(const void* z, const uint8_t* mask, const void* ext_bias,
     triatt_proj_kernel<true><<<grid, triatt_proj::THREADS, triatt_proj::SMEM_BYTES, stream>>>(tmW, tmQKG, tmVT, pp);
   else
     triatt_proj_kernel<false><<<grid, triatt_proj::THREADS, triatt_proj::SMEM_BYTES, stream>>>(tmW, tmQKG, tmVT, pp);
-  B200_CUDA(cudaGetLastError());
+  B200_AFTER_LAUNCH();
   if (!ext_bias) {
     if (int e = launch_pair_bias(z, f32, w->ln_w, w->ln_b, w->w_b, tb, lines, pos, line_b, pos_b, (long long)pos * pl.Nk,
                                  pl.Nk, 4, stream))
@@ -1161,7 +1217,7 @@ int b200_swiglu_fwd(const void* h12, void* h, int64_t rows, int hidden, b200_str
   if (rows == 0) return B200_OK;
   swiglu_rows_kernel<<<grid_for(rows * (hidden / 8), 256), 256, 0, static_cast<cudaStream_t>(stream)>>>(
       static_cast<const __nv_bfloat16*>(h12), static_cast<__nv_bfloat16*>(h), rows, hidden);
-  B200_CUDA(cudaGetLastError());
+  B200_AFTER_LAUNCH();
   return B200_OK;
 }
 
@@ -1183,7 +1239,7 @@ int b200_adaln_fwd(const void* x, const float* cond, int cond_width, int alpha_c
   else
     adaln_rows_kernel<false><<<grid, 256, 0, st>>>(x, cond, cond_width, alpha_col, beta_col, lns,
                                                    static_cast<__nv_bfloat16*>(y), rows, cols, 1e-5f);
-  B200_CUDA(cudaGetLastError());
+  B200_AFTER_LAUNCH();
   return B200_OK;
 }
 
@@ -1203,7 +1259,7 @@ int b200_gated_residual_fwd(void* x, const void* h, const float* cond, int cond_
   else if (xf) gated_residual_rows_kernel<true, false><<<grid, 256, 0, st>>>(x, h, cond, cond_width, gamma_col, rows, cols);
   else if (hf) gated_residual_rows_kernel<false, true><<<grid, 256, 0, st>>>(x, h, cond, cond_width, gamma_col, rows, cols);
   else gated_residual_rows_kernel<false, false><<<grid, 256, 0, st>>>(x, h, cond, cond_width, gamma_col, rows, cols);
-  B200_CUDA(cudaGetLastError());
+  B200_AFTER_LAUNCH();
   return B200_OK;
 }
 

@@ -13,8 +13,12 @@ namespace b200 {
 // Device status word.  A wait that runs out writes a non-zero code here and
 // every later wait in the grid returns at once, so a protocol bug ends the
 // kernel with wrong data and a readable status instead of a hung GPU.
+// The same code is also stored through g_host_status_ptr when the host has set
+// it: a word in pinned, mapped host memory that the host can read without
+// synchronising, so the next library call on that device reports the failure.
 // ---------------------------------------------------------------------------
 __device__ int g_dev_status = 0;  // this header is compiled into exactly one translation unit
+__device__ int* g_host_status_ptr = nullptr;
 
 enum DevStatus : int {
   kDevOk = 0,
@@ -72,7 +76,14 @@ __device__ __noinline__ void mbar_wait_slow(uint64_t* bar, uint32_t parity, int 
     if ((++spins & 0xff) == 0) {
       if (*reinterpret_cast<volatile int*>(&g_dev_status) != 0) return;
       if (clock64() - t0 > (1ll << 31)) {
-        atomicCAS(&g_dev_status, 0, kDevWaitTimeout | (site << 8));
+        const int code = kDevWaitTimeout | (site << 8);
+        if (atomicCAS(&g_dev_status, 0, code) == 0) {
+          int* hp = g_host_status_ptr;
+          if (hp) {
+            *reinterpret_cast<volatile int*>(hp) = code;
+            __threadfence_system();
+          }
+        }
         return;
       }
     }

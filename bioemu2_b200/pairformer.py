@@ -16,6 +16,7 @@ import torch
 import torch.nn as nn
 from torch import Tensor
 
+from . import _lib
 from .attention_pair_bias import AttentionPairBias
 from .transition import Transition
 from .triangle_attention import TriangleAttention
@@ -65,4 +66,5 @@ class PairformerModule(nn.Module):
         pm = (token_mask[:, :, None] & token_mask[:, None, :]).to(torch.uint8)
         for layer in self.layers:
             layer.forward_(s, z, token_mask, pm)
+        _lib.raise_if_device_wait()  # a kernel whose bounded wait ran out earlier in the stack invalidates the result
         return s, z

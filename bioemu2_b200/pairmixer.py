@@ -10,6 +10,7 @@ import torch
 import torch.nn as nn
 from torch import Tensor
 
+from . import _lib
 from .transition import Transition
 from .triangle_multiplication import TriangleMultiplication
 
@@ -58,4 +59,5 @@ class PairMixerModule(nn.Module):
         mask8 = pair_mask.to(torch.uint8).contiguous()  # converted once for all layers
         for layer in self.layers:
             layer.forward_(z, mask8)
+        _lib.raise_if_device_wait()  # a kernel whose bounded wait ran out earlier in the stack invalidates the result
         return s, z

@@ -13,8 +13,10 @@
  *     state_dict tensors);
  *   - the return value is a status code (B200_OK == 0); b200_last_error() gives the message of the
  *     calling thread's last failure.  No exception crosses the boundary.
- *   - kernels bound every wait; if one runs out the kernel finishes with wrong data and
- *     b200_device_status() reports it.
+ *   - kernels bound every wait; if one runs out the kernel finishes with wrong data, writes a status word, and
+ *     every later compute entry point on that device returns B200_ERR_DEVICE_WAIT until b200_device_status()
+ *     has read and cleared it (b200_peek_status() reads it without synchronising).  Kernels that were already
+ *     enqueued behind the failing one still run, and finish early with invalid results.
  */
 #ifndef B200PAIR_H_
 #define B200PAIR_H_
@@ -48,12 +50,23 @@ int b200_version(void);
 /* Message of the calling thread's most recent failure ("" if none). */
 const char* b200_last_error(void);
 
-/* Checks that the current device is compute capability 10.x.  Every compute entry point calls it. */
+/* Checks that the current device is compute capability 10.x and that no earlier kernel on it gave up a bounded
+ * wait (B200_ERR_DEVICE_WAIT otherwise).  Every compute entry point calls it first.  The first call on a device
+ * sets up 64 bytes of pinned host memory through which kernels report such a failure; make that first call
+ * outside any stream capture. */
 int b200_check_device(void);
 
 /* Synchronises the device, then reads and clears the device status word into *status (host pointer).
  * 0 = every kernel wait completed; otherwise low byte 1 = a bounded wait ran out, bits 8.. = its site. */
 int b200_device_status(int* status);
+
+/* The same word as far as kernels that have FINISHED wrote it, read from host memory: no synchronisation, no
+ * CUDA call on the fast path, nothing cleared.  For polling between launches (before a device-to-host copy, before
+ * a collective, at the end of a forward). */
+int b200_peek_status(int* status);
+
+/* Number of kernels this library has launched since it was loaded (all threads, all devices). */
+unsigned long long b200_launch_count(void);
 
 /* ---------------------------------------------------------------------------------------------------
  * Row LayerNorm: y[r,:] = (x[r,:] - mean) * rsqrt(var + eps) * w + b over `cols` (multiple of 8, <= 1024).
@@ -144,8 +157,10 @@ int b200_bmm_nt(const void* A, const void* B, void* C, int batch, int M, int N, 
  * allocating library routine.  The first call on each device resolves the array's device address
  * (cudaGetSymbolAddress with that device current); make that first call outside any stream capture.
  * All calls on a device share the one array: calls that may overlap on the GPU (different streams) race and
- * must be serialised by the caller.  Nothing in the array needs to start at zero -- every element that is
- * read has been written earlier in the same call -- so it is not cleared between calls.
+ * must be serialised by the caller.  Nothing in the array needs to start at zero, so it is not cleared between
+ * calls: the planes are padded to a multiple of 128 rows and columns, the padding may hold what an earlier call
+ * left there (any bit pattern), and it is read only into padded rows and columns of the intermediate products,
+ * whose results are never stored to the output.
  * ------------------------------------------------------------------------------------------------- */
 int b200_trimul_fwd_static(const void* z, const uint8_t* mask, void* out, const b200_trimul_weights* w, int B, int N,
                            int incoming, int add_residual, int z_dtype, b200_stream_t stream);

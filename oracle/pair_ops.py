@@ -36,11 +36,15 @@ def linear(x: Tensor, weight: Tensor, bias: Tensor | None = None) -> Tensor:
     return y if bias is None else y + bias
 
 
-def triangle_multiplication(x: Tensor, mask: Tensor, w: dict, mode: str) -> Tensor:
+def triangle_multiplication(x: Tensor, mask: Tensor, w: dict, mode: str, rows: slice | None = None) -> Tensor:
     """``TriangleMultiplicationFull.forward``.
 
     src/bioemu2/biomoa/ops/triangle_multiplication.py:86-99 (weights :62-76).
     No residual: the caller adds it (src/bioemu2/biomoa/modules/pairmixer.py:447-452).
+
+    ``rows`` restricts the result to output rows ``i in rows`` (the projections still see the whole tensor,
+    only the contraction and the output stage are cut down): the check used at sizes where the full
+    contraction would take the CPU minutes.
     """
     assert mode in ("outgoing", "incoming")
     h = layer_norm(x, w["norm_in.weight"], w["norm_in.bias"])
@@ -48,11 +52,12 @@ def triangle_multiplication(x: Tensor, mask: Tensor, w: dict, mode: str) -> Tens
     proj = torch.where(mask.bool().unsqueeze(-1), proj, torch.zeros_like(proj))
     a, b = proj.chunk(2, dim=-1)
     if mode == "outgoing":
-        t = torch.einsum("bikd,bjkd->bijd", a, b)
+        t = torch.einsum("bikd,bjkd->bijd", a if rows is None else a[:, rows], b)
     else:
-        t = torch.einsum("bkid,bkjd->bijd", a, b)
+        t = torch.einsum("bkid,bkjd->bijd", a if rows is None else a[:, :, rows], b)
     t = layer_norm(t, w["norm_out.weight"], w["norm_out.bias"])
-    return linear(t, w["p_out.weight"]) * torch.sigmoid(linear(h, w["g_out.weight"]))
+    h_rows = h if rows is None else h[:, rows]
+    return linear(t, w["p_out.weight"]) * torch.sigmoid(linear(h_rows, w["g_out.weight"]))
 
 
 def transition(x: Tensor, w: dict) -> Tensor:
@@ -110,11 +115,12 @@ def attention_pair_bias(
     return linear(g * o, w["proj_o.weight"])
 
 
-def outer_product_mean(m: Tensor, mask: Tensor, w: dict) -> Tensor:
+def outer_product_mean(m: Tensor, mask: Tensor, w: dict, i_chunk: int | None = None) -> Tensor:
     """``OuterProductMeanVanilla.forward``.
 
     src/bioemu2/biomoa/ops/outer_product_mean.py:45-75.  ``mask`` is ``[B,S,N]``
-    (rows averaged over, :66-67) or ``[B,N]`` (divisor 1, :68-69).
+    (rows averaged over, :66-67) or ``[B,N]`` (divisor 1, :68-69).  ``i_chunk`` only bounds the size of the
+    ``[B, i, N, c, c]`` outer-product tensor (the reference's ``tile_size`` plays the same role).
     """
     mask = mask.bool()
     c_hidden = w["proj_ab.weight"].shape[0] // 2
@@ -125,9 +131,14 @@ def outer_product_mean(m: Tensor, mask: Tensor, w: dict) -> Tensor:
         num_valid = mask.any(dim=-1).sum(dim=1).clamp(min=1).to(m.dtype)
     else:
         num_valid = torch.ones(m.shape[0], dtype=m.dtype)
-    z = torch.einsum("bsic,bsjd->bijcd", a, b)
-    z = z.reshape(*z.shape[:3], c_hidden * c_hidden) / num_valid[:, None, None, None]
-    return linear(z, w["proj_o.weight"], w["proj_o.bias"])
+    n = m.shape[2]
+    step = n if i_chunk is None else i_chunk
+    outs = []
+    for i0 in range(0, n, step):
+        z = torch.einsum("bsic,bsjd->bijcd", a[:, :, i0:i0 + step], b)
+        z = z.reshape(*z.shape[:3], c_hidden * c_hidden) / num_valid[:, None, None, None]
+        outs.append(linear(z, w["proj_o.weight"], w["proj_o.bias"]))
+    return torch.cat(outs, dim=1)
 
 
 def _sub(w: dict, prefix: str) -> dict:
@@ -155,7 +166,7 @@ def pairmixer_module(z: Tensor, pair_mask: Tensor, w: dict, num_blocks: int) -> 
 
 
 def triangle_attention(x: Tensor, mask: Tensor, w: dict, num_heads: int, ending: bool, inf: float = 1e6,
-                       row_chunk: int | None = None) -> Tensor:
+                       row_chunk: int | None = None, lines: slice | None = None) -> Tensor:
     """Triangle self-attention around the starting (or ending) node.
 
     NOT IN THE REFERENCE -- parity unpinned.  The reference removed this op
@@ -168,7 +179,9 @@ def triangle_attention(x: Tensor, mask: Tensor, w: dict, num_heads: int, ending:
     ``x[B,N,N,D]``, ``mask[B,N,N]``.  Starting node: row ``i`` attends from
     ``j`` to ``k`` with logits ``q[i,j]·k[i,k]/sqrt(dh) + bias[j,k]`` and keys
     masked by ``mask[i,k]``.  Ending node is the same on the transposed pair
-    tensor.
+    tensor.  ``lines`` restricts the result to attention lines ``i in lines``
+    (rows of the output for the starting node, columns for the ending node);
+    the triangle bias still comes from the whole tensor.
     """
     if ending:
         x = x.transpose(1, 2)
@@ -183,18 +196,19 @@ def triangle_attention(x: Tensor, mask: Tensor, w: dict, num_heads: int, ending:
     tri_bias = linear(h, w["linear_b.weight"]).permute(0, 3, 1, 2)  # [B,H,j,k]
     g = torch.sigmoid(linear(h, w["linear_g.weight"], w["linear_g.bias"]))
     # rows i are independent; row_chunk only bounds the size of the [B, rows, H, N, N] logits tensor
-    step = N if row_chunk is None else row_chunk
+    lo, hi, _ = (lines or slice(None)).indices(N)
+    step = (hi - lo) if row_chunk is None else row_chunk
     o_rows = []
-    for i0 in range(0, N, step):
-        sl = slice(i0, min(i0 + step, N))
+    for i0 in range(lo, hi, step):
+        sl = slice(i0, min(i0 + step, hi))
         logits = torch.einsum("bijhd,bikhd->bihjk", q[:, sl], k[:, sl]) / math.sqrt(dh)
         logits = logits + tri_bias.unsqueeze(1)
         key_mask = mask[:, sl].bool().view(B, -1, 1, 1, N)
         logits = torch.where(key_mask, logits, torch.full_like(logits, -inf))
         p = logits.softmax(dim=-1)
         o_rows.append(torch.einsum("bihjk,bikhd->bijhd", p, v[:, sl]))
-    o = torch.cat(o_rows, dim=1).reshape(B, N, N, H * dh)
-    out = linear(g * o, w["linear_o.weight"])
+    o = torch.cat(o_rows, dim=1).reshape(B, hi - lo, N, H * dh)
+    out = linear(g[:, lo:hi] * o, w["linear_o.weight"])
     if ending:
         out = out.transpose(1, 2)
     return out

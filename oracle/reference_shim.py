@@ -4,7 +4,10 @@ TEST INFRASTRUCTURE ONLY.  The reference package's ``__init__`` pulls
 dependencies (mdtraj, rdkit) that this image lacks, so two stub modules are
 registered before the hot-path files are imported from the reference checkout.
 Used by ``tests/golden/make_golden.py`` and by the pinning tests, both of which
-skip when the checkout is absent (it never travels to a GPU box).
+skip when the checkout is absent (it never travels to a GPU box).  The checkout is
+found through the environment variable ``BIOEMU2_REFERENCE_SRC`` (the directory that
+contains the ``bioemu2`` package) or, failing that, as a checkout named ``reference``
+beside this repository; otherwise the shim reports "not available".
 """
 from __future__ import annotations
 
@@ -12,11 +15,12 @@ import os
 import sys
 import types
 
-REFERENCE_SRC = os.environ.get("BIOEMU2_REFERENCE_SRC", "/root/reference/src")
+_SIBLING = os.path.join(os.path.dirname(os.path.dirname(os.path.dirname(os.path.abspath(__file__)))), "reference", "src")
+REFERENCE_SRC = os.environ.get("BIOEMU2_REFERENCE_SRC") or (_SIBLING if os.path.isdir(_SIBLING) else "")
 
 
 def available() -> bool:
-    return os.path.isdir(os.path.join(REFERENCE_SRC, "bioemu2", "biomoa", "ops"))
+    return bool(REFERENCE_SRC) and os.path.isdir(os.path.join(REFERENCE_SRC, "bioemu2", "biomoa", "ops"))
 
 
 def install() -> None:
@@ -24,7 +28,8 @@ def install() -> None:
     if "bioemu2" in sys.modules and getattr(sys.modules["bioemu2"], "_oracle_shim", False):
         return
     if not available():
-        raise RuntimeError(f"reference checkout not found under {REFERENCE_SRC}")
+        raise RuntimeError("reference checkout not found: set BIOEMU2_REFERENCE_SRC to the directory holding the "
+                           "bioemu2 package")
     pkg = types.ModuleType("bioemu2")
     pkg.__path__ = [os.path.join(REFERENCE_SRC, "bioemu2")]
     pkg.HAS_TRITON = True  # src/bioemu2/__init__.py exports this flag

@@ -37,3 +37,22 @@ def test_layernorm_rows():
         y = F.layernorm(x, w, b)
         ref = torch.nn.functional.layer_norm(x.double(), (cols,), w.double(), b.double())
         assert_close(f"layernorm[{cols}]", y, ref, rel=5e-3)
+
+
+def test_linear_bias_is_not_read_past_its_end():
+    """out_features = 160 is a multiple of 32 but not of the 128-column output tile: the last column tile of the bulk
+    epilogue must not read bias entries beyond the 160th.  The bias sits at the very end of its allocation and the
+    columns beyond it are poisoned, so an unguarded read would show up as NaN or as a fault."""
+    from bioemu2_b200 import functional as F
+
+    g = torch.Generator().manual_seed(5)
+    rows, fin, fout = 256, 64, 160
+    x = torch.randn(rows, fin, generator=g)
+    w = torch.randn(fout, fin, generator=g) / 8
+    store = torch.full((4096,), float("nan"))
+    store[-fout:] = torch.randn(fout, generator=g)
+    bias = store.cuda()[-fout:]
+    for out_dtype in (torch.float32, torch.bfloat16):
+        out = F.linear_bf16(x.bfloat16().cuda(), w.bfloat16().cuda(), bias, out_dtype=out_dtype)
+        ref = x.bfloat16().double() @ w.bfloat16().double().T + store[-fout:].double()
+        assert_close(f"linear_out160_bias_{out_dtype}", out, ref)
