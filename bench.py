@@ -96,17 +96,18 @@ def block_weights(gen, kind: str) -> dict:
 
 
 def workload(tokens: int, blocks: int, kind: str, seed: int = 2):
-    """Seeded synthetic trunk input: z, s ~ N(0,1), last 37 tokens padded (scaled for other sizes)."""
+    """Seeded synthetic trunk input: z, s ~ N(0,1), last 37 tokens padded (scaled for other sizes).  The inputs are
+    drawn before the weights and the weights block by block, so neither depends on how many blocks are asked for."""
     import helpers as H
 
     g = torch.Generator().manual_seed(seed)
-    w = {}
-    for i in range(blocks):
-        w.update(H.prefixed(f"layers.{i}", block_weights(g, kind)))
     z = torch.randn(1, tokens, tokens, 128, generator=g)
     s = torch.randn(1, tokens, 384, generator=g)
     tok = torch.ones(1, tokens, dtype=torch.bool)
     tok[0, tokens - pad_tokens(tokens):] = False
+    w = {}
+    for i in range(blocks):
+        w.update(H.prefixed(f"layers.{i}", block_weights(g, kind)))
     return w, s, z, tok
 
 

@@ -10,6 +10,7 @@ from .outer_product_mean import (
 )
 from .pairformer import PairformerBlock, PairformerModule
 from .pairmixer import PairMixerLayer, PairMixerModule
+from .swap import swap_into, to_b200
 from .transformer import AttentionLayer, ConditionedTransformerLayer
 from .transition import Transition
 from .triangle_attention import (
@@ -36,6 +37,8 @@ __all__ = [
     "PairformerModule",
     "PairMixerLayer",
     "PairMixerModule",
+    "swap_into",
+    "to_b200",
     "Transition",
     "TriangleAttention",
     "TriangleAttentionEndingNode",

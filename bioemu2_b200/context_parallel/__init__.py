@@ -2,8 +2,13 @@
 R x C grid, NCCL all-gather / reduce-scatter over row and column groups around the single-GPU kernels."""
 from .mesh import CPGrid, GridCoords, kernel_shard_multiple, pad_amount, shard_multiple, shard_range
 from .attention import cp_attention_pair_bias, cp_outer_product_mean, cp_triangle_attention_
+from . import ops
 from .modules import (
     CPAttentionPairBias,
+    CPConditionedTransformerLayer,
+    DistributedConditionedTransformerLayer,
+    DistributedPairMixerLayer,
+    DistributedPairMixerModule,
     CPOuterProductMean,
     CPPairformerBlock,
     CPPairformerModule,
@@ -17,7 +22,8 @@ from .trimul import cp_triangle_multiplication_
 
 __all__ = [
     "CPGrid", "GridCoords", "kernel_shard_multiple", "pad_amount", "shard_multiple", "shard_range",
-    "CPAttentionPairBias", "CPOuterProductMean", "CPPairformerBlock", "CPPairformerModule", "CPPairMixerLayer", "CPPairMixerModule", "CPTransition",
+    "ops", "CPConditionedTransformerLayer", "DistributedConditionedTransformerLayer", "DistributedPairMixerLayer",
+    "DistributedPairMixerModule", "CPAttentionPairBias", "CPOuterProductMean", "CPPairformerBlock", "CPPairformerModule", "CPPairMixerLayer", "CPPairMixerModule", "CPTransition",
     "CPTriangleAttention", "CPTriangleMultiplication", "cp_attention_pair_bias", "cp_outer_product_mean",
     "cp_triangle_attention_", "cp_triangle_multiplication_",
 ]

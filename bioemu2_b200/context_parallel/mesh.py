@@ -90,6 +90,57 @@ class CPGrid:
             if c == self.coords.c:
                 self.col_group = g
 
+    _FROM_MESH: dict = {}
+
+    @classmethod
+    def from_device_mesh(cls, device_mesh) -> "CPGrid":
+        """The grid of a ``torch.distributed`` ``DeviceMesh`` laid out as the reference lays its own out:
+        ``(dp, cp_axis_0, cp_axis_1)`` (src/bioemu2/context_parallel/utils/mesh.py:17-39 reads the two cp sizes from
+        mesh dimensions 1 and 2).  Rows of the pair tensor go over dimension 1, columns over dimension 2; the mesh's
+        own process groups along those dimensions become the column and row groups.  A 2-D mesh is taken as
+        ``(cp_axis_0, cp_axis_1)``.  Collective on first use for a given mesh (the group spanning both cp axes is
+        created here); the result is cached per mesh.
+        """
+        key = id(device_mesh)
+        hit = cls._FROM_MESH.get(key)
+        if hit is not None and hit[0] is device_mesh:
+            return hit[1]
+        if device_mesh.ndim == 3:
+            d0, d1, n_dp = 1, 2, device_mesh.size(0)
+        elif device_mesh.ndim == 2:
+            d0, d1, n_dp = 0, 1, 1
+        else:
+            raise ValueError(f"expected a (dp, cp_axis_0, cp_axis_1) or (cp_axis_0, cp_axis_1) mesh, got {device_mesh.ndim} dims")
+        rows, cols = device_mesh.size(d0), device_mesh.size(d1)
+        layout = device_mesh.mesh.reshape(n_dp, rows, cols)
+        me = dist.get_rank()
+        where = (layout == me).nonzero()
+        if where.shape[0] != 1:
+            raise ValueError("this rank is not part of the device mesh")
+        dp, r, c = (int(v) for v in where[0])
+        grid = cls.__new__(cls)
+        grid.coords = GridCoords(rows, cols, r, c)
+        grid.row_group = device_mesh.get_group(d1)   # ranks (r, *): they differ along cp_axis_1
+        grid.col_group = device_mesh.get_group(d0)   # ranks (*, c)
+        grid.group = None
+        for i in range(n_dp):                        # every rank creates every dp slice's group, in the same order
+            members = [int(v) for v in layout[i].flatten()]
+            if n_dp == 1 and members == list(range(dist.get_world_size())):
+                break                                # the default group already is the cp group
+            g = dist.new_group(members)
+            if i == dp:
+                grid.group = g
+        # collectives return members in group-rank order, which torch keeps sorted by global rank: the gathers below
+        # rely on that order being (r, c) row-major, c along the row group and r along the column group
+        for grp, want in ((grid.group, [int(v) for v in layout[dp].flatten()]),
+                          (grid.row_group, [int(v) for v in layout[dp, r]]),
+                          (grid.col_group, [int(v) for v in layout[dp, :, c]])):
+            have = dist.get_process_group_ranks(grp) if grp is not None else list(range(dist.get_world_size()))
+            if list(have) != want:
+                raise ValueError(f"device mesh layout {want} is not in increasing rank order along its cp axes ({have})")
+        cls._FROM_MESH[key] = (device_mesh, grid)
+        return grid
+
     @property
     def rows(self) -> int:
         return self.coords.rows

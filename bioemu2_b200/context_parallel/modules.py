@@ -75,11 +75,21 @@ class CPTransition(nn.Module):
         return x
 
 
-class CPPairMixerLayer(nn.Module):
-    """``z -> z`` after triangle multiplication out / in and the pair transition, all in place on the local block."""
+def _grid(grid_or_mesh) -> CPGrid:
+    """A ``CPGrid`` as given, or the one of a ``DeviceMesh`` / of an object exposing ``device_mesh_subgroups``."""
+    if isinstance(grid_or_mesh, CPGrid):
+        return grid_or_mesh
+    return CPGrid.from_device_mesh(getattr(grid_or_mesh, "device_mesh_subgroups", grid_or_mesh))
 
-    def __init__(self, serial, grid: CPGrid, backend=None) -> None:
+
+class CPPairMixerLayer(nn.Module):
+    """``z -> z`` after triangle multiplication out / in and the pair transition, all in place on the local block.
+    ``grid`` may be a ``CPGrid``, a ``DeviceMesh`` or the reference's distributed manager
+    (``DistributedPairMixerLayer(serial, dist_manager)``, src/bioemu2/context_parallel/modules/pairmixer.py:77-99)."""
+
+    def __init__(self, serial, grid, backend=None) -> None:
         super().__init__()
+        grid = _grid(grid)
         self.tri_mul_out = CPTriangleMultiplication(serial.tri_mul_out, grid, backend)
         self.tri_mul_in = CPTriangleMultiplication(serial.tri_mul_in, grid, backend)
         self.transition_z = CPTransition(serial.transition_z, grid)
@@ -91,8 +101,12 @@ class CPPairMixerLayer(nn.Module):
 
 
 class CPPairMixerModule(nn.Module):
-    def __init__(self, serial, grid: CPGrid, backend=None) -> None:
+    """``DistributedPairMixerModule(serial, dist_manager)`` of the reference
+    (src/bioemu2/context_parallel/modules/pairmixer.py:102-115); ``grid`` as for ``CPPairMixerLayer``."""
+
+    def __init__(self, serial, grid, backend=None) -> None:
         super().__init__()
+        grid = _grid(grid)
         self.layers = nn.ModuleList(CPPairMixerLayer(layer, grid, backend) for layer in serial.layers)
 
     def forward(self, z, pair_mask):
@@ -156,7 +170,12 @@ class CPOuterProductMean(nn.Module):
         packed = self.serial.packed()
         outs = [cp_outer_product_mean(ml[b], kl[b], row_count[b:b + 1], packed, self.grid, local=self.local)
                 for b in range(ml.shape[0])]
-        return torch.stack(outs).to(ml.dtype)
+        out = torch.stack(outs).to(ml.dtype)
+        if hasattr(m, "to_local"):  # pair placements: batch, rows and columns sharded like the input's three axes
+            from torch.distributed.tensor import DTensor
+
+            return DTensor.from_local(out, m.device_mesh, m.placements, run_check=False)
+        return out
 
 
 class CPPairformerBlock(nn.Module):
@@ -213,3 +232,34 @@ class CPPairformerModule(nn.Module):
 
     def forward(self, s, z, mask_rows, mask_cols):
         return self.forward_(s.clone(), z.clone(), mask_rows, mask_cols)
+
+
+class CPConditionedTransformerLayer(nn.Module):
+    """The token block of the diffusion module on sharded inputs
+    (``DistributedConditionedTransformerLayer(serial, dist_manager)``,
+    src/bioemu2/context_parallel/layers/transformer_layers.py:29-67).
+
+    The token stream ``x[B*M, n_r, dim]``, the conditioning ``c`` and the mask are row-sharded and replicated over the
+    grid's columns, ``pairs`` is this rank's block of the pair tensor.  Conditioning, adaptive LayerNorm, gated
+    residuals and the transition touch only local rows; the attention is the context-parallel one.
+    """
+
+    def __init__(self, serial, grid) -> None:
+        super().__init__()
+        self.serial = serial
+        self.attention = CPAttentionPairBias(serial.attention.pair_bias_attn, _grid(grid))
+
+    def forward(self, x, pairs, c, mask=None, multiplicity: int = 1):
+        xl, pl, cl = _local(x), _local(pairs), _local(c)
+        ml = _local(mask) if mask is not None else torch.ones(pl.shape[0], pl.shape[1], dtype=torch.bool, device=xl.device)
+        out = self.serial._forward(xl, pl, cl, ml, multiplicity, lambda s, z, m, mult: self.attention(s, z, m, mult))
+        if hasattr(x, "to_local"):
+            from torch.distributed.tensor import DTensor
+
+            return DTensor.from_local(out, x.device_mesh, x.placements, run_check=False)
+        return out
+
+
+DistributedPairMixerLayer = CPPairMixerLayer
+DistributedPairMixerModule = CPPairMixerModule
+DistributedConditionedTransformerLayer = CPConditionedTransformerLayer

@@ -60,12 +60,17 @@ class ConditionedTransformerLayer(PackedWeightsMixin, nn.Module):
     def forward(self, x: Tensor, pairs: Tensor, c: Tensor, mask: Tensor | None = None, multiplicity: int = 1) -> Tensor:
         if mask is None:
             mask = torch.ones(pairs.shape[0], pairs.shape[1], dtype=torch.bool, device=x.device)
+        return self._forward(x, pairs, c, mask, multiplicity, self.attention)
+
+    def _forward(self, x: Tensor, pairs: Tensor, c: Tensor, mask: Tensor, multiplicity: int, attention) -> Tensor:
+        """The block with the attention supplied by the caller (``attention(tokens, pairs, mask, multiplicity)``): the
+        serial layer passes its own, the context-parallel wrapper the sharded one; everything else is per token."""
         w_cond, b_cond = self.packed()
         D = self.dim
         cn = F.rows_to_bf16(c, self.cond[0].weight, self.cond[0].bias, normalize=True, silu=True)
         cond = F.linear_bf16(cn, w_cond, b_cond, out_dtype=torch.float32)  # [rows, 6*dim] fp32
         x = x.contiguous().clone()
-        h = self.attention(F.adaln(x, cond, 0, D, self.lns_scale), pairs, mask, multiplicity)
+        h = attention(F.adaln(x, cond, 0, D, self.lns_scale), pairs, mask, multiplicity)
         F.gated_residual_(x, h, cond, 2 * D)
         h = self.transition(F.adaln(x, cond, 3 * D, 4 * D, self.lns_scale))
         F.gated_residual_(x, h, cond, 5 * D)

@@ -168,3 +168,167 @@ def test_cp_attention_ops_match_serial_on_gloo(rows, cols, n):
     for _ in range(world):
         rank, errs = q.get(timeout=5)
         assert max(errs.values()) < 1e-7, (rank, errs)  # the 1/row_count scale is an fp32 scalar
+
+
+# --------------------------------------------------------------------------------------------------------------
+# The reference's calling convention: DTensors on a (dp, cp_axis_0, cp_axis_1) DeviceMesh, wrapper constructors
+# (direction, layer, device_mesh, comm), in-place update returning the very object that was passed in.
+class _OracleLayer:
+    """Stands in for a loaded serial triangle multiplication on CPU: ``packed()`` hands the CPU backend its weights."""
+
+    def __init__(self, w, mode):
+        from cp_cpu_backend import OracleWeights
+
+        self.mode = mode
+        self._packed = OracleWeights(w, mode)
+
+    def packed(self):
+        return self._packed
+
+
+def _dtensor_worker(rank, world, port, q):
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    torch.set_num_threads(1)
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        from torch.distributed.device_mesh import init_device_mesh
+        from torch.distributed.tensor import DTensor, Shard, distribute_tensor
+
+        from bioemu2_b200.context_parallel import CPGrid
+        from bioemu2_b200.context_parallel.ops import TriangleMultiplicationAddRes
+        from cp_cpu_backend import CpuTriMulBackend
+
+        mesh = init_device_mesh("cpu", (1, 2, 2), mesh_dim_names=("dp", "cp_axis_0", "cp_axis_1"))
+        grid = CPGrid.from_device_mesh(mesh)
+        assert (grid.rows, grid.cols, grid.coords.r, grid.coords.c) == (2, 2, rank // 2, rank % 2)
+        assert CPGrid.from_device_mesh(mesh) is grid  # cached: no second round of group creation
+        n = 12
+        g = torch.Generator().manual_seed(9)
+        w = {k: v.double() for k, v in H.trimul_weights(g, 16).items()}
+        z = torch.randn(1, n, n, 16, generator=g).double()
+        mask = torch.rand(1, n, n, generator=g) > 0.25
+        placements = (Shard(0), Shard(1), Shard(2))
+        errs = {}
+        for direction in ("Outgoing", "Incoming"):
+            ref = z + O.triangle_multiplication(z, mask, w, direction.lower())
+            zd = distribute_tensor(z.clone(), mesh, placements)
+            md = distribute_tensor(mask.clone(), mesh, placements)
+            op = TriangleMultiplicationAddRes(direction, _OracleLayer(w, direction.lower()), mesh, comm=None,
+                                              backend=CpuTriMulBackend())
+            ret = op(zd, md)
+            assert ret is zd and isinstance(ret, DTensor), "the update is in place and returns the object it was given"
+            errs[direction] = float((zd.full_tensor() - ref).abs().max())
+        q.put((rank, errs))
+    finally:
+        dist.destroy_process_group()
+
+
+def test_reference_style_wrapper_on_dtensors_2x2():
+    """src/bioemu2/context_parallel/ops/triangle_multiplication.py:45-67 (constructor) and
+    tests/context_parallel/ops/test_trimul_serial_vs_cp.py:89 (same object returned) in the reference."""
+    world = 4
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    port = 33000 + os.getpid() % 2000
+    procs = [ctx.Process(target=_dtensor_worker, args=(r, world, port, q)) for r in range(world)]
+    for p in procs:
+        p.start()
+    for p in procs:
+        p.join(180)
+        assert p.exitcode == 0
+    for _ in range(world):
+        rank, errs = q.get(timeout=5)
+        assert max(errs.values()) < 1e-10, (rank, errs)
+
+
+def _bad_shape_worker(rank, world, port, q):
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        from bioemu2_b200.context_parallel import CPGrid
+        from bioemu2_b200.context_parallel.trimul import cp_triangle_multiplication_
+        from cp_cpu_backend import CpuTriMulBackend, OracleWeights
+
+        grid = CPGrid(1, 2)
+
+        def no_collective(*a, **k):
+            raise AssertionError("a collective was reached with inconsistent shapes")
+
+        grid.all_gather = grid.reduce_scatter = grid.all_to_all = no_collective
+        g = torch.Generator().manual_seed(3)
+        w = {k: v.double() for k, v in H.trimul_weights(g, 16).items()}
+        outcome = []
+        for z_shape, m_shape, n_tokens in (((12, 6, 16), (12, 5), 12),     # mask does not match the block
+                                           ((12, 7, 16), (12, 7), 12)):    # block is not a cell of the 1x2 grid
+            try:
+                cp_triangle_multiplication_(torch.zeros(z_shape, dtype=torch.float64), torch.ones(m_shape, dtype=torch.bool),
+                                            OracleWeights(w, "outgoing"), grid, False, n_tokens, backend=CpuTriMulBackend())
+                outcome.append("no error")
+            except ValueError as exc:
+                outcome.append(f"ValueError: {exc}")
+        q.put((rank, outcome))
+    finally:
+        dist.destroy_process_group()
+
+
+def test_shape_errors_are_raised_on_every_rank_before_any_collective():
+    """The reference raises shape and placement violations on every rank before communicating
+    (src/bioemu2/context_parallel/ops/triangular_mult_impl.py:431-522; tests/context_parallel/helpers.py:64-67)."""
+    world = 2
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    port = 35000 + os.getpid() % 2000
+    procs = [ctx.Process(target=_bad_shape_worker, args=(r, world, port, q)) for r in range(world)]
+    for p in procs:
+        p.start()
+    for p in procs:
+        p.join(120)
+        assert p.exitcode == 0
+    for _ in range(world):
+        rank, outcome = q.get(timeout=5)
+        assert len(outcome) == 2 and all(o.startswith("ValueError") for o in outcome), (rank, outcome)
+
+
+def _absent_rank_worker(rank, world, port, q):
+    import datetime
+    import time
+
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=world, timeout=datetime.timedelta(seconds=4))
+    from bioemu2_b200.context_parallel import CPGrid
+
+    grid = CPGrid(1, 2)
+    t0 = time.time()
+    if rank == 1:
+        # this rank fails on the host before the exchange and never joins it
+        q.put((rank, "raised before the collective", 0.0))
+        time.sleep(8)  # stay alive past the peer's timeout, so the peer sees a missing partner, not a closed socket
+        return
+    try:
+        grid.all_gather(torch.zeros(4), grid.row_group)
+        q.put((rank, "collective returned", time.time() - t0))
+    except Exception as exc:  # gloo reports the timeout as a RuntimeError / DistBackendError
+        q.put((rank, f"{type(exc).__name__}", time.time() - t0))
+
+
+def test_a_rank_that_never_joins_ends_the_peers_collective_with_an_error():
+    """Failure made on the host: one rank raises before the exchange; the other's collective is bounded by the process
+    group's timeout and surfaces as an exception instead of a hang (no GPU involved)."""
+    world = 2
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    port = 37000 + os.getpid() % 2000
+    procs = [ctx.Process(target=_absent_rank_worker, args=(r, world, port, q)) for r in range(world)]
+    for p in procs:
+        p.start()
+    got = dict((r, (what, dt)) for r, what, dt in (q.get(timeout=60) for _ in range(world)))
+    for p in procs:
+        p.join(30)
+        if p.is_alive():
+            p.kill()
+    assert got[1][0] == "raised before the collective"
+    what, dt = got[0]
+    assert what != "collective returned" and dt < 30, got
