@@ -2,7 +2,7 @@
 ``nn.Module`` contracts.  Importing the package loads the CUDA library; without it the import fails."""
 from . import _lib  # noqa: F401  (fails loudly when the library is not built)
 from . import context_parallel, functional
-from .attention_pair_bias import AttentionPairBias
+from .attention_pair_bias import AttentionPairBias, PairBiasCache
 from .outer_product_mean import (
     OuterProductMean,
     OuterProductMeanTritonMemorySaving,
@@ -28,6 +28,7 @@ __all__ = [
     "context_parallel",
     "functional",
     "AttentionPairBias",
+    "PairBiasCache",
     "OuterProductMean",
     "OuterProductMeanTritonMemorySaving",
     "OuterProductMeanVanilla",

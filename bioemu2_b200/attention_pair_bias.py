@@ -54,8 +54,104 @@ class AttentionPairBias(PackedWeightsMixin, nn.Module):
             self.norm_z.weight, self.norm_z.bias, self.proj_z.weight, self.proj_o.weight,
             self.norm_s.weight if self.initial_norm else None, self.norm_s.bias if self.initial_norm else None)
 
+    _bias_cache = None   # (PairBiasCache, index of this module in it) once a cache has adopted the module
+
     def forward(self, s: Tensor, z: Tensor, mask: Tensor, multiplicity: int = 1) -> Tensor:
         """``s[B*M,N,c_s]``, ``z[B,N,N,c_z]``, ``mask[B,N]`` bool -> ``[B*M,N,c_s]``."""
         assert s.ndim == 3 and z.ndim == 4 and mask.ndim == 2, f"{s.shape}, {z.shape}, {mask.shape}"
         assert s.shape[0] == z.shape[0] * multiplicity, f"{s.shape}, {z.shape}, multiplicity={multiplicity}"
+        if self._bias_cache is not None:
+            cache, index = self._bias_cache
+            bias = cache.lookup(index, z)
+            if bias is not None:
+                return F.attention_pair_bias_with_bias(s, bias, mask, self.packed(), multiplicity)
         return F.attention_pair_bias(s, z, mask, self.packed(), multiplicity)
+
+
+class PairBiasCache:
+    """The pair biases ``proj_z(norm_z(z))`` of a stack of ``AttentionPairBias`` modules, computed in ONE pass over a
+    pair tensor that stays the same for many calls.
+
+    The diffusion module runs its token blocks once per denoising step on a pair tensor that is part of the static
+    context (``compute_static_context``, src/bioemu2/biomoa/modules/diffusion.py:197-208; the layer loop :307-320), yet
+    the reference projects the bias again in every layer of every step (src/bioemu2/biomoa/ops/attention_pair_bias.py:163),
+    which re-reads all of ``z`` each time.  ``prepare(z)`` normalises ``z`` once (LayerNorm without its affine part,
+    bf16) and multiplies it by all layers' projection weights at once -- the LayerNorm weights are folded into the
+    projection rows -- giving ``[L, B, H, N, N]`` in bf16, already in the base-2 units the attention kernel works in.
+    Afterwards a forward call of an adopted module that is handed the SAME tensor object (same storage, same version
+    counter, same shape) skips its own projection and reads its slice; any other ``z`` takes the normal path.
+
+        cache = PairBiasCache([layer.token_block.attention.pair_bias_attn for layer in diffusion.layers])
+        cache.prepare(context.z)          # once per static context
+        ...                               # the model's forward calls are unchanged
+
+    Modules whose ``norm_z`` carries a bias, or a token count that is not a multiple of 8, fall back to one projection
+    pass per layer inside ``prepare`` (still once per static context instead of once per step).
+    """
+
+    def __init__(self, attentions) -> None:
+        self.attentions = list(attentions)
+        if not self.attentions:
+            raise ValueError("PairBiasCache needs at least one AttentionPairBias module")
+        for i, a in enumerate(self.attentions):
+            if not isinstance(a, AttentionPairBias):
+                raise TypeError(f"module {i} is a {type(a).__name__}, not a bioemu2_b200 AttentionPairBias")
+            a._bias_cache = (self, i)
+        self._key = None
+        self._bias = None
+        self._weights = None
+        self._weights_key = None
+
+    def release(self) -> None:
+        self._key, self._bias = None, None
+
+    @staticmethod
+    def _z_key(z: Tensor):
+        return (z.data_ptr(), z._version, tuple(z.shape), z.dtype, str(z.device))
+
+    def _fused_weights(self, device):
+        key = tuple((a.proj_z.weight.data_ptr(), a.proj_z.weight._version, a.norm_z.weight.data_ptr(),
+                     a.norm_z.weight._version) for a in self.attentions) + (str(device),)
+        if self._weights is None or key != self._weights_key:
+            with torch.no_grad():
+                rows = [a.proj_z.weight.detach().float() * a.norm_z.weight.detach().float()[None, :] * F.LOG2E
+                        for a in self.attentions]
+                self._weights = torch.cat(rows, dim=0).to(device=device, dtype=torch.bfloat16).contiguous()
+            self._weights_key = key
+        return self._weights
+
+    def prepare(self, z: Tensor) -> Tensor:
+        """Compute and keep the biases of every adopted module for ``z[B, N, N, 128]``; returns ``[L, B, H, N, pitch]``."""
+        if z.ndim != 4 or z.shape[1] != z.shape[2] or z.shape[3] != 128:
+            raise ValueError(f"expected z[B,N,N,128], got {tuple(z.shape)}")
+        B, N = z.shape[0], z.shape[1]
+        heads = {a.num_heads for a in self.attentions}
+        one_pass = (len(heads) == 1 and N % 8 == 0 and all(a.norm_z.bias is None for a in self.attentions))
+        with torch.no_grad():
+            if one_pass:
+                H, L = heads.pop(), len(self.attentions)
+                w_all = self._fused_weights(z.device)                               # [L*H, 128]
+                bias = torch.empty(L, B, H, N, N, dtype=torch.bfloat16, device=z.device)
+                zc = z.contiguous()
+                for b in range(B):
+                    zhat = F.rows_to_bf16(zc[b].view(N * N, 128), None, None, normalize=True)   # [N*N, 128]
+                    out = bias[:, b].view(1, L * H, N * N) if B == 1 else torch.empty(1, L * H, N * N, dtype=torch.bfloat16,
+                                                                                     device=z.device)
+                    F.bmm_nt_into(w_all.view(1, L * H, 128), zhat.view(1, N * N, 128), out)
+                    if B != 1:
+                        bias[:, b] = out.view(L, H, N, N)
+            else:
+                per_layer = []
+                for a in self.attentions:
+                    pk = a.packed()
+                    per_layer.append(torch.stack([F.pair_bias_slab(z[b], pk.ln_z_w, pk.ln_z_b, pk.w_z, pk.H) for b in range(B)]))
+                bias = per_layer  # a list: head counts or pitches may differ between layers
+        self._bias = bias
+        self._key = self._z_key(z)
+        return bias
+
+    def lookup(self, index: int, z: Tensor):
+        """The bias of module ``index`` if ``z`` is the tensor ``prepare`` saw, else ``None``."""
+        if self._bias is None or self._key != self._z_key(z):
+            return None
+        return self._bias[index]

@@ -809,6 +809,7 @@ int b200_attention_core_fwd(const b200_attention_core_args* a, b200_stream_t str
   p.mask_key_stride = a->mask_key_stride;
   p.bias_div = a->bias_div;
   p.gate = static_cast<const __nv_bfloat16*>(a->gate);
+  p.gate_activated = 0;
   p.gate_b_stride = a->gate_batch_stride;
   p.gate_pitch = a->gate_pitch;
   p.gate_col0 = a->gate_col0;
@@ -926,6 +927,7 @@ static int apb_run(const void* s, const void* z, const void* ext_bias, int64_t e
     p.mask_key_stride = 1;
     p.bias_div = M;
     p.gate = qkg;
+    p.gate_activated = 0;
     p.gate_b_stride = int64_t(N) * pl.W1;
     p.gate_pitch = pl.W1;
     p.gate_col0 = 2 * HD;
@@ -1090,6 +1092,7 @@ static int triatt_slab(const void* z, const uint8_t* mask, const void* ext_bias,
     p.mask_key_stride = ending ? n_cols : 1;
     p.bias_div = lines;
     p.gate = qkg;
+    p.gate_activated = 1;  // the projection kernel stores sigmoid(g)
     p.gate_b_stride = int64_t(pos) * 384;
     p.gate_pitch = 384;
     p.gate_col0 = 256;

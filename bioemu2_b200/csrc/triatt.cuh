@@ -1,4 +1,4 @@
-// Triangle attention, projection stage: h = LN(x);  q | k | g = h Wq^T, h Wk^T, h Wg^T + b_g  (pair-major,
+// Triangle attention, projection stage: h = LN(x);  q | k | g = h Wq^T, h Wk^T, sigmoid(h Wg^T + b_g)  (pair-major,
 // bf16, row pitch 384) and V^T = Wv h^T (channel-major per line, bf16, pitch Nk), the layouts the flash
 // core reads.  x is the pair tensor for the starting node and its transpose for the ending node: a tile
 // is 128 consecutive `pos` on one `line`, pair (line, pos) = z[line][pos] or z[pos][line].
@@ -175,7 +175,7 @@ triatt_proj_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constan
           for (int e = 0; e < 8; ++e) y[e] = __uint_as_float(v[g * 8 + e]);
           if (c >= 8 && c < 12) {
 #pragma unroll
-            for (int e = 0; e < 8; ++e) y[e] += gb_s[(c - 8) * 32 + g * 8 + e];
+            for (int e = 0; e < 8; ++e) y[e] = sigmoid_fast(y[e] + gb_s[(c - 8) * 32 + g * 8 + e]);  // the gate leaves activated
           }
           *reinterpret_cast<uint4*>(stage + sw128_offset(r, (c & 1) * 4 + g)) = make_uint4(
               pack_bf16x2(y[0], y[1]), pack_bf16x2(y[2], y[3]), pack_bf16x2(y[4], y[5]), pack_bf16x2(y[6], y[7]));

@@ -67,13 +67,29 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
   return ok != 0;
 }
 
+// The same with a suspend-time hint: the thread sleeps in hardware until the phase completes or about `ns`
+// nanoseconds have passed, instead of returning at once.  A waiting warp then costs a handful of instructions per
+// microsecond instead of a tight polling loop that competes with the working warps for issue slots and for the
+// shared-memory instruction queue.
+__device__ __forceinline__ bool mbar_try_wait_sleep(uint64_t* bar, uint32_t parity, uint32_t ns) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred P;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 P, [%1], %2, %3;\n\t"
+      "selp.u32 %0, 1, 0, P;\n\t}"
+      : "=r"(ok)
+      : "r"(smem_u32(bar)), "r"(parity), "r"(ns)
+      : "memory");
+  return ok != 0;
+}
+
 // Bounded wait: gives up after ~2^31 clock ticks (about a second) or as soon
 // as another wait anywhere in the grid has given up.  `site` names the wait.
 __device__ __noinline__ void mbar_wait_slow(uint64_t* bar, uint32_t parity, int site) {
   const long long t0 = clock64();
   uint32_t spins = 0;
-  while (!mbar_try_wait(bar, parity)) {
-    if ((++spins & 0xff) == 0) {
+  while (!mbar_try_wait_sleep(bar, parity, 2000)) {
+    if ((++spins & 0xf) == 0) {
       if (*reinterpret_cast<volatile int*>(&g_dev_status) != 0) return;
       if (clock64() - t0 > (1ll << 31)) {
         const int code = kDevWaitTimeout | (site << 8);
@@ -166,6 +182,10 @@ __device__ __forceinline__ void tma_store_wait_read1() {  // at most the newest 
 // Barrier among a subset of the CTA's warps (ids 1..15; 0 is __syncthreads).
 __device__ __forceinline__ void named_bar_sync(int id, int nthreads) {
   asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(nthreads) : "memory");
+}
+// Non-blocking arrival at a named barrier that other warps wait on with named_bar_sync.
+__device__ __forceinline__ void named_bar_arrive(int id, int nthreads) {
+  asm volatile("bar.arrive %0, %1;" ::"r"(id), "r"(nthreads) : "memory");
 }
 __device__ __forceinline__ void tma_store_wait0() { asm volatile("cp.async.bulk.wait_group 0;" ::: "memory"); }
 
@@ -268,6 +288,15 @@ __device__ __forceinline__ void tmem_st_32x16_f(uint32_t taddr, const float* v) 
       ::"r"(taddr), "f"(v[0]), "f"(v[1]), "f"(v[2]), "f"(v[3]), "f"(v[4]), "f"(v[5]), "f"(v[6]), "f"(v[7]),
       "f"(v[8]), "f"(v[9]), "f"(v[10]), "f"(v[11]), "f"(v[12]), "f"(v[13]), "f"(v[14]), "f"(v[15])
       : "memory");
+}
+// One fp32 column of 32 lanes (a per-row scalar kept in tensor memory).
+__device__ __forceinline__ float tmem_ld_32x1_f(uint32_t taddr) {
+  float v;
+  asm volatile("tcgen05.ld.sync.aligned.32x32b.x1.b32 {%0}, [%1];" : "=f"(v) : "r"(taddr) : "memory");
+  return v;
+}
+__device__ __forceinline__ void tmem_st_32x1_f(uint32_t taddr, float v) {
+  asm volatile("tcgen05.st.sync.aligned.32x32b.x1.b32 [%0], {%1};" ::"r"(taddr), "f"(v) : "memory");
 }
 __device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
 
@@ -417,11 +446,20 @@ __device__ __forceinline__ float max3(float a, float b, float c) {
   asm("max.f32 %0, %1, %2, %3;" : "=f"(d) : "f"(a), "f"(b), "f"(c));
   return d;
 }
+// 2^lo, 2^hi of two fp32 exponents as packed bf16: one conversion and ONE exponential instruction for the pair
+// (the bf16x2 form of ex2 runs at the same instruction rate as the fp32 one, so it does twice the work).
+__device__ __forceinline__ uint32_t exp2_bf16x2(float lo, float hi) {
+  uint32_t d;
+  asm("{ .reg .b32 t; cvt.rn.bf16x2.f32 t, %2, %1; ex2.approx.ftz.bf16x2 %0, t; }" : "=r"(d) : "f"(lo), "f"(hi));
+  return d;
+}
 __device__ __forceinline__ uint32_t pack_bf16x2(float lo, float hi) {
   __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
   return *reinterpret_cast<uint32_t*>(&v);
 }
 __device__ __forceinline__ float bf16lo(uint32_t u) { return __uint_as_float(u << 16); }
 __device__ __forceinline__ float bf16hi(uint32_t u) { return __uint_as_float(u & 0xffff0000u); }
+
+
 
 }  // namespace b200

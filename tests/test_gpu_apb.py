@@ -102,3 +102,36 @@ def test_attention_core_entry_point(Bt, N, H, dh):
     logits = torch.where(mask[:, None, None, :], logits, torch.full_like(logits, -1e6))
     ref = torch.einsum("bhij,bjhd->bihd", logits.softmax(-1), v.double()) * torch.sigmoid(gate.double())
     assert_close(f"attention_core_B{Bt}_N{N}_H{H}_dh{dh}", out, ref)
+
+
+@pytest.mark.parametrize("B,N", [(1, 136), (2, 72), (1, 77)])
+def test_pair_bias_cache_one_pass_matches_per_layer_projection(B, N):
+    """Three token-block attentions (c_token 768, 16 heads) sharing one static pair tensor: the biases computed in one
+    pass over z give the same attention output as every layer projecting its own, and both match the oracle.  N = 77
+    is not a multiple of 8 and takes the per-layer fallback inside ``prepare``."""
+    import bioemu2_b200 as b
+
+    g = torch.Generator().manual_seed(700 + N)
+    L, c_s, heads, M = 3, 768, 16, 2
+    ws = [H.apb_weights(g, c_s, 128, heads, initial_norm=False) for _ in range(L)]
+    mods = [_module(w, c_s, heads, initial_norm=False) for w in ws]
+    s = torch.randn(B * M, N, c_s, generator=g)
+    z = torch.randn(B, N, N, 128, generator=g)
+    mask = torch.ones(B, N, dtype=torch.bool)
+    mask[0, N - 5:] = False
+    sd, zd, md = s.cuda(), z.cuda(), mask.cuda()
+    with torch.no_grad():
+        plain = [m(sd, zd, md, multiplicity=M) for m in mods]
+        cache = b.PairBiasCache(mods)
+        bias = cache.prepare(zd)
+        assert all(cache.lookup(i, zd) is not None for i in range(L))
+        assert cache.lookup(0, zd.clone()) is None, "another tensor object must not hit the cache"
+        cached = [m(sd, zd, md, multiplicity=M) for m in mods]
+        zd.add_(1.0)  # an in-place change bumps the version counter: the cache no longer applies
+        assert cache.lookup(0, zd) is None
+    if N % 8 == 0:
+        assert tuple(bias.shape) == (L, B, heads, N, N)
+    for i in range(L):
+        ref = O.attention_pair_bias(s.double(), z.double(), mask, {k: v.double() for k, v in ws[i].items()}, heads, M)
+        assert_close(f"apb_cached_bias_layer{i}_B{B}_N{N}", cached[i], ref)
+        assert_close(f"apb_plain_bias_layer{i}_B{B}_N{N}", plain[i], ref)

@@ -51,4 +51,7 @@ def test_pairmixer_module_4_blocks_vs_oracle():
     mod.cuda()
     with torch.no_grad():
         _, out = mod(torch.zeros(1, N, 384, device="cuda"), z.cuda(), pm.cuda())
-    assert_close("pairmixer_module_4", out[0][pm[0].cuda()], ref[0][pm[0]])
+    # Four blocks = twelve residual updates on top of each other: the per-element bar is the single-op one with its
+    # absolute part doubled (errors of independent updates add in quadrature, sqrt(12) ~ 3.5 would be the loose
+    # choice); the normalised maximum keeps the single-op 2e-2.
+    assert_close("pairmixer_module_4", out[0][pm[0].cuda()], ref[0][pm[0]], atol=4e-2)
