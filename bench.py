@@ -69,6 +69,10 @@ def parse_args():
                     help="grid for the context-parallel run (default: 1x2, 2x2, 2x4 for 2, 4, 8 ranks)")
     ap.add_argument("--replicas", action="store_true",
                     help="with --gpus N > 1: N independent replicas (weak scaling) instead of context parallelism")
+    ap.add_argument("--config4", action="store_true",
+                    help="the largest configuration, under torchrun on 4 or 8 ranks: context-parallel 48-block trunk at "
+                         "N = 3072 (three chains of 1024 tokens, ragged padding) followed by 24 diffusion token blocks "
+                         "(16 heads, width 768, pair bias from the trunk's pair tensor); --tokens / --blocks shrink it")
     ap.add_argument("--probe", default=None, choices=PROBES,
                     help="run one kernel family alone (--steps launches after --warmup) and print its time")
     return ap.parse_args()
@@ -143,6 +147,10 @@ def config_dict(args, impl_note: str, parallelism: str) -> dict:
     what = ("triangle multiplication out/in, triangle attention start/end (4x32), pair transition, single-track "
             "pair-bias attention (16x24), single transition" if args.block == "pairformer"
             else "triangle multiplication out/in + pair transition (the reference trunk's own block)")
+    if "context parallel" in parallelism:
+        launch = "eager launches (NCCL collectives between the kernels)"
+    else:
+        launch = "eager" if args.no_graph else "CUDA graph replay of the step (value); eager launches (e2e)"
     return {
         "workload": f"Pairformer trunk forward, {args.blocks} blocks ({what}), N={args.tokens}, c_z=128, c_s=384, "
                     f"batch 1, last {pad_tokens(args.tokens)} tokens padded, seed 2",
@@ -152,7 +160,7 @@ def config_dict(args, impl_note: str, parallelism: str) -> dict:
         "z_stream": "fp32",
         "arithmetic": "bf16 tensor cores, fp32 accumulate",
         "cache": "inputs larger than L2: z is 134 MB fp32 at N=512 and every kernel streams >=200 MB of scratch",
-        "launch": "eager" if args.no_graph else "CUDA graph replay of the step (value); eager launches (e2e)",
+        "launch": launch,
         "parallelism": parallelism,
         "note": impl_note,
     }
@@ -863,11 +871,146 @@ def run_cp(args) -> None:
     dist.destroy_process_group()
 
 
+def run_config4(args) -> None:
+    """Context-parallel trunk at N = 3072 plus the 24 token blocks of the diffusion module on the same grid.
+
+    Inputs: three chains of N/3 tokens, the last 5-15 % of each chain masked (fractions drawn from the seed-4
+    generator), z and s ~ N(0,1); every rank draws its own block of z on the device (seed 400 + rank) -- at this size
+    nothing is compared with the CPU oracle, the sharded arithmetic is the one `cp_parity_rel` checks at N = 256.
+    Weights: seed 4, identical on all ranks."""
+    import math
+
+    import torch.distributed as dist
+
+    import bioemu2_b200 as b
+    from bioemu2_b200.context_parallel import (CPConditionedTransformerLayer, CPGrid, CPPairformerModule,
+                                               kernel_shard_multiple)
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    rows, cols = (int(v) for v in args.cp.lower().split("x")) if args.cp else GRIDS.get(world, (1, world))
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+    os.environ.setdefault("MASTER_PORT", "29512")
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=dev)
+    N = args.tokens if args.tokens != 512 else 3072
+    n_blocks, n_token_layers, width = args.blocks, 24, 768
+    mult = math.lcm(kernel_shard_multiple(rows, cols), 3)
+    if N % mult:
+        raise SystemExit(f"--tokens must be a multiple of {mult} for a {rows}x{cols} grid and three chains")
+    grid = CPGrid(rows, cols)
+    g4 = torch.Generator().manual_seed(4)
+    fracs = (0.05 + 0.10 * torch.rand(3, generator=g4)).tolist()
+    chain = N // 3
+    tok = torch.ones(1, N, dtype=torch.bool)
+    for i, f in enumerate(fracs):
+        tok[0, (i + 1) * chain - int(round(f * chain)):(i + 1) * chain] = False
+    import helpers as H
+
+    w = {}
+    for i in range(n_blocks):
+        w.update(H.prefixed(f"layers.{i}", block_weights(g4, "pairformer")))
+    serial = b.PairformerModule(384, 128, n_blocks).eval()
+    serial.load_state_dict(w, strict=True)
+    serial.to(dev)
+    del w
+    trunk = CPPairformerModule(serial, grid)
+    (r0, r1), (c0, c1) = grid.coords.my_rows(N), grid.coords.my_cols(N)
+    gd = torch.Generator(device=dev).manual_seed(400 + rank)
+    z0 = torch.randn(1, r1 - r0, c1 - c0, 128, device=dev, generator=gd)
+    gs = torch.Generator(device=dev).manual_seed(40 + grid.coords.r)   # s rows are replicated over grid columns
+    s0 = torch.randn(1, r1 - r0, 384, device=dev, generator=gs)
+    tr, tc = tok[:, r0:r1].to(dev), tok[:, c0:c1].to(dev)
+    z, s = torch.empty_like(z0), torch.empty_like(s0)
+
+    def barrier():
+        dist.barrier()
+        torch.cuda.synchronize()
+
+    def trunk_step():
+        z.copy_(z0)
+        s.copy_(s0)
+        trunk.forward_(s, z, tr, tc)
+
+    steps = max(1, min(args.steps, 3))
+    with torch.no_grad():
+        trunk_step()
+        barrier()
+        trunk_ms = event_time_ms(trunk_step, steps)
+        barrier()
+        # ---- 24 token blocks on the trunk's pair tensor (static for the whole denoising loop)
+        torch.manual_seed(4)
+        layers = []
+        for l in range(n_token_layers):
+            m = b.ConditionedTransformerLayer(dim=width, dim_pairwise=128, dim_cond=width, heads=16,
+                                              transition_hidden=4 * width, lns_scale=1.0 / math.sqrt(l + 1)).eval().to(dev)
+            layers.append(CPConditionedTransformerLayer(m, grid))
+        ga = torch.Generator(device=dev).manual_seed(44 + grid.coords.r)
+        a0 = torch.randn(1, r1 - r0, width, device=dev, generator=ga)
+        c0_ = torch.randn(1, r1 - r0, width, device=dev, generator=ga)
+
+        def denoise_step():
+            a = a0
+            for layer in layers:
+                a = layer(a, z, c0_, tr, 1)
+            return a
+
+        denoise_step()
+        barrier()
+        per_layer_ms = event_time_ms(denoise_step, steps)
+        barrier()
+        t0 = torch.cuda.Event(enable_timing=True)
+        t1 = torch.cuda.Event(enable_timing=True)
+        t0.record()
+        for layer in layers:
+            layer.attention.prepare_static(z)
+        t1.record()
+        torch.cuda.synchronize()
+        prepare_ms = t0.elapsed_time(t1)
+        denoise_step()
+        barrier()
+        hoisted_ms = event_time_ms(denoise_step, steps)
+        barrier()
+        status = b._lib.device_status()
+    tt = torch.tensor([trunk_ms, per_layer_ms, hoisted_ms, prepare_ms, float(status)], device=dev, dtype=torch.float64)
+    dist.all_reduce(tt, op=dist.ReduceOp.MAX)
+    trunk_ms, per_layer_ms, hoisted_ms, prepare_ms, status = (float(v) for v in tt)
+    if rank == 0:
+        fl = block_flops(N, "pairformer")
+        line = {
+            "metric": METRIC, "value": N * N / (trunk_ms * 1e-3), "unit": UNIT, "n_gpus": world, "steps": steps,
+            "warmup": 1, "ms_per_step": trunk_ms, "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
+            "dtype": "bf16", "data": "synthetic",
+            "config": {"workload": f"context-parallel Pairformer trunk, {n_blocks} blocks, N={N} (three chains of {chain}, "
+                                   f"last {', '.join(f'{100 * f:.1f}%' for f in fracs)} of the chains padded), seed 4, pair tensor tiled "
+                                   f"{rows}x{cols}; then {n_token_layers} diffusion token blocks (16 heads, width {width}, pair bias "
+                                   "from the trunk's pair tensor)",
+                       "tokens": N, "blocks": n_blocks, "grid": f"{rows}x{cols}", "z_stream": "fp32",
+                       "arithmetic": "bf16 tensor cores, fp32 accumulate", "launch": "eager"},
+            "ops": {"trunk_tflops_aggregate": n_blocks * fl["block"] / (trunk_ms * 1e-3) / 1e12},
+            "diffusion_token_blocks": {
+                "layers": n_token_layers,
+                "ms_per_denoise_step_bias_per_layer": per_layer_ms,
+                "ms_per_denoise_step_bias_hoisted": hoisted_ms,
+                "ms_one_time_bias_for_all_layers": prepare_ms,
+                "note": "per_layer: every layer projects and all-gathers its pair bias on every step, as the reference does; "
+                        "hoisted: the static pair tensor is projected once per context (prepare_static)",
+            },
+            "device_status": int(status),
+        }
+        print(json.dumps(line), flush=True)
+    dist.destroy_process_group()
+
+
 def main():
     args = parse_args()
     world = int(os.environ.get("WORLD_SIZE", "1"))
     if args.impl == "reference":
         run_reference(args)
+    elif args.config4:
+        run_config4(args)
     elif args.probe:
         run_probe(args)
     elif world > 1 and not args.replicas:

@@ -57,6 +57,15 @@ class CudaAttentionLocal:
 
         return F.outer_product_mean_cols(m_rows, mask_rows, opm_packed, j0, nj, inv_count, add_bias)
 
+    def to_exchange(self, x: Tensor) -> Tensor:
+        """The pair block as it travels to the ranks that attend over its lines: bf16, half the bytes on NVLink.  The
+        slab kernel normalises what it receives (LayerNorm in fp32) and rounds to bf16 for the tensor cores anyway."""
+        from .. import functional as F
+
+        if x.dtype != torch.float32:
+            return x
+        return F.rows_to_bf16(x.reshape(-1, x.shape[-1]), normalize=False).view(x.shape)
+
     bias_dtype = torch.bfloat16
 
 
@@ -74,20 +83,36 @@ def _assemble_bias(blocks: list[Tensor], grid: CPGrid, n: int, transposed: bool)
     return full
 
 
-def cp_attention_pair_bias(s_loc: Tensor, z_loc: Tensor, mask_loc: Tensor, apb_packed, grid: CPGrid,
-                           multiplicity: int = 1, local=None) -> Tensor:
-    """``s_loc[B*M, n_r, c_s]`` (rows of this rank, replicated over grid columns), ``z_loc[B, n_r, n_c, 128]``,
-    ``mask_loc[B, n_r]`` -> attention update for the same rows ``[B*M, n_r, c_s]``."""
+def cp_pair_bias_full(z_loc: Tensor, apb_packed, grid: CPGrid, local=None) -> Tensor:
+    """The whole ``[B, H, N, pitch]`` pair bias of one attention module, assembled from every rank's projection of its
+    own block of ``z_loc[B, n_r, n_c, 128]`` (one pass over local z, one all-gather over the grid)."""
     local = local or CudaAttentionLocal()
     B, n_r = z_loc.shape[0], z_loc.shape[1]
     n = n_r * grid.rows
     zb_loc = torch.stack([local.pair_bias(z_loc[b], apb_packed) for b in range(B)])  # [B, H, n_r, pitch]
-    bias_full = _assemble_bias(grid.all_gather(zb_loc, grid.group), grid, n, False)
+    return _assemble_bias(grid.all_gather(zb_loc, grid.group), grid, n, False)
+
+
+def cp_attention_pair_bias(s_loc: Tensor, z_loc: Tensor, mask_loc: Tensor, apb_packed, grid: CPGrid,
+                           multiplicity: int = 1, local=None, bias_full: Tensor | None = None) -> Tensor:
+    """``s_loc[B*M, n_r, c_s]`` (rows of this rank, replicated over grid columns), ``z_loc[B, n_r, n_c, 128]``,
+    ``mask_loc[B, n_r]`` -> attention update for the same rows ``[B*M, n_r, c_s]``.  ``bias_full`` (from
+    ``cp_pair_bias_full``) skips the projection and its all-gather: the pair tensor of the diffusion token blocks is
+    static, so a caller computes it once per context instead of once per layer and step."""
+    local = local or CudaAttentionLocal()
+    n = z_loc.shape[1] * grid.rows
+    if bias_full is None:
+        bias_full = cp_pair_bias_full(z_loc, apb_packed, grid, local)
     s_full = torch.cat(grid.all_gather(s_loc, grid.col_group), dim=1)
     mask_full = torch.cat(grid.all_gather(mask_loc, grid.col_group), dim=1)
     out_full = local.attention(s_full, bias_full, mask_full, apb_packed, multiplicity)
     r0, r1 = grid.coords.my_rows(n)
     return out_full[:, r0:r1].contiguous()
+
+
+def _to_exchange(local, x: Tensor) -> Tensor:
+    fn = getattr(local, "to_exchange", None)
+    return fn(x) if fn is not None else x
 
 
 def cp_triangle_attention_(z_loc: Tensor, mask_loc: Tensor, tri_packed, grid: CPGrid, ending: bool, local=None) -> Tensor:
@@ -112,11 +137,11 @@ def cp_triangle_attention_(z_loc: Tensor, mask_loc: Tensor, tri_packed, grid: CP
                 got = grid.all_to_all(x.reshape(gs, share, *x.shape[1:]).contiguous(), g)   # [src c, share, n_c, ...]
                 return got.transpose(0, 1).reshape(share, gs * n_c, *x.shape[2:]).contiguous()
 
-            upd = local.tri_slab(lines_in(z_loc), lines_in(mask_loc), bias_full, tri_packed, False)  # [share, N, 128]
+            upd = local.tri_slab(lines_in(_to_exchange(local, z_loc)), lines_in(mask_loc), bias_full, tri_packed, False)  # [share, N, 128]
             back = grid.all_to_all(upd.reshape(share, gs, n_c, upd.shape[-1]).transpose(0, 1).contiguous(), g)
             z_loc += back.reshape(n_r, n_c, upd.shape[-1])
             return z_loc
-        slab = torch.cat(grid.all_gather(z_loc, g), dim=1)          # [n_r, N, 128]
+        slab = torch.cat(grid.all_gather(_to_exchange(local, z_loc), g), dim=1)          # [n_r, N, 128]
         mslab = torch.cat(grid.all_gather(mask_loc, g), dim=1)
         upd = local.tri_slab(slab, mslab, bias_full, tri_packed, False)
         c0, c1 = grid.coords.my_cols(n)
@@ -130,11 +155,11 @@ def cp_triangle_attention_(z_loc: Tensor, mask_loc: Tensor, tri_packed, grid: CP
                 send = x.reshape(n_r, gs, share, *x.shape[2:]).transpose(0, 1).contiguous()   # [dst r, n_r, share, ...]
                 return grid.all_to_all(send, g).reshape(gs * n_r, share, *x.shape[2:])
 
-            upd = local.tri_slab(lines_in(z_loc), lines_in(mask_loc), bias_full, tri_packed, True)   # [N, share, 128]
+            upd = local.tri_slab(lines_in(_to_exchange(local, z_loc)), lines_in(mask_loc), bias_full, tri_packed, True)   # [N, share, 128]
             back = grid.all_to_all(upd.reshape(gs, n_r, share, upd.shape[-1]).contiguous(), g)      # [src r, n_r, share, 128]
             z_loc += back.transpose(0, 1).reshape(n_r, n_c, upd.shape[-1])
             return z_loc
-        slab = torch.cat(grid.all_gather(z_loc, g), dim=0)          # [N, n_c, 128]
+        slab = torch.cat(grid.all_gather(_to_exchange(local, z_loc), g), dim=0)          # [N, n_c, 128]
         mslab = torch.cat(grid.all_gather(mask_loc, g), dim=0)
         upd = local.tri_slab(slab, mslab, bias_full, tri_packed, True)
         r0, r1 = grid.coords.my_rows(n)

@@ -119,17 +119,40 @@ class CPPairMixerModule(nn.Module):
 class CPAttentionPairBias(nn.Module):
     """``forward(s, z, mask, multiplicity)`` on sharded inputs: ``s`` rows of this rank (replicated over grid columns),
     ``z`` this rank's pair block, ``mask`` this rank's token rows; returns the update for the same rows
-    (reference wrapper: src/bioemu2/context_parallel/ops/attention.py:74-105)."""
+    (reference wrapper: src/bioemu2/context_parallel/ops/attention.py:74-105).
+
+    ``prepare_static(z)`` computes and keeps the assembled pair bias for a pair block that will be passed again and
+    again (the diffusion module's static context): later calls with the SAME tensor object (same storage and version
+    counter) skip the projection of ``z`` and the all-gather of the bias; any other ``z`` takes the normal path."""
 
     def __init__(self, attention: AttentionPairBias, grid: CPGrid, local=None) -> None:
         super().__init__()
         self.attention = attention
         self.grid = grid
         self.local = local
+        self._static_key = None
+        self._static_bias = None
+
+    @staticmethod
+    def _key(z):
+        return (z.data_ptr(), z._version, tuple(z.shape), z.dtype)
+
+    def prepare_static(self, z) -> None:
+        from .attention import cp_pair_bias_full
+
+        zl = _local(z)
+        with torch.no_grad():
+            self._static_bias = cp_pair_bias_full(zl, self.attention.packed(), self.grid, self.local)
+        self._static_key = self._key(zl)
+
+    def release_static(self) -> None:
+        self._static_key, self._static_bias = None, None
 
     def forward(self, s, z, mask, multiplicity: int = 1):
-        out = cp_attention_pair_bias(_local(s), _local(z), _local(mask), self.attention.packed(), self.grid, multiplicity,
-                                     local=self.local)
+        zl = _local(z)
+        bias = self._static_bias if (self._static_key is not None and self._static_key == self._key(zl)) else None
+        out = cp_attention_pair_bias(_local(s), zl, _local(mask), self.attention.packed(), self.grid, multiplicity,
+                                     local=self.local, bias_full=bias)
         if hasattr(s, "to_local"):
             from torch.distributed.tensor import DTensor
 

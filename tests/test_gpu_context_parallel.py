@@ -50,8 +50,7 @@ def _run_rank(rank, world, rows, cols, port, n_tokens, blocks, q):
         torch.cuda.synchronize()
         assert ret.data_ptr() == z_loc.data_ptr()
         ref_loc = grid.shard_pair(ref.cpu()).to(dev)
-        valid = m_loc[0]
-        num = float((z_loc[0][valid] - ref_loc[0][valid]).abs().max()) if valid.any() else 0.0
+        num = float((z_loc[0] - ref_loc[0]).abs().max())  # every cell: the update is defined at masked pairs too
         den = float(ref.abs().max())
         q.put((rank, num / den, b._lib.device_status()))
     finally:
@@ -97,11 +96,16 @@ def _run_block_rank(rank, world, rows, cols, port, n, q):
     dist.init_process_group("nccl", rank=rank, world_size=world, device_id=dev)
     try:
         import bioemu2_b200 as b
-        from bioemu2_b200.context_parallel import CPGrid, CPOuterProductMean, CPPairformerBlock, shard_range
+        from bioemu2_b200.context_parallel import (CPConditionedTransformerLayer, CPGrid, CPOuterProductMean,
+                                                   CPPairformerBlock, shard_range)
 
         torch.manual_seed(21)  # same seed on every rank: replicated weights
         blk = b.PairformerBlock().eval().to(dev)
         opm = b.OuterProductMean(64, 32, 128).eval().to(dev)
+        tokblk = b.ConditionedTransformerLayer(dim=768, dim_pairwise=128, dim_cond=768, heads=16, transition_hidden=3072,
+                                               lns_scale=0.5).eval().to(dev)
+        with torch.no_grad():
+            tokblk.attention.pair_bias_attn.proj_q_bias.normal_(0.0, 0.02)
         g = torch.Generator().manual_seed(22)
         z = torch.randn(1, n, n, 128, generator=g)
         s = torch.randn(1, n, 384, generator=g)
@@ -112,9 +116,12 @@ def _run_block_rank(rank, world, rows, cols, port, n, q):
         mm = torch.ones(1, S, n, dtype=torch.bool)
         mm[0, 3] = False
         mm[0, :, n - 6:] = False
+        a = torch.randn(2, n, 768, generator=g)       # token stream with multiplicity 2
+        c = torch.randn(2, n, 768, generator=g)
         with torch.no_grad():
             s_ref, z_ref = blk(s.to(dev), z.to(dev), tok.to(dev))
             o_ref = opm(m.to(dev), mm.to(dev))
+            a_ref = tokblk(a.to(dev), z.to(dev), c.to(dev), tok.to(dev), multiplicity=2)
         grid = CPGrid(rows, cols)
         cpb = CPPairformerBlock(blk, grid)
         z_loc, s_loc = grid.shard_pair(z).to(dev), grid.shard_single(s).to(dev)
@@ -124,13 +131,21 @@ def _run_block_rank(rank, world, rows, cols, port, n, q):
             s0, s1 = shard_range(S, rows, grid.coords.r)
             o_out = CPOuterProductMean(opm, grid)(m[:, s0:s1, c0:c1].contiguous().to(dev),
                                                    mm[:, s0:s1, c0:c1].contiguous().to(dev), mm.any(-1).sum(1).to(dev))
+            # the diffusion module's token block on the ORIGINAL pair block, with and without the static bias
+            cpt = CPConditionedTransformerLayer(tokblk, grid)
+            z_blk = grid.shard_pair(z).to(dev)
+            a_loc, c_loc, t_loc = a[:, r0:r1].contiguous().to(dev), c[:, r0:r1].contiguous().to(dev), tok[:, r0:r1].to(dev)
+            a_out = cpt(a_loc, z_blk, c_loc, t_loc, 2)
+            cpt.attention.prepare_static(z_blk)
+            a_out_static = cpt(a_loc, z_blk, c_loc, t_loc, 2)
         torch.cuda.synchronize()
-        pm = (tok[:, r0:r1, None] & tok[:, None, c0:c1])[0].to(dev)
-        rel = lambda a, e, sel: float((a - e)[sel].abs().max() / e.abs().max()) if sel.any() else 0.0  # noqa: E731
+        rel = lambda x, e: float((x - e).abs().max() / e.abs().max())  # noqa: E731  (every cell, masked ones included)
         errs = {
-            "z": rel(z_out[0], z_ref[0, r0:r1, c0:c1], pm),
-            "s": rel(s_out[0], s_ref[0, r0:r1], tok[0, r0:r1].to(dev)),
-            "opm": rel(o_out[0], o_ref[0, r0:r1, c0:c1], pm),
+            "z": rel(z_out[0], z_ref[0, r0:r1, c0:c1]),
+            "s": rel(s_out[0], s_ref[0, r0:r1]),
+            "opm": rel(o_out[0], o_ref[0, r0:r1, c0:c1]),
+            "token_block": rel(a_out, a_ref[:, r0:r1]),
+            "token_block_static_bias": rel(a_out_static, a_ref[:, r0:r1]),
         }
         q.put((rank, errs, b._lib.device_status()))
     finally:
