@@ -9,7 +9,8 @@ from .outer_product_mean import (
     OuterProductMeanVanilla,
 )
 from .pairformer import PairformerBlock, PairformerModule
-from .pairmixer import PairMixerLayer, PairMixerModule
+from .pair_weighted_averaging import PairWeightedAveraging
+from .pairmixer import PairMixerLayer, PairMixerModule, PairMixerMSALayer
 from .swap import swap_into, to_b200
 from .transformer import AttentionLayer, ConditionedTransformerLayer
 from .transition import Transition
@@ -38,6 +39,8 @@ __all__ = [
     "PairformerModule",
     "PairMixerLayer",
     "PairMixerModule",
+    "PairMixerMSALayer",
+    "PairWeightedAveraging",
     "swap_into",
     "to_b200",
     "Transition",

@@ -35,6 +35,7 @@ struct BmmParams {
   // bf16 columns) and the C tensor map, 1 = stored, 2 = added into C (the residual is C itself, which the
   // epilogue then never reads).
   int tma_c;
+  int a_shared;              // 1: every batch item multiplies the same A (the A tensor map has a single batch slice)
 };
 
 template <int BN>
@@ -102,7 +103,7 @@ bmm_nt_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ C
           mbar_wait(&empty[stage], phase ^ 1, 1);
           uint8_t* sa = smem + stage * Cfg::STAGE_BYTES;
           mbar_arrive_expect_tx(&full[stage], Cfg::STAGE_BYTES);
-          tma_load_3d(sa, &tmA, &full[stage], kb * 64, tm * 128, b);
+          tma_load_3d(sa, &tmA, &full[stage], kb * 64, tm * 128, p.a_shared ? 0 : b);
           tma_load_3d(sa + Cfg::A_BYTES, &tmB, &full[stage], kb * 64, tn * BN, b);
           if (++stage == Cfg::STAGES) {
             stage = 0;

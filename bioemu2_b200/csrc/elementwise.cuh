@@ -182,4 +182,78 @@ gated_residual_rows_kernel(void* __restrict__ x, const void* __restrict__ h, con
   }
 }
 
+// Row softmax of pair-bias logits with the reference's masking convention, one warp per row:
+//   w[h][i][j] = softmax_j( mask[i][j] ? logit[h][i][j] : -1e6 )      for j < n; columns n .. pitch-1 are written as 0.
+// The logits arrive in base-2 units (pre-multiplied by log2(e), as the pair-bias projection kernel writes them), bf16;
+// the weights leave as bf16.  The row is read three times (maximum, sum, store): it is a few KB and stays in L1/L2.
+__global__ void __launch_bounds__(256)
+masked_softmax_rows_kernel(const __nv_bfloat16* __restrict__ logits, const uint8_t* __restrict__ mask,
+                           __nv_bfloat16* __restrict__ out, int H, int n, int pitch) {
+  constexpr float kNegMasked = -1.0e6f * 1.4426950408889634f;
+  const int lane = threadIdx.x & 31;
+  const long long rows = (long long)H * n;
+  const long long warp_global = (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  const long long warp_stride = (long long)gridDim.x * (blockDim.x >> 5);
+  const int nvec = pitch >> 3;
+  for (long long r = warp_global; r < rows; r += warp_stride) {
+    const int i = int(r % n);
+    const __nv_bfloat16* src = logits + r * pitch;
+    const uint8_t* mrow = mask + (long long)i * n;
+    auto load_masked = [&](int v, float (&x)[8]) {
+      load8<false>(src, v * 8, x);
+#pragma unroll
+      for (int e = 0; e < 8; ++e) {
+        const int j = v * 8 + e;
+        x[e] = j < n ? (mrow[j] ? x[e] : kNegMasked) : -INFINITY;
+      }
+    };
+    float mx = -INFINITY;
+    for (int v = lane; v < nvec; v += 32) {
+      float x[8];
+      load_masked(v, x);
+#pragma unroll
+      for (int e = 0; e < 8; ++e) mx = fmaxf(mx, x[e]);
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
+    float sum = 0.f;
+    for (int v = lane; v < nvec; v += 32) {
+      float x[8];
+      load_masked(v, x);
+#pragma unroll
+      for (int e = 0; e < 8; ++e) sum += exp2_approx(x[e] - mx);
+    }
+    const float inv = 1.0f / warp_sum(sum);
+    for (int v = lane; v < nvec; v += 32) {
+      float x[8];
+      load_masked(v, x);
+#pragma unroll
+      for (int e = 0; e < 8; ++e) x[e] = exp2_approx(x[e] - mx) * inv;
+      store8<false>(out + r * pitch, v * 8, x);
+    }
+  }
+}
+
+// Gating and re-layout after the pair-weighted average:  og[(s, i)][h*32 + d] = sigmoid(g[(s, i)][h*32 + d]) * o[h][i][s*32 + d]
+// (o is what the per-head product  w_h . v_h^T  leaves: token rows, (MSA row, channel) columns).  One thread per 8 channels.
+__global__ void __launch_bounds__(256)
+pwa_gate_kernel(const __nv_bfloat16* __restrict__ o, const __nv_bfloat16* __restrict__ g, __nv_bfloat16* __restrict__ og,
+                int S, int n, int H) {
+  const long long total = (long long)S * n * H * 4;
+  const long long o_plane = (long long)n * S * 32;
+  for (long long t = (long long)blockIdx.x * blockDim.x + threadIdx.x; t < total; t += (long long)gridDim.x * blockDim.x) {
+    const int d8 = int(t & 3);
+    const int h = int((t >> 2) % H);
+    const long long si = (t >> 2) / H;          // s * n + i
+    const int i = int(si % n);
+    const long long s_ = si / n;
+    float a[8], b[8];
+    load8<false>(o + h * o_plane + ((long long)i * S + s_) * 32, d8 * 8, a);
+    load8<false>(g + si * (H * 32) + h * 32, d8 * 8, b);
+#pragma unroll
+    for (int e = 0; e < 8; ++e) a[e] *= sigmoid_fast(b[e]);
+    store8<false>(og + si * (H * 32) + h * 32, d8 * 8, a);
+  }
+}
+
 }  // namespace b200

@@ -40,8 +40,9 @@ struct BmmLaunch {
 static int launch_bmm(const BmmLaunch& a, cudaStream_t stream) {
   const int BN = (a.N % 256 == 0 || a.N > 1024) ? 256 : 128;
   CUtensorMap tmA, tmB;
+  const bool a_shared = a.batch > 1 && a.sa == 0;  // one A for every batch item
   {
-    const uint64_t dims[3] = {uint64_t(a.K), uint64_t(a.M), uint64_t(a.batch)};
+    const uint64_t dims[3] = {uint64_t(a.K), uint64_t(a.M), uint64_t(a_shared ? 1 : a.batch)};
     const uint64_t str[2] = {uint64_t(a.lda) * 2, uint64_t(a.sa > 0 ? a.sa : a.lda * a.M) * 2};
     const uint32_t box[3] = {64, 128, 1};
     if (int e = make_tmap_bf16(&tmA, a.A, 3, dims, str, box, CU_TENSOR_MAP_SWIZZLE_128B)) return e;
@@ -70,6 +71,7 @@ static int launch_bmm(const BmmLaunch& a, cudaStream_t stream) {
   p.residual = a.residual;
   p.remap_n = a.remap_n;
   p.remap_m = a.remap_m > 0 ? a.remap_m : a.remap_n;
+  p.a_shared = a_shared ? 1 : 0;
   // Bulk output through the C tensor map where the layout allows it: whole 128-byte column groups, the
   // residual (if any) being C itself, and for the transposed pair store lines that are whole row tiles.
   p.tma_c = 0;
@@ -555,7 +557,8 @@ int b200_bmm_nt(const void* A, const void* B, void* C, int batch, int M, int N, 
   B200_CHECK_ARG(N % 8 == 0 && lda % 8 == 0 && ldb % 8 == 0 && ldc % 8 == 0, "N and the row pitches must be multiples of 8");
   B200_CHECK_ARG(a_batch_stride % 8 == 0 && b_batch_stride % 8 == 0 && c_batch_stride % 8 == 0,
                  "batch strides must be multiples of 8 elements");
-  B200_CHECK_ARG(batch == 1 || (a_batch_stride > 0 && b_batch_stride > 0), "batch strides must be positive");
+  B200_CHECK_ARG(batch == 1 || (a_batch_stride >= 0 && b_batch_stride > 0),
+                 "batch strides must be positive (a_batch_stride may be 0: one A shared by every batch item)");
   B200_CHECK_ARG(lda >= K && ldb >= K && ldc >= N, "row pitch smaller than the row");
   B200_CHECK_ARG((out_dtype | 1) == 1, "unknown out_dtype %d", out_dtype);
   B200_CHECK_ARG(aligned(A, 16) && aligned(B, 16) && aligned(C, 32), "A/B must be 16-byte aligned, C 32-byte aligned");
@@ -1262,6 +1265,29 @@ int b200_gated_residual_fwd(void* x, const void* h, const float* cond, int cond_
   else if (xf) gated_residual_rows_kernel<true, false><<<grid, 256, 0, st>>>(x, h, cond, cond_width, gamma_col, rows, cols);
   else if (hf) gated_residual_rows_kernel<false, true><<<grid, 256, 0, st>>>(x, h, cond, cond_width, gamma_col, rows, cols);
   else gated_residual_rows_kernel<false, false><<<grid, 256, 0, st>>>(x, h, cond, cond_width, gamma_col, rows, cols);
+  B200_AFTER_LAUNCH();
+  return B200_OK;
+}
+
+int b200_masked_softmax_rows(const void* logits, const uint8_t* mask, void* out, int H, int n, int pitch,
+                             b200_stream_t stream) {
+  if (int e = b200_check_device()) return e;
+  B200_CHECK_ARG(logits && mask && out, "logits/mask/out is NULL");
+  B200_CHECK_ARG(H > 0 && n > 0 && pitch >= n && pitch % 8 == 0, "need H, n > 0 and a pitch >= n that is a multiple of 8");
+  B200_CHECK_ARG(aligned(logits, 16) && aligned(out, 16), "logits/out must be 16-byte aligned");
+  masked_softmax_rows_kernel<<<grid_for((int64_t)H * n, 8), 256, 0, static_cast<cudaStream_t>(stream)>>>(
+      static_cast<const __nv_bfloat16*>(logits), mask, static_cast<__nv_bfloat16*>(out), H, n, pitch);
+  B200_AFTER_LAUNCH();
+  return B200_OK;
+}
+
+int b200_pwa_gate(const void* o, const void* g, void* og, int S, int n, int H, b200_stream_t stream) {
+  if (int e = b200_check_device()) return e;
+  B200_CHECK_ARG(o && g && og, "o/g/og is NULL");
+  B200_CHECK_ARG(S > 0 && n > 0 && H > 0, "S, n, H must be positive");
+  B200_CHECK_ARG(aligned(o, 16) && aligned(g, 16) && aligned(og, 16), "o/g/og must be 16-byte aligned");
+  pwa_gate_kernel<<<grid_for((int64_t)S * n * H * 4, 256), 256, 0, static_cast<cudaStream_t>(stream)>>>(
+      static_cast<const __nv_bfloat16*>(o), static_cast<const __nv_bfloat16*>(g), static_cast<__nv_bfloat16*>(og), S, n, H);
   B200_AFTER_LAUNCH();
   return B200_OK;
 }

@@ -569,3 +569,66 @@ def outer_product_mean_cols(m: Tensor, mask: Tensor, w: OpmPacked, j0: int, nj: 
                                      inv_count.data_ptr(), 1 if add_bias else 0, zd, _lib.DTYPE_F32, ws.data_ptr(), nbytes,
                                      _stream()))
     return out
+
+
+# ----------------------------------------------------------------------------------- pair-weighted averaging
+class PwaPacked:
+    """Weights of pair-weighted averaging (heads of 32 channels, c_z = 128) in kernel layouts."""
+
+    def __init__(self, norm_m_w, norm_m_b, norm_z_w, norm_z_b, proj_m, proj_g, proj_z, proj_o, num_heads: int):
+        H = num_heads
+        if proj_m.shape[0] != 32 * H or proj_z.shape[1] != 128 or H > 16 or proj_m.shape[1] % 8:
+            raise ValueError("pair-weighted averaging is built for heads of 32 channels, at most 16 heads, c_z = 128")
+        bf = torch.bfloat16
+        self.H, self.c_m = H, proj_m.shape[1]
+        self.w_m = proj_m.detach().to(bf).contiguous()          # [H*32, c_m]: rows h*32 .. h*32+31 are head h
+        self.w_g = proj_g.detach().to(bf).contiguous()
+        self.w_o = proj_o.detach().to(bf).contiguous()          # [c_m, H*32]
+        wz = torch.zeros(16, 128, dtype=torch.float32, device=proj_z.device)
+        wz[:H] = proj_z.detach().float()
+        self.w_z = wz.to(bf).contiguous()
+        self.ln_m = (norm_m_w.detach().float().contiguous(), norm_m_b.detach().float().contiguous())
+        self.ln_z_w = norm_z_w.detach().float().contiguous()
+        self.ln_z_b = norm_z_b.detach().float().contiguous() if norm_z_b is not None else None
+
+
+def pair_weighted_averaging(m: Tensor, z: Tensor, mask: Tensor, w: PwaPacked, add_residual: bool = False) -> Tensor:
+    """``m[B,S,N,c_m]``, ``z[B,N,N,128]``, ``mask[B,N,N]`` -> update ``[B,S,N,c_m]`` (plus ``m`` when ``add_residual``).
+
+    Per batch item: ``norm_m`` and the gate / value projections of the MSA rows, the per-head weights
+    ``softmax_j(proj_z(norm_z(z))[i,j,h])`` with masked pairs at -1e6, the per-head product ``w_h . v_h^T`` on the tensor
+    cores (``v_h^T`` is written transposed by its projection GEMM, so both operands are K-major), gating, ``proj_o``.
+    """
+    _require_cuda(m, z, mask)
+    if m.ndim != 4 or z.ndim != 4 or tuple(z.shape[1:]) != (m.shape[2], m.shape[2], 128) or z.shape[0] != m.shape[0]:
+        raise ValueError(f"expected m[B,S,N,c_m] and z[B,N,N,128], got {tuple(m.shape)}, {tuple(z.shape)}")
+    if tuple(mask.shape) != tuple(z.shape[:3]):
+        raise ValueError(f"mask shape {tuple(mask.shape)} does not match z {tuple(z.shape)}")
+    B, S, N, c_m = m.shape
+    if c_m != w.c_m:
+        raise ValueError(f"m has {c_m} channels, the module was built for {w.c_m}")
+    H, Nk = w.H, pad8(N)
+    m = m.contiguous()
+    m8 = mask_u8(mask)
+    out = torch.empty_like(m)
+    bf = torch.bfloat16
+    for b in range(B):
+        mn = rows_to_bf16(m[b].view(S * N, c_m), w.ln_m[0], w.ln_m[1], normalize=True)            # [S*N, c_m]
+        g = linear_bf16(mn, w.w_g)                                                                 # [S*N, H*32]
+        mn_p = mn.view(S, N, c_m)
+        if N != Nk:   # the token axis is the GEMM's column count, which the kernel wants in multiples of 8
+            mn_p = torch.zeros(S, Nk, c_m, dtype=bf, device=m.device)
+            mn_p[:, :N] = mn.view(S, N, c_m)
+        vT = torch.empty(H, S * 32, Nk, dtype=bf, device=m.device)                                 # [h][(s, d)][j]
+        for h in range(H):   # v_h^T[s] = W_m[h] . mn[s]^T : one A for all S batch items
+            bmm_nt_into(w.w_m[h * 32:(h + 1) * 32].unsqueeze(0).expand(S, 32, c_m), mn_p, vT[h].view(S, 32, Nk))
+        logits = pair_bias_slab(z[b], w.ln_z_w, w.ln_z_b, w.w_z, H)                                # [H, N, Nk], base 2
+        wts = torch.empty_like(logits)
+        _lib.check(lib.b200_masked_softmax_rows(logits.data_ptr(), m8[b].data_ptr(), wts.data_ptr(), H, N, Nk, _stream()))
+        o = torch.empty(H, N, S * 32, dtype=bf, device=m.device)
+        bmm_nt_into(wts, vT, o)                                                                    # o[h][i][(s, d)]
+        og = torch.empty(S * N, H * 32, dtype=bf, device=m.device)
+        _lib.check(lib.b200_pwa_gate(o.data_ptr(), g.data_ptr(), og.data_ptr(), S, N, H, _stream()))
+        linear_bf16(og, w.w_o, residual=m[b].view(S * N, c_m) if add_residual else None, out_dtype=m.dtype,
+                    out=out[b].view(S * N, c_m))
+    return out

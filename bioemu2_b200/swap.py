@@ -9,7 +9,8 @@ package is never imported here), builds the twin with the same constructor attri
 Recognised classes (src/bioemu2/biomoa/ops/):
 ``TriangleMultiplicationFull / Cueq / CueqTiled / Outgoing / Incoming`` (triangle_multiplication.py:86-395),
 ``Transition`` (transition.py:17-91), ``AttentionPairBias`` (attention_pair_bias.py:42-225),
-``OuterProductMeanVanilla / TritonMemorySaving`` (outer_product_mean.py:32-152).
+``OuterProductMeanVanilla / TritonMemorySaving`` (outer_product_mean.py:32-152),
+``PairWeightedAveraging`` (pair_weighted_averaging.py:6-153).
 A module whose sizes the kernels are not built for (for example a triangle multiplication of width 64) is left in
 place and reported, unless ``strict=True``.
 """
@@ -19,13 +20,14 @@ import torch.nn as nn
 
 from .attention_pair_bias import AttentionPairBias
 from .outer_product_mean import OuterProductMean
+from .pair_weighted_averaging import PairWeightedAveraging
 from .transition import Transition
 from .triangle_multiplication import TriangleMultiplication
 
 _TRIMUL = {"TriangleMultiplicationFull", "TriangleMultiplicationCueq", "TriangleMultiplicationCueqTiled",
            "TriangleMultiplicationOutgoing", "TriangleMultiplicationIncoming"}
 _OPM = {"OuterProductMeanVanilla", "OuterProductMeanTritonMemorySaving"}
-_OWN = (TriangleMultiplication, Transition, AttentionPairBias, OuterProductMean)
+_OWN = (TriangleMultiplication, Transition, AttentionPairBias, OuterProductMean, PairWeightedAveraging)
 
 
 def _is_reference_op(m: nn.Module) -> bool:
@@ -47,6 +49,9 @@ def to_b200(ref: nn.Module) -> nn.Module:
         new = AttentionPairBias(ref.proj_g.in_features, ref.proj_z.in_features, ref.num_heads, inf=ref.inf,
                                 initial_norm=ref.initial_norm, tile_size=getattr(ref, "tile_size", 512),
                                 use_bias_in_layer_norm=ref.norm_z.bias is not None)
+    elif name == "PairWeightedAveraging":
+        new = PairWeightedAveraging(ref.c_m, ref.c_z, ref.c_h, ref.num_heads, inf=ref.inf,
+                                    use_bias_in_layer_norm=ref.norm_z.bias is not None)
     elif name in _OPM:
         new = OuterProductMean(ref.norm.normalized_shape[0], ref.c_hidden, ref.proj_o.out_features,
                                tile_size=getattr(ref, "tile_size", None))
@@ -67,7 +72,7 @@ def swap_into(model: nn.Module, strict: bool = False) -> dict[str, tuple[str, st
     def walk(parent: nn.Module, prefix: str) -> None:
         for name, child in list(parent.named_children()):
             path = f"{prefix}.{name}" if prefix else name
-            if _is_reference_op(child) and (type(child).__name__ in _TRIMUL | _OPM | {"Transition", "AttentionPairBias"}):
+            if _is_reference_op(child) and (type(child).__name__ in _TRIMUL | _OPM | {"Transition", "AttentionPairBias", "PairWeightedAveraging"}):
                 try:
                     twin = to_b200(child)
                 except ValueError as exc:

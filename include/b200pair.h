@@ -380,6 +380,21 @@ int b200_adaln_fwd(const void* x, const float* cond, int cond_width, int alpha_c
 int b200_gated_residual_fwd(void* x, const void* h, const float* cond, int cond_width, int gamma_col, int64_t rows,
                             int cols, int x_dtype, int h_dtype, b200_stream_t stream);
 
+/* ---------------------------------------------------------------------------------------------------
+ * Pair-weighted averaging, PairWeightedAveraging.forward (src/bioemu2/biomoa/ops/pair_weighted_averaging.py:121-153),
+ * is assembled from b200_rows_to_bf16 (norm_m), b200_linear_bf16 (proj_g, proj_o), b200_pair_bias_fwd (proj_z(norm_z(z))),
+ * b200_bmm_nt (proj_m written transposed per head; the weighted average itself) and the two kernels below.
+ *
+ * b200_masked_softmax_rows  w[h][i][j] = softmax_j(mask[i][j] ? logits[h][i][j] : -1e6) (:141-142); logits bf16 in base-2
+ *                           units [H][n][pitch] as b200_pair_bias_fwd writes them, mask one byte per pair [n][n],
+ *                           w bf16 [H][n][pitch] with zeros in columns n .. pitch-1.
+ * b200_pwa_gate             og[(s,i)][h*32+d] = sigmoid(g[(s,i)][h*32+d]) * o[h][i][s*32+d] (:145-151): gating and the
+ *                           re-layout from per-head products to MSA rows; heads of 32 channels.
+ * ------------------------------------------------------------------------------------------------- */
+int b200_masked_softmax_rows(const void* logits, const uint8_t* mask, void* out, int H, int n, int pitch,
+                             b200_stream_t stream);
+int b200_pwa_gate(const void* o, const void* g, void* og, int S, int n, int H, b200_stream_t stream);
+
 #ifdef __cplusplus
 }
 #endif

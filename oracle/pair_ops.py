@@ -158,6 +158,42 @@ def pairmixer_layer(z: Tensor, pair_mask: Tensor, w: dict) -> Tensor:
     return z
 
 
+def pair_weighted_averaging(m: Tensor, z: Tensor, mask: Tensor, w: dict, num_heads: int = 8, inf: float = 1e6) -> Tensor:
+    """``PairWeightedAveraging.forward`` (un-chunked branch).
+
+    src/bioemu2/biomoa/ops/pair_weighted_averaging.py:121-153: weights ``softmax_j(proj_z(norm_z(z))[i, j, h])`` with
+    masked pairs REPLACED by ``-inf`` (finite 1e6, :141), values ``proj_m(norm_m(m))``, gate ``sigmoid(proj_g(norm_m(m)))``,
+    ``out[s, i] = proj_o(gate * sum_j w[h, i, j] v[s, j, h, :])``.  ``m[B,S,N,c_m]``, ``z[B,N,N,c_z]``, ``mask[B,N,N]``.
+    """
+    B, S, N, _ = m.shape
+    H = num_heads
+    mn = layer_norm(m, w["norm_m.weight"], w["norm_m.bias"])
+    v = linear(mn, w["proj_m.weight"])
+    c_h = v.shape[-1] // H
+    v = v.view(B, S, N, H, c_h)
+    b = linear(layer_norm(z, w["norm_z.weight"], w.get("norm_z.bias")), w["proj_z.weight"]).permute(0, 3, 1, 2)
+    b = torch.where(mask.bool()[:, None], b, torch.full_like(b, -inf))
+    wts = b.softmax(dim=-1)                                   # [B, H, i, j]
+    g = torch.sigmoid(linear(mn, w["proj_g.weight"]))
+    o = torch.einsum("bhij,bsjhd->bsihd", wts, v).reshape(B, S, N, H * c_h)
+    return linear(g * o, w["proj_o.weight"])
+
+
+def pairmixer_msa_layer(z: Tensor, m: Tensor, pair_mask: Tensor, msa_mask: Tensor, w: dict):
+    """``PairMixerMSALayer.forward`` in eval mode: returns ``(z, m)`` (``s`` passes through).
+
+    src/bioemu2/biomoa/modules/pairmixer.py:738-757: ``m += PWA(m, z); m += T(m); z += OPM(m); z += TriMul_out(z);
+    z += TriMul_in(z); z += T(z)``.
+    """
+    m = m + pair_weighted_averaging(m, z, pair_mask, _sub(w, "pair_weighted_averaging"))
+    m = m + transition(m, _sub(w, "msa_transition"))
+    z = z + outer_product_mean(m, msa_mask, _sub(w, "outer_product_mean"))
+    z = z + triangle_multiplication(z, pair_mask, _sub(w, "tri_mul_out"), "outgoing")
+    z = z + triangle_multiplication(z, pair_mask, _sub(w, "tri_mul_in"), "incoming")
+    z = z + transition(z, _sub(w, "z_transition"))
+    return z, m
+
+
 def pairmixer_module(z: Tensor, pair_mask: Tensor, w: dict, num_blocks: int) -> Tensor:
     """``PairMixerModule.forward``: src/bioemu2/biomoa/modules/pairmixer.py:368-370."""
     for i in range(num_blocks):

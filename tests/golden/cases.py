@@ -107,6 +107,30 @@ def cond_layer_case(seed: int = 16, B: int = 1, M: int = 2, N: int = 24, dim: in
                 lns_scale=0.5)
 
 
+def pwa_case(seed: int = 17, B: int = 2, S: int = 10, N: int = 24, c_m: int = 64, c_z: int = 128):
+    g = _gen(seed)
+    w = H.pwa_weights(g, c_m, c_z, 32, 8)
+    m = torch.randn(B, S, N, c_m, generator=g)
+    z = torch.randn(B, N, N, c_z, generator=g)
+    tok = torch.ones(B, N, dtype=torch.bool)
+    tok[0, N - 4:] = False
+    mask = tok[:, :, None] & tok[:, None, :]
+    return dict(kind="pwa", w=w, m=m, z=z, mask=mask)
+
+
+def msa_layer_case(seed: int = 18, S: int = 12, N: int = 24):
+    g = _gen(seed)
+    w = H.msa_layer_weights(g)
+    m = torch.randn(1, S, N, 64, generator=g)
+    z = torch.randn(1, N, N, 128, generator=g)
+    tok = torch.ones(1, N, dtype=torch.bool)
+    tok[0, N - 3:] = False
+    pair_mask = tok[:, :, None] & tok[:, None, :]
+    msa_mask = tok[:, None, :].expand(1, S, N).clone()
+    msa_mask[0, 2] = False
+    return dict(kind="msa_layer", w=w, m=m, z=z, pair_mask=pair_mask, msa_mask=msa_mask)
+
+
 CASES = {
     "trimul_outgoing": lambda: trimul_case("outgoing"),
     "trimul_incoming": lambda: trimul_case("incoming", seed=21),
@@ -119,12 +143,14 @@ CASES = {
     "opm_mask2d": lambda: opm_case(seed=25, B=1, S=3, mask_2d=True),
     "pairmixer_layer": lambda: pairmixer_case(),
     "cond_layer": lambda: cond_layer_case(),
+    "pwa": lambda: pwa_case(),
+    "msa_layer": lambda: msa_layer_case(),
 }
 
 
 def case_tensors(case: dict):
     out = [v for _, v in sorted(case["w"].items())]
-    for k in ("x", "s", "z", "m", "c", "mask", "pair_mask"):
+    for k in ("x", "s", "z", "m", "c", "mask", "pair_mask", "msa_mask"):
         if k in case:
             out.append(case[k].float())
     return out

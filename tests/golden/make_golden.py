@@ -61,6 +61,21 @@ def run_reference(case: dict) -> torch.Tensor:
             ).eval()
             mod.load_state_dict(w, strict=True)
             return mod(case["x"], case["z"], case["c"], case["mask"], multiplicity=case["M"])
+        if kind == "pwa":
+            from bioemu2.biomoa.ops.pair_weighted_averaging import PairWeightedAveraging
+
+            mod = PairWeightedAveraging(c_m=case["m"].shape[-1], c_z=case["z"].shape[-1], c_h=32, num_heads=8).eval()
+            mod.load_state_dict(w, strict=True)
+            return mod(case["m"], case["z"], case["mask"])
+        if kind == "msa_layer":
+            from bioemu2.biomoa.modules.pairmixer import PairMixerMSALayer
+
+            mod = PairMixerMSALayer(token_s=384, msa_s=64, token_z=128, msa_dropout=0.0, z_dropout=0.0,
+                                    trimul_variant="full").eval()
+            mod.load_state_dict(w, strict=True)
+            s = torch.zeros(1, case["z"].shape[1], 384)
+            _, z, m = mod(s, case["z"], case["m"], case["pair_mask"], case["msa_mask"])
+            return torch.cat([z.flatten(), m.flatten()])   # both updated tensors, pair first
     raise KeyError(kind)
 
 

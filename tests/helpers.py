@@ -73,6 +73,29 @@ def triatt_weights(gen, dim=128, heads=4, head_dim=32, perturbed=True) -> dict:
     return w
 
 
+def pwa_weights(gen, c_m=64, c_z=128, c_h=32, heads=8, perturbed=True) -> dict:
+    w = {}
+    w["norm_m.weight"], w["norm_m.bias"] = ln_params(gen, c_m, perturbed)
+    w["norm_z.weight"], w["norm_z.bias"] = ln_params(gen, c_z, perturbed)
+    w["proj_m.weight"] = kaiming_linear(gen, c_h * heads, c_m)
+    w["proj_g.weight"] = kaiming_linear(gen, c_h * heads, c_m)
+    w["proj_z.weight"] = kaiming_linear(gen, heads, c_z)
+    w["proj_o.weight"] = kaiming_linear(gen, c_m, c_h * heads)
+    return w
+
+
+def msa_layer_weights(gen, msa_s=64, token_z=128, perturbed=True) -> dict:
+    """State dict of the reference's ``PairMixerMSALayer`` in module-construction order."""
+    w = {}
+    w.update(prefixed("msa_transition", transition_weights(gen, msa_s, 4 * msa_s, True, perturbed)))
+    w.update(prefixed("pair_weighted_averaging", pwa_weights(gen, msa_s, token_z, 32, 8, perturbed)))
+    w.update(prefixed("tri_mul_out", trimul_weights(gen, token_z, perturbed)))
+    w.update(prefixed("tri_mul_in", trimul_weights(gen, token_z, perturbed)))
+    w.update(prefixed("z_transition", transition_weights(gen, token_z, 4 * token_z, True, perturbed)))
+    w.update(prefixed("outer_product_mean", opm_weights(gen, msa_s, 32, token_z, perturbed)))
+    return w
+
+
 def prefixed(prefix: str, w: dict) -> dict:
     return {f"{prefix}.{k}": v for k, v in w.items()}
 

@@ -36,6 +36,11 @@ def run_oracle(case: dict, dtype=torch.float32) -> torch.Tensor:
     if kind == "cond_layer":
         return O.conditioned_transformer_layer(f(case["x"]), f(case["z"]), f(case["c"]), case["mask"], w,
                                                case["heads"], case["M"], case["lns_scale"])
+    if kind == "pwa":
+        return O.pair_weighted_averaging(f(case["m"]), f(case["z"]), case["mask"], w)
+    if kind == "msa_layer":
+        z, m = O.pairmixer_msa_layer(f(case["z"]), f(case["m"]), case["pair_mask"], case["msa_mask"], w)
+        return torch.cat([z.flatten(), m.flatten()])
     raise KeyError(kind)
 
 
