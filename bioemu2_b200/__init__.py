@@ -1,7 +1,7 @@
 """B200-native (sm_100a) kernels for BioEmu2's pair-representation hot path behind the reference's
 ``nn.Module`` contracts.  Importing the package loads the CUDA library; without it the import fails."""
 from . import _lib  # noqa: F401  (fails loudly when the library is not built)
-from . import context_parallel, functional
+from . import context_parallel, functional, ieee, precision
 from .attention_pair_bias import AttentionPairBias, PairBiasCache
 from .outer_product_mean import (
     OuterProductMean,
@@ -28,6 +28,8 @@ from .triangle_multiplication import (
 __all__ = [
     "context_parallel",
     "functional",
+    "ieee",
+    "precision",
     "AttentionPairBias",
     "PairBiasCache",
     "OuterProductMean",

@@ -14,6 +14,7 @@ import torch.nn as nn
 from torch import Tensor
 
 from . import functional as F
+from . import ieee, precision
 from .triangle_multiplication import PackedWeightsMixin
 
 
@@ -56,10 +57,17 @@ class AttentionPairBias(PackedWeightsMixin, nn.Module):
 
     _bias_cache = None   # (PairBiasCache, index of this module in it) once a cache has adopted the module
 
+    def _build_split(self):
+        wz = torch.zeros(16, self.c_z, dtype=torch.float32, device=self.proj_z.weight.device)
+        wz[:self.num_heads] = self.proj_z.weight.detach().float()
+        return ieee.SplitWeights(w_qkv=self.proj_qkv.weight, w_g=self.proj_g.weight, w_z=wz, w_o=self.proj_o.weight)
+
     def forward(self, s: Tensor, z: Tensor, mask: Tensor, multiplicity: int = 1) -> Tensor:
         """``s[B*M,N,c_s]``, ``z[B,N,N,c_z]``, ``mask[B,N]`` bool -> ``[B*M,N,c_s]``."""
         assert s.ndim == 3 and z.ndim == 4 and mask.ndim == 2, f"{s.shape}, {z.shape}, {mask.shape}"
         assert s.shape[0] == z.shape[0] * multiplicity, f"{s.shape}, {z.shape}, multiplicity={multiplicity}"
+        if precision.use_ieee(None, s, z):
+            return ieee.attention_pair_bias(s, z, mask, self, self.split_weights(), multiplicity)
         if self._bias_cache is not None:
             cache, index = self._bias_cache
             bias = cache.lookup(index, z)

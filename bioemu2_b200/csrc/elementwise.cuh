@@ -256,4 +256,119 @@ pwa_gate_kernel(const __nv_bfloat16* __restrict__ o, const __nv_bfloat16* __rest
   }
 }
 
+// ---------------------------------------------------------------------------------------------------------------
+// fp32-accurate arithmetic on the bf16 tensor cores: a value x is carried as hi = bf16(x) and lo = bf16(x - hi)
+// (16 significant bits together), and a product of two such operands as hi.hi + hi.lo + lo.hi accumulated in fp32.
+// With the three pieces laid side by side along K -- (hi | hi | lo) for one operand, (hi | lo | hi) for the other --
+// that sum is ONE ordinary K-major product of width 3K, so the GEMM kernel needs no change.
+//
+// y[r] = split([LayerNorm](x[r])) : x fp32 [rows][cols] -> bf16 [rows][3*cols].  order 0 = (hi | hi | lo), 1 = (hi | lo | hi).
+// One warp per row; LayerNorm (fp32, two-pass) only for cols <= 1024.
+__global__ void __launch_bounds__(256)
+split_rows_kernel(const float* __restrict__ x, __nv_bfloat16* __restrict__ y, const float* __restrict__ w,
+                  const float* __restrict__ b, long long rows, int cols, float eps, int normalize, int order) {
+  const int lane = threadIdx.x & 31;
+  const long long warp_global = (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  const long long warp_stride = (long long)gridDim.x * (blockDim.x >> 5);
+  const int nvec = cols >> 3;
+  for (long long r = warp_global; r < rows; r += warp_stride) {
+    const float* xr = x + r * cols;
+    float mean = 0.f, rstd = 1.f;
+    if (normalize) {
+      float s = 0.f;
+      for (int v = lane; v < nvec; v += 32) {
+        float f[8];
+        load8<true>(xr, v * 8, f);
+#pragma unroll
+        for (int e = 0; e < 8; ++e) s += f[e];
+      }
+      mean = warp_sum(s) / float(cols);
+      float ss = 0.f;
+      for (int v = lane; v < nvec; v += 32) {
+        float f[8];
+        load8<true>(xr, v * 8, f);
+#pragma unroll
+        for (int e = 0; e < 8; ++e) ss = fmaf(f[e] - mean, f[e] - mean, ss);
+      }
+      rstd = rsqrtf(warp_sum(ss) / float(cols) + eps);
+    }
+    __nv_bfloat16* yr = y + r * 3 * (long long)cols;
+    for (int v = lane; v < nvec; v += 32) {
+      float f[8], hi[8], lo[8];
+      load8<true>(xr, v * 8, f);
+#pragma unroll
+      for (int e = 0; e < 8; ++e) {
+        if (normalize) {
+          f[e] = (f[e] - mean) * rstd;
+          if (w) f[e] *= w[v * 8 + e];
+          if (b) f[e] += b[v * 8 + e];
+        }
+        hi[e] = __bfloat162float(__float2bfloat16_rn(f[e]));
+        lo[e] = f[e] - hi[e];
+      }
+      store8<false>(yr, v * 8, hi);
+      store8<false>(yr + cols, v * 8, order ? lo : hi);
+      store8<false>(yr + 2 * cols, v * 8, order ? hi : lo);
+    }
+  }
+}
+
+// fp32 gating: out[r][c] = a[r][c] * act(b[r][c]) [* (rowmask[r] != 0)], a and b given with their own row pitches.
+// mode 0: a * sigmoid(b) (gated projections); mode 1: silu(a) * b (SwiGLU); mode 2: a alone (row masking only).
+// Accurate exponentials, no approximations.
+__global__ void __launch_bounds__(256)
+gate_rows_f32_kernel(const float* __restrict__ a, long long a_pitch, const float* __restrict__ b, long long b_pitch,
+                     const uint8_t* __restrict__ rowmask, float* __restrict__ out, long long rows, int cols, int mode) {
+  const int nvec = cols >> 2;
+  const long long total = rows * nvec;
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (long long)gridDim.x * blockDim.x) {
+    const long long r = i / nvec;
+    const int v = int(i - r * nvec);
+    const float4 av = *reinterpret_cast<const float4*>(a + r * a_pitch + v * 4);
+    const float4 bv = *reinterpret_cast<const float4*>(b + r * b_pitch + v * 4);
+    const float keep = (rowmask == nullptr || rowmask[r]) ? 1.f : 0.f;
+    float x[4] = {av.x, av.y, av.z, av.w}, g[4] = {bv.x, bv.y, bv.z, bv.w}, o[4];
+#pragma unroll
+    for (int e = 0; e < 4; ++e)
+      o[e] = keep * (mode == 0 ? x[e] / (1.f + expf(-g[e])) : mode == 1 ? x[e] / (1.f + expf(-x[e])) * g[e] : x[e]);
+    *reinterpret_cast<float4*>(out + r * cols + v * 4) = make_float4(o[0], o[1], o[2], o[3]);
+  }
+}
+
+// fp32 softmax over keys of attention logits with an additive bias and the reference's key mask:
+//   p[g][q][k] = softmax_k( keymask[g / mask_div][k] ? s[g][q][k] + bias[g_bias][q][k] : -1e6 ),   in place in s,
+// g_bias = (g / (H * bias_div)) * H + g % H  (the bias of a batch item is shared by its `bias_div` copies).
+__global__ void __launch_bounds__(256)
+softmax_bias_f32_kernel(float* __restrict__ s, const float* __restrict__ bias, const uint8_t* __restrict__ keymask,
+                        long long groups, int n, int H, int bias_div, int mask_div_heads) {
+  const int lane = threadIdx.x & 31;
+  const long long rows = groups * n;
+  const long long warp_global = (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  const long long warp_stride = (long long)gridDim.x * (blockDim.x >> 5);
+  for (long long r = warp_global; r < rows; r += warp_stride) {
+    const long long g = r / n;
+    const int q = int(r - g * n);
+    const long long gb = (g / ((long long)H * bias_div)) * H + g % H;
+    float* sr = s + r * n;
+    const float* br = bias ? bias + (gb * n + q) * (long long)n : nullptr;
+    const uint8_t* mr = keymask + (g / mask_div_heads) * n;
+    float mx = -INFINITY;
+    for (int k = lane; k < n; k += 32) {
+      const float v = mr[k] ? sr[k] + (br ? br[k] : 0.f) : -1.0e6f;
+      sr[k] = v;
+      mx = fmaxf(mx, v);
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
+    float sum = 0.f;
+    for (int k = lane; k < n; k += 32) {
+      const float e = expf(sr[k] - mx);
+      sr[k] = e;
+      sum += e;
+    }
+    const float inv = 1.f / warp_sum(sum);
+    for (int k = lane; k < n; k += 32) sr[k] *= inv;
+  }
+}
+
 }  // namespace b200

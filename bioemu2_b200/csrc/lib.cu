@@ -1292,4 +1292,46 @@ int b200_pwa_gate(const void* o, const void* g, void* og, int S, int n, int H, b
   return B200_OK;
 }
 
+int b200_split_rows(const void* x, void* y, const float* w, const float* b, int64_t rows, int cols, float eps,
+                    int normalize, int order, b200_stream_t stream) {
+  if (int e = b200_check_device()) return e;
+  B200_CHECK_ARG(x && y, "x/y is NULL");
+  B200_CHECK_ARG(rows >= 0 && cols > 0 && cols % 8 == 0, "cols=%d must be a positive multiple of 8", cols);
+  B200_CHECK_ARG(!normalize || cols <= 1024, "LayerNorm rows hold at most 1024 channels");
+  B200_CHECK_ARG(order == 0 || order == 1, "order must be 0 (hi|hi|lo) or 1 (hi|lo|hi)");
+  B200_CHECK_ARG(aligned(x, 32) && aligned(y, 16), "x must be 32-byte aligned, y 16-byte aligned");
+  if (rows == 0) return B200_OK;
+  split_rows_kernel<<<grid_for(rows, 8), 256, 0, static_cast<cudaStream_t>(stream)>>>(
+      static_cast<const float*>(x), static_cast<__nv_bfloat16*>(y), w, b, rows, cols, eps, normalize, order);
+  B200_AFTER_LAUNCH();
+  return B200_OK;
+}
+
+int b200_gate_rows_f32(const float* a, int64_t a_pitch, const float* b, int64_t b_pitch, const uint8_t* rowmask,
+                       float* out, int64_t rows, int cols, int mode, b200_stream_t stream) {
+  if (int e = b200_check_device()) return e;
+  B200_CHECK_ARG(a && b && out, "a/b/out is NULL");
+  B200_CHECK_ARG(rows >= 0 && cols > 0 && cols % 4 == 0 && a_pitch % 4 == 0 && b_pitch % 4 == 0,
+                 "cols and the pitches must be multiples of 4");
+  B200_CHECK_ARG(mode >= 0 && mode <= 2, "mode must be 0 (a * sigmoid(b)), 1 (silu(a) * b) or 2 (a)");
+  B200_CHECK_ARG(aligned(a, 16) && aligned(b, 16) && aligned(out, 16), "a/b/out must be 16-byte aligned");
+  if (rows == 0) return B200_OK;
+  gate_rows_f32_kernel<<<grid_for(rows * (cols / 4), 256), 256, 0, static_cast<cudaStream_t>(stream)>>>(
+      a, a_pitch, b, b_pitch, rowmask, out, rows, cols, mode);
+  B200_AFTER_LAUNCH();
+  return B200_OK;
+}
+
+int b200_softmax_bias_f32(float* s, const float* bias, const uint8_t* keymask, int64_t groups, int n, int H, int bias_div,
+                          b200_stream_t stream) {
+  if (int e = b200_check_device()) return e;
+  B200_CHECK_ARG(s && keymask, "s/keymask is NULL");
+  B200_CHECK_ARG(groups > 0 && n > 0 && H > 0 && bias_div > 0 && groups % ((int64_t)H * bias_div) == 0,
+                 "groups must be a multiple of H * bias_div");
+  softmax_bias_f32_kernel<<<grid_for(groups * n, 8), 256, 0, static_cast<cudaStream_t>(stream)>>>(
+      s, bias, keymask, groups, n, H, bias_div, H * bias_div);
+  B200_AFTER_LAUNCH();
+  return B200_OK;
+}
+
 }  // extern "C"

@@ -11,6 +11,7 @@ import torch.nn as nn
 from torch import Tensor
 
 from . import functional as F
+from . import ieee, precision
 from .triangle_multiplication import PackedWeightsMixin
 
 
@@ -36,13 +37,26 @@ class Transition(PackedWeightsMixin, nn.Module):
         return cls(self.norm.weight if self.use_norm else None, self.norm.bias if self.use_norm else None,
                    self.fc1.weight, self.fc2.weight, self.fc3.weight)
 
+    def _build_split(self):
+        import torch
+
+        return ieee.SplitWeights(w12=torch.cat([self.fc1.weight, self.fc2.weight], dim=0), w3=self.fc3.weight)
+
+    def _ieee(self, x: Tensor, add_residual: bool) -> Tensor:
+        return ieee.transition(x, self.norm if self.use_norm else None, self.fc1, self.fc2, self.fc3, self.split_weights(),
+                               add_residual)
+
     def forward(self, x: Tensor) -> Tensor:
+        if precision.use_ieee(None, x):
+            return self._ieee(x, False)
         if self._fused:
             return F.transition(x, self.packed())
         return F.transition_generic(x, self.packed())
 
     def forward_residual_(self, x: Tensor) -> Tensor:
         """``x += forward(x)`` in place, fused into the kernel's final store; returns ``x``."""
+        if precision.use_ieee(None, x):
+            return x.copy_(self._ieee(x, True))
         if self._fused:
             return F.transition(x, self.packed(), add_residual=True, out=x)
         return F.transition_generic(x, self.packed(), add_residual=True, out=x)

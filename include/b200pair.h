@@ -395,6 +395,30 @@ int b200_masked_softmax_rows(const void* logits, const uint8_t* mask, void* out,
                              b200_stream_t stream);
 int b200_pwa_gate(const void* o, const void* g, void* og, int S, int n, int H, b200_stream_t stream);
 
+/* ---------------------------------------------------------------------------------------------------
+ * fp32-accurate ("ieee") arithmetic.  The reference keeps some products in fp32 whatever the autocast state -- the
+ * attention core (src/bioemu2/biomoa/ops/attention_pair_bias.py:165-167), the outer-product contraction
+ * (outer_product_mean.py:66-74, matmul_precision "ieee"), the whole denoiser (biomoa/models/score_model.py:355) -- and
+ * its fp32 tests hold the variants to 1e-6 .. 2e-6 (tests/biomoa/ops/test_triangle_multiplication.py:19-48).  On the
+ * bf16 tensor cores an fp32 value travels as hi = bf16(x), lo = bf16(x - hi); with one operand laid out along K as
+ * (hi | hi | lo) and the other as (hi | lo | hi), the ordinary K-major product of width 3K is hi.hi + hi.lo + lo.hi,
+ * accumulated in fp32: b200_bmm_nt / b200_linear_bf16 serve unchanged (out_dtype fp32).
+ *
+ * b200_split_rows       y[r] = split([LayerNorm](x[r])): x fp32 [rows][cols] -> bf16 [rows][3*cols]; order 0 = hi|hi|lo
+ *                       (the A side), 1 = hi|lo|hi (the B side, weights).  normalize != 0: LayerNorm with w, b (may be
+ *                       NULL), eps, cols <= 1024.
+ * b200_gate_rows_f32    out = a * sigmoid(b) (mode 0), silu(a) * b (mode 1) or a (mode 2), fp32, exact exponentials; a and b with
+ *                       their own row pitches (elements); rowmask (one byte per row, may be NULL) zeroes masked rows.
+ * b200_softmax_bias_f32 in place: s[g][q][:] = softmax_k(keymask[g / (H*bias_div)][k] ? s + bias[(g / (H*bias_div))*H + g % H][q][k] : -1e6)
+ *                       for fp32 logits s[groups][n][n], g = (batch item * bias_div + copy) * H + head.
+ * ------------------------------------------------------------------------------------------------- */
+int b200_split_rows(const void* x, void* y, const float* w, const float* b, int64_t rows, int cols, float eps,
+                    int normalize, int order, b200_stream_t stream);
+int b200_gate_rows_f32(const float* a, int64_t a_pitch, const float* b, int64_t b_pitch, const uint8_t* rowmask,
+                       float* out, int64_t rows, int cols, int mode, b200_stream_t stream);
+int b200_softmax_bias_f32(float* s, const float* bias, const uint8_t* keymask, int64_t groups, int n, int H, int bias_div,
+                          b200_stream_t stream);
+
 #ifdef __cplusplus
 }
 #endif
