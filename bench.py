@@ -557,8 +557,8 @@ def run_b200(args) -> None:
                 "ms_per_launch": t["attention_core"],
                 # dram__bytes_read.sum + dram__bytes_write.sum of one launch at N=512 (ncu capture summarised in
                 # profiles/flash_core_triatt_n512.md); the operands scale with N^2, so other sizes are scaled from it
-                "traffic": 323.5e6 * (N / 512.0) ** 2,
-                "traffic_source": "ncu capture at N=512 (271.1 MB read + 52.4 MB written), scaled by (N/512)^2; the "
+                "traffic": 323.3e6 * (N / 512.0) ** 2,
+                "traffic_source": "ncu capture at N=512 (270.8 MB read + 52.5 MB written), scaled by (N/512)^2; the "
                                   "algorithmic bytes of the launch are 337.6 MB at N=512 (four 67.1 MB operands read, one "
                                   "67.1 MB result written, 2.1 MB of bias), so the kernel moves no byte twice",
                 "note": "head dim 32 makes the core ex2-bound, not tensor-bound: N^3*4 exponentials at 16/clk/SM "
