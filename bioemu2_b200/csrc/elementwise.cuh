@@ -16,14 +16,17 @@ template <bool F32IN>
 __global__ void __launch_bounds__(256)
 layernorm_rows_kernel(const void* __restrict__ x, __nv_bfloat16* __restrict__ y,
                       const float* __restrict__ w, const float* __restrict__ b, long long rows, int cols,
-                      float eps, int normalize, int silu) {
+                      float eps, int normalize, int silu, const void* __restrict__ x2 = nullptr, int cols1 = 0) {
   const int lane = threadIdx.x & 31;
   const int nvec = cols >> 3;
   const long long warp_global = (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
   const long long warp_stride = (long long)gridDim.x * (blockDim.x >> 5);
   const float inv = 1.0f / float(cols);
   for (long long r = warp_global; r < rows; r += warp_stride) {
-    const uint8_t* xr = static_cast<const uint8_t*>(x) + r * cols * (long long)(F32IN ? 4 : 2);
+    // With a second source the row is the concatenation x[r, :cols1] | x2[r, :cols - cols1] (never materialised).
+    const int c1 = x2 ? cols1 : cols;
+    const uint8_t* xr = static_cast<const uint8_t*>(x) + r * c1 * (long long)(F32IN ? 4 : 2);
+    const uint8_t* xr2 = x2 ? static_cast<const uint8_t*>(x2) + r * (cols - c1) * (long long)(F32IN ? 4 : 2) : nullptr;
     uint4 v[4];
     float s = 0.f;
 #pragma unroll
@@ -31,7 +34,8 @@ layernorm_rows_kernel(const void* __restrict__ x, __nv_bfloat16* __restrict__ y,
       const int vi = lane + i * 32;
       if (vi < nvec) {
         float f[8];
-        load8<F32IN>(xr, vi * 8, f);
+        if (vi * 8 < c1) load8<F32IN>(xr, vi * 8, f);
+        else load8<F32IN>(xr2, vi * 8 - c1, f);
         v[i] = make_uint4(pack_bf16x2(f[0], f[1]), pack_bf16x2(f[2], f[3]), pack_bf16x2(f[4], f[5]),
                           pack_bf16x2(f[6], f[7]));
 #pragma unroll
@@ -89,6 +93,50 @@ layernorm_rows_kernel(const void* __restrict__ x, __nv_bfloat16* __restrict__ y,
         yr[vi] = make_uint4(o[0], o[1], o[2], o[3]);
       }
     }
+  }
+}
+
+// Pair initialisation: z[i, j, :] = a[i, :] + c[j, :] (+ extra[i, j, :]) in fp32; one thread per 8 channels,
+// cols a multiple of 8.  a and c are tiny and stay in L1/L2: the kernel is the write (and the read of extra).
+__global__ void __launch_bounds__(256)
+pair_outer_sum_kernel(const float* __restrict__ a, const float* __restrict__ c, const float* __restrict__ extra,
+                      float* __restrict__ z, int n_i, int n_j, int cols) {
+  const int nvec = cols >> 3;
+  const long long total = (long long)n_i * n_j * nvec;
+  for (long long t = (long long)blockIdx.x * blockDim.x + threadIdx.x; t < total; t += (long long)gridDim.x * blockDim.x) {
+    const long long pair = t / nvec;
+    const int v = int(t - pair * nvec);
+    const int i = int(pair / n_j), j = int(pair - (long long)i * n_j);
+    float fa[8], fc[8];
+    load8<true>(a + (long long)i * cols, v * 8, fa);
+    load8<true>(c + (long long)j * cols, v * 8, fc);
+#pragma unroll
+    for (int e = 0; e < 8; ++e) fa[e] += fc[e];
+    if (extra) {
+      load8<true>(extra + pair * cols, v * 8, fc);
+#pragma unroll
+      for (int e = 0; e < 8; ++e) fa[e] += fc[e];
+    }
+    store8<true>(z + pair * cols, v * 8, fa);
+  }
+}
+
+// out[r, :] = x[r, :] + y[r % period, :]  (x, out fp32 - out may be x; y fp32 or bf16).  period == rows is a plain
+// add; a smaller period broadcasts a block of `period` rows over the leading axis.
+template <bool YF32>
+__global__ void __launch_bounds__(256)
+add_rows_kernel(const float* x, const void* __restrict__ y, float* out, long long rows, long long period, int cols) {
+  const int nvec = cols >> 3;
+  const long long total = rows * nvec;
+  for (long long t = (long long)blockIdx.x * blockDim.x + threadIdx.x; t < total; t += (long long)gridDim.x * blockDim.x) {
+    const long long r = t / nvec;
+    const int v = int(t - r * nvec);
+    float fx[8], fy[8];
+    load8<true>(x + r * cols, v * 8, fx);
+    load8<YF32>(static_cast<const uint8_t*>(y) + (r % period) * cols * (long long)(YF32 ? 4 : 2), v * 8, fy);
+#pragma unroll
+    for (int e = 0; e < 8; ++e) fx[e] += fy[e];
+    store8<true>(out + r * cols, v * 8, fx);
   }
 }
 

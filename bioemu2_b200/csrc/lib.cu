@@ -114,16 +114,19 @@ static int launch_bmm(const BmmLaunch& a, cudaStream_t stream) {
 }
 
 static int launch_rows_to_bf16(const void* x, bool f32, __nv_bfloat16* y, const float* w, const float* b,
-                               int64_t rows, int cols, bool normalize, cudaStream_t stream, bool silu = false) {
+                               int64_t rows, int cols, bool normalize, cudaStream_t stream, bool silu = false,
+                               const void* x2 = nullptr, int cols1 = 0) {
   const int warps = 8;
   int64_t blocks = (rows + warps - 1) / warps;
   const int64_t cap = int64_t(sm_count()) * 16;
   if (blocks > cap) blocks = cap;
   if (blocks < 1) blocks = 1;
   if (f32)
-    layernorm_rows_kernel<true><<<int(blocks), warps * 32, 0, stream>>>(x, y, w, b, rows, cols, 1e-5f, normalize, silu);
+    layernorm_rows_kernel<true><<<int(blocks), warps * 32, 0, stream>>>(x, y, w, b, rows, cols, 1e-5f, normalize, silu,
+                                                                       x2, cols1);
   else
-    layernorm_rows_kernel<false><<<int(blocks), warps * 32, 0, stream>>>(x, y, w, b, rows, cols, 1e-5f, normalize, silu);
+    layernorm_rows_kernel<false><<<int(blocks), warps * 32, 0, stream>>>(x, y, w, b, rows, cols, 1e-5f, normalize, silu,
+                                                                        x2, cols1);
   B200_AFTER_LAUNCH();
   return 0;
 }
@@ -1198,6 +1201,49 @@ int b200_rows_to_bf16(const void* x, void* y, const float* w, const float* b, in
   if (rows == 0) return B200_OK;
   return launch_rows_to_bf16(x, x_dtype == B200_DTYPE_F32, static_cast<__nv_bfloat16*>(y), w, b, rows, cols,
                              normalize != 0, static_cast<cudaStream_t>(stream), silu != 0);
+}
+
+int b200_rows2_to_bf16(const void* x1, int cols1, const void* x2, int cols2, void* y, const float* w, const float* b,
+                       int64_t rows, int x_dtype, int normalize, b200_stream_t stream) {
+  if (int e = b200_check_device()) return e;
+  B200_CHECK_ARG(x1 && x2 && y, "x1/x2/y is NULL");
+  B200_CHECK_ARG(rows >= 0 && cols1 > 0 && cols2 > 0 && cols1 % 8 == 0 && cols2 % 8 == 0 && cols1 + cols2 <= 1024,
+                 "cols1=%d and cols2=%d must be positive multiples of 8 with a sum <= 1024", cols1, cols2);
+  B200_CHECK_ARG((x_dtype | 1) == 1, "unknown dtype");
+  B200_CHECK_ARG(aligned(x1, 32) && aligned(x2, 32) && aligned(y, 16), "x1/x2 must be 32-byte aligned, y 16-byte aligned");
+  if (rows == 0) return B200_OK;
+  return launch_rows_to_bf16(x1, x_dtype == B200_DTYPE_F32, static_cast<__nv_bfloat16*>(y), w, b, rows, cols1 + cols2,
+                             normalize != 0, static_cast<cudaStream_t>(stream), false, x2, cols1);
+}
+
+int b200_pair_outer_sum(const float* a, const float* c, const float* extra, float* z, int n_i, int n_j, int cols,
+                        b200_stream_t stream) {
+  if (int e = b200_check_device()) return e;
+  B200_CHECK_ARG(a && c && z, "a/c/z is NULL");
+  B200_CHECK_ARG(n_i >= 0 && n_j >= 0 && cols > 0 && cols % 8 == 0, "cols=%d must be a positive multiple of 8", cols);
+  B200_CHECK_ARG(aligned(a, 32) && aligned(c, 32) && aligned(z, 32) && (!extra || aligned(extra, 32)),
+                 "a/c/extra/z must be 32-byte aligned");
+  if (n_i == 0 || n_j == 0) return B200_OK;
+  pair_outer_sum_kernel<<<grid_for((int64_t)n_i * n_j * (cols / 8), 256), 256, 0, static_cast<cudaStream_t>(stream)>>>(
+      a, c, extra, z, n_i, n_j, cols);
+  B200_AFTER_LAUNCH();
+  return B200_OK;
+}
+
+int b200_add_rows(const float* x, const void* y, float* out, int64_t rows, int64_t period, int cols, int y_dtype,
+                  b200_stream_t stream) {
+  if (int e = b200_check_device()) return e;
+  B200_CHECK_ARG(x && y && out, "x/y/out is NULL");
+  B200_CHECK_ARG(rows >= 0 && period > 0 && cols > 0 && cols % 8 == 0, "need period > 0 and cols a positive multiple of 8");
+  B200_CHECK_ARG((y_dtype | 1) == 1, "unknown dtype");
+  B200_CHECK_ARG(aligned(x, 32) && aligned(y, 32) && aligned(out, 32), "x/y/out must be 32-byte aligned");
+  if (rows == 0) return B200_OK;
+  const int grid = grid_for(rows * (cols / 8), 256);
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  if (y_dtype == B200_DTYPE_F32) add_rows_kernel<true><<<grid, 256, 0, st>>>(x, y, out, rows, period, cols);
+  else add_rows_kernel<false><<<grid, 256, 0, st>>>(x, y, out, rows, period, cols);
+  B200_AFTER_LAUNCH();
+  return B200_OK;
 }
 
 int b200_linear_bf16(const void* x, const void* w, const float* bias, const void* residual, void* out, int64_t rows,

@@ -358,6 +358,57 @@ def linear_bf16(x: Tensor, w_bf16: Tensor, bias_f32: Tensor | None = None, resid
     return out
 
 
+def rows2_to_bf16(x1: Tensor, x2: Tensor, weight: Tensor | None = None, bias: Tensor | None = None,
+                  normalize: bool = True) -> Tensor:
+    """``LayerNorm(cat(x1, x2, -1)) * weight + bias`` as bf16 without materialising the concatenation."""
+    _require_cuda(x1, x2)
+    if x1.shape[:-1] != x2.shape[:-1] or x1.dtype != x2.dtype:
+        raise ValueError("x1 and x2 must agree in dtype and in every axis but the last")
+    x1, x2 = x1.contiguous(), x2.contiguous()
+    c1, c2 = x1.shape[-1], x2.shape[-1]
+    y = torch.empty(x1.shape[:-1] + (c1 + c2,), dtype=torch.bfloat16, device=x1.device)
+    w = weight.detach().float().contiguous() if weight is not None else None
+    b = bias.detach().float().contiguous() if bias is not None else None
+    _lib.check(lib.b200_rows2_to_bf16(x1.data_ptr(), c1, x2.data_ptr(), c2, y.data_ptr(), _ptr(w), _ptr(b),
+                                      x1.numel() // c1, _zdtype(x1), 1 if normalize else 0, _stream()))
+    return y
+
+
+def pair_outer_sum(a: Tensor, c: Tensor, extra: Tensor | None = None) -> Tensor:
+    """``a[:, :, None, :] + c[:, None, :, :] (+ extra)`` in fp32: ``a[B, Ni, D]``, ``c[B, Nj, D]``, ``extra[B, Ni, Nj, D]``."""
+    _require_cuda(a, c)
+    if a.dtype != torch.float32 or c.dtype != torch.float32 or (extra is not None and extra.dtype != torch.float32):
+        raise ValueError("pair_outer_sum expects float32 tensors")
+    B, ni, D = a.shape
+    nj = c.shape[1]
+    if c.shape != (B, nj, D) or (extra is not None and extra.shape != (B, ni, nj, D)):
+        raise ValueError("shape mismatch between a, c and extra")
+    a, c = a.contiguous(), c.contiguous()
+    extra = extra.contiguous() if extra is not None else None
+    z = torch.empty(B, ni, nj, D, dtype=torch.float32, device=a.device)
+    for b in range(B):
+        _lib.check(lib.b200_pair_outer_sum(a[b].data_ptr(), c[b].data_ptr(), extra[b].data_ptr() if extra is not None else None,
+                                           z[b].data_ptr(), ni, nj, D, _stream()))
+    return z
+
+
+def add_rows(x: Tensor, y: Tensor, out: Tensor | None = None) -> Tensor:
+    """``x + y`` for fp32 ``x[..., cols]`` where ``y`` (fp32 or bf16) has x's shape or only its trailing axes (it is
+    then broadcast over the leading ones); ``out`` may be ``x``."""
+    _require_cuda(x, y)
+    if x.dtype != torch.float32 or not x.is_contiguous():
+        raise ValueError("add_rows expects a contiguous float32 x")
+    if tuple(x.shape[x.dim() - y.dim():]) != tuple(y.shape):
+        raise ValueError(f"y {tuple(y.shape)} does not match the trailing axes of x {tuple(x.shape)}")
+    y = y.contiguous()
+    cols = x.shape[-1]
+    if out is None:
+        out = torch.empty_like(x)
+    _lib.check(lib.b200_add_rows(x.data_ptr(), y.data_ptr(), out.data_ptr(), x.numel() // cols, y.numel() // cols, cols,
+                                 _zdtype(y), _stream()))
+    return out
+
+
 def swiglu(h12: Tensor) -> Tensor:
     """``silu(h12[..., :H]) * h12[..., H:]`` for bf16 ``h12[..., 2H]``."""
     H = h12.shape[-1] // 2

@@ -381,6 +381,28 @@ int b200_gated_residual_fwd(void* x, const void* h, const float* cond, int cond_
                             int cols, int x_dtype, int h_dtype, b200_stream_t stream);
 
 /* ---------------------------------------------------------------------------------------------------
+ * Sequence-trunk prologue, recycling and pairwise conditioning: the HBM-bound glue around the pair blocks.
+ *
+ * b200_pair_outer_sum   z[i][j][:] = a[i][:] + c[j][:] (+ extra[i][j][:]), fp32: the pair initialisation
+ *                       z_init_1(s_inputs)[:, :, None] + z_init_2(s_inputs)[:, None, :] plus the pair terms of the
+ *                       feature encoders (src/bioemu2/biomoa/modules/pairmixer.py:231-250).  One batch item per call.
+ * b200_add_rows         out[r][:] = x[r][:] + y[r % period][:], x/out fp32 (out may be x), y fp32 or bf16: the residual
+ *                       of the unconditional branch (pairmixer.py:268) with period = rows, and the broadcast of
+ *                       s_proj(emb) over the MSA rows (pairmixer.py:598) with period = tokens.
+ * b200_rows2_to_bf16    y = LN(x1[r] | x2[r]) * w + b as bf16 [rows][cols1 + cols2]: LayerNorm over the concatenation
+ *                       of two row sources that is never materialised - cat(z_trunk, token_rel_pos_feats) of
+ *                       PairwiseConditioning.forward (src/bioemu2/biomoa/modules/diffusion.py:526-529).
+ * The recycling update z_init + z_recycle(z_norm(z)) (pairmixer.py:282-283) is b200_rows_to_bf16 followed by
+ * b200_linear_bf16 with z_init as the residual.
+ * ------------------------------------------------------------------------------------------------- */
+int b200_pair_outer_sum(const float* a, const float* c, const float* extra, float* z, int n_i, int n_j, int cols,
+                        b200_stream_t stream);
+int b200_add_rows(const float* x, const void* y, float* out, int64_t rows, int64_t period, int cols, int y_dtype,
+                  b200_stream_t stream);
+int b200_rows2_to_bf16(const void* x1, int cols1, const void* x2, int cols2, void* y, const float* w, const float* b,
+                       int64_t rows, int x_dtype, int normalize, b200_stream_t stream);
+
+/* ---------------------------------------------------------------------------------------------------
  * Pair-weighted averaging, PairWeightedAveraging.forward (src/bioemu2/biomoa/ops/pair_weighted_averaging.py:121-153),
  * is assembled from b200_rows_to_bf16 (norm_m), b200_linear_bf16 (proj_g, proj_o), b200_pair_bias_fwd (proj_z(norm_z(z))),
  * b200_bmm_nt (proj_m written transposed per head; the weighted average itself) and the two kernels below.

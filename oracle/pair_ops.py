@@ -201,6 +201,61 @@ def pairmixer_module(z: Tensor, pair_mask: Tensor, w: dict, num_blocks: int) -> 
     return z
 
 
+def pairwise_conditioning(z_trunk: Tensor, rel_pos_feats: Tensor, w: dict, num_transitions: int = 2) -> Tensor:
+    """``PairwiseConditioning.forward``: src/bioemu2/biomoa/modules/diffusion.py:526-534.
+
+    ``Linear(LN(cat(z_trunk, rel_pos_feats)))`` (:493-494, no bias), then ``z = T(z) + z`` per transition.
+    """
+    z = torch.cat((z_trunk, rel_pos_feats), dim=-1)
+    z = linear(layer_norm(z, w["dim_pairwise_init_proj.0.weight"], w["dim_pairwise_init_proj.0.bias"]),
+               w["dim_pairwise_init_proj.1.weight"])
+    for i in range(num_transitions):
+        z = transition(z, _sub(w, f"transitions.{i}")) + z
+    return z
+
+
+def pairmixer_msa_module(z: Tensor, emb: Tensor, feats: dict, w: dict, blocks: int, use_paired_feature: bool = True) -> Tensor:
+    """``PairMixerMSAModule.forward`` with ``s=None``: src/bioemu2/biomoa/modules/pairmixer.py:582-612.
+
+    ``m = msa_proj(cat(msa, has_deletion, deletion_value[, msa_paired])) + s_proj(emb)[:, None]`` (:590-599), then the MSA
+    layers; only the pair tensor leaves the module.
+    """
+    dt = w["msa_proj.weight"].dtype
+    cols = [feats["msa"].to(dt), feats["has_deletion"].to(dt)[..., None], feats["deletion_value"].to(dt)[..., None]]
+    if use_paired_feature:
+        cols.append(feats["msa_paired"].to(dt)[..., None])
+    m = linear(torch.cat(cols, dim=-1), w["msa_proj.weight"]) + linear(emb, w["s_proj.weight"])[:, None]
+    tok = feats["token_pad_mask"].bool()
+    pair_mask = tok[:, :, None] & tok[:, None, :]
+    for i in range(blocks):
+        z, m = pairmixer_msa_layer(z, m, pair_mask, feats["msa_mask"], _sub(w, f"layers.{i}"))
+    return z
+
+
+def sequence_trunk(s_inputs: Tensor, pair_terms: Tensor, feats: dict, w: dict, *, recycles: int, msa_blocks: int,
+                   num_blocks: int, unconditional: bool = False, use_paired_feature: bool = True):
+    """``PairMixerSequenceEmbedder.forward``: src/bioemu2/biomoa/modules/pairmixer.py:231-299.
+
+    ``pair_terms`` is the sum of what the feature encoders add to the pair initialisation (relative positions, token
+    bonds, optional conditioning; :240-256): they are input featurisation, not part of the hot path, and enter as data.
+    """
+    s_init = linear(s_inputs, w["s_init.weight"])
+    z_init = linear(s_inputs, w["z_init_1.weight"])[:, :, None] + linear(s_inputs, w["z_init_2.weight"])[:, None, :]
+    z_init = z_init + pair_terms
+    if unconditional:  # :262-270
+        zn = layer_norm(z_init, w["z_norm.weight"], w["z_norm.bias"])
+        return s_init, z_init + transition(zn, _sub(w, "uncond_transition"))
+    tok = feats["token_pad_mask"].bool()
+    pair_mask = tok[:, :, None] & tok[:, None, :]
+    s, z = torch.zeros_like(s_init), torch.zeros_like(z_init)
+    for _ in range(recycles + 1):  # :272-297
+        s = s_init + linear(layer_norm(s, w["s_norm.weight"], w["s_norm.bias"]), w["s_recycle.weight"])
+        z = z_init + linear(layer_norm(z, w["z_norm.weight"], w["z_norm.bias"]), w["z_recycle.weight"])
+        z = pairmixer_msa_module(z, s_inputs, feats, _sub(w, "msa_module"), msa_blocks, use_paired_feature)
+        z = pairmixer_module(z, pair_mask, _sub(w, "pairmixer_module"), num_blocks)  # s passes through (:368-370)
+    return s, z
+
+
 def triangle_attention(x: Tensor, mask: Tensor, w: dict, num_heads: int, ending: bool, inf: float = 1e6,
                        row_chunk: int | None = None, lines: slice | None = None) -> Tensor:
     """Triangle self-attention around the starting (or ending) node.

@@ -131,6 +131,45 @@ def msa_layer_case(seed: int = 18, S: int = 12, N: int = 24):
     return dict(kind="msa_layer", w=w, m=m, z=z, pair_mask=pair_mask, msa_mask=msa_mask)
 
 
+def pairwise_conditioning_case(seed: int = 19, N: int = 24):
+    g = _gen(seed)
+    w = H.pairwise_conditioning_weights(g)
+    z = torch.randn(1, N, N, 128, generator=g)
+    rel = torch.randn(1, N, N, 128, generator=g)
+    return dict(kind="pairwise_conditioning", w=w, z=z, rel=rel)
+
+
+def msa_feats(g: torch.Generator, S: int, N: int, n_pad: int) -> dict:
+    """Seeded stand-ins for the MSA features of the reference's feature dict (one-hot rows, 0/1 flags, a real value)."""
+    tok = torch.ones(1, N, dtype=torch.bool)
+    tok[0, N - n_pad:] = False
+    msa = torch.nn.functional.one_hot(torch.randint(0, 33, (1, S, N), generator=g), 33).float()
+    msa_mask = tok[:, None, :].expand(1, S, N).clone()
+    msa_mask[0, S - 1, : N // 2] = False
+    return dict(msa=msa, msa_mask=msa_mask,
+                has_deletion=(torch.rand(1, S, N, generator=g) < 0.2).float(),
+                deletion_value=torch.rand(1, S, N, generator=g),
+                msa_paired=(torch.rand(1, S, N, generator=g) < 0.5).float(),
+                token_pad_mask=tok)
+
+
+def msa_module_case(seed: int = 20, S: int = 10, N: int = 24, s_input_dim: int = 100, blocks: int = 2):
+    g = _gen(seed)
+    w = H.msa_module_weights(g, s_input_dim, blocks)
+    z = torch.randn(1, N, N, 128, generator=g)
+    emb = torch.randn(1, N, s_input_dim, generator=g)
+    return dict(kind="msa_module", w=w, z=z, emb=emb, feats=msa_feats(g, S, N, 3), blocks=blocks)
+
+
+def sequence_trunk_case(seed: int = 26, S: int = 8, N: int = 24, s_input_dim: int = 100, unconditional: bool = False):
+    g = _gen(seed)
+    w = H.sequence_trunk_weights(g, s_input_dim, msa_blocks=1, num_blocks=1)
+    s_inputs = torch.randn(1, N, s_input_dim, generator=g)
+    pair_terms = torch.randn(1, N, N, 128, generator=g)
+    return dict(kind="sequence_trunk", w=w, s_inputs=s_inputs, pair_terms=pair_terms, feats=msa_feats(g, S, N, 2),
+                recycles=1, msa_blocks=1, num_blocks=1, unconditional=unconditional)
+
+
 CASES = {
     "trimul_outgoing": lambda: trimul_case("outgoing"),
     "trimul_incoming": lambda: trimul_case("incoming", seed=21),
@@ -145,12 +184,18 @@ CASES = {
     "cond_layer": lambda: cond_layer_case(),
     "pwa": lambda: pwa_case(),
     "msa_layer": lambda: msa_layer_case(),
+    "pairwise_conditioning": lambda: pairwise_conditioning_case(),
+    "msa_module": lambda: msa_module_case(),
+    "sequence_trunk": lambda: sequence_trunk_case(),
+    "sequence_trunk_unconditional": lambda: sequence_trunk_case(seed=27, unconditional=True),
 }
 
 
 def case_tensors(case: dict):
     out = [v for _, v in sorted(case["w"].items())]
-    for k in ("x", "s", "z", "m", "c", "mask", "pair_mask", "msa_mask"):
+    for k in ("x", "s", "z", "m", "c", "mask", "pair_mask", "msa_mask", "rel", "emb", "s_inputs", "pair_terms"):
         if k in case:
             out.append(case[k].float())
+    for _, v in sorted(case.get("feats", {}).items()):
+        out.append(v.float())
     return out

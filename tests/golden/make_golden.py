@@ -76,6 +76,46 @@ def run_reference(case: dict) -> torch.Tensor:
             s = torch.zeros(1, case["z"].shape[1], 384)
             _, z, m = mod(s, case["z"], case["m"], case["pair_mask"], case["msa_mask"])
             return torch.cat([z.flatten(), m.flatten()])   # both updated tensors, pair first
+        if kind == "pairwise_conditioning":
+            from bioemu2.biomoa.modules.diffusion import PairwiseConditioning
+
+            mod = PairwiseConditioning(token_z=128, dim_token_rel_pos_feats=128).eval()
+            mod.load_state_dict(w, strict=True)
+            return mod(case["z"], case["rel"])
+        if kind == "msa_module":
+            from bioemu2.biomoa.modules.pairmixer import PairMixerMSAModule
+
+            f = case["feats"]
+            mod = PairMixerMSAModule(token_s=384, msa_s=64, token_z=128, s_input_dim=case["emb"].shape[-1],
+                                     msa_blocks=case["blocks"], msa_dropout=0.0, z_dropout=0.0, use_paired_feature=True,
+                                     trimul_variant="full").eval()
+            mod.load_state_dict(w, strict=True)
+            return mod(None, case["z"], case["emb"], f["msa"], f["msa_mask"], f["has_deletion"], f["deletion_value"],
+                       f["msa_paired"], f["token_pad_mask"])[1]
+        if kind == "sequence_trunk":
+            from bioemu2.biomoa.modules.pairmixer import PairMixerSequenceEmbedder
+
+            class Fixed(torch.nn.Module):  # stands in for a feature encoder: returns a fixed tensor
+                def __init__(self, t):
+                    super().__init__()
+                    self.t = t
+
+                def forward(self, *args, **kwargs):
+                    return self.t
+
+            mod = PairMixerSequenceEmbedder(
+                token_s=384, token_z=128, s_input_dim=case["s_inputs"].shape[-1], msa_s=64, msa_blocks=case["msa_blocks"],
+                msa_dropout=0.0, z_dropout=0.0, num_blocks=case["num_blocks"], trimul_variant="full", opm_variant="vanilla",
+                use_contact_conditioning=False, use_method_conditioning=False, use_paired_feature=True,
+                use_unconditional_branch=True).eval()
+            missing, unexpected = mod.load_state_dict(w, strict=False)
+            assert not unexpected and all(k.startswith(("rel_pos.", "token_bonds.")) for k in missing), (missing, unexpected)
+            # The feature encoders are input featurisation outside the path: their sum enters as the fixed `pair_terms`.
+            mod.rel_pos = Fixed(case["pair_terms"])
+            mod.token_bonds = Fixed(torch.zeros_like(case["pair_terms"]))
+            feats = dict(case["feats"], asym_id=None, entity_id=None, residue_index=None, sym_id=None, token_bonds=None)
+            s, z = mod(case["s_inputs"], feats, num_steps_recycle=case["recycles"], unconditional=case["unconditional"])
+            return torch.cat([z.flatten(), s.flatten()])   # pair tensor first, then the single representation
     raise KeyError(kind)
 
 

@@ -96,6 +96,40 @@ def msa_layer_weights(gen, msa_s=64, token_z=128, perturbed=True) -> dict:
     return w
 
 
+def pairwise_conditioning_weights(gen, token_z=128, rel=128, a_z=128, num_transitions=2, factor=2, perturbed=True) -> dict:
+    """State dict of the reference's ``PairwiseConditioning``."""
+    w = {}
+    w["dim_pairwise_init_proj.0.weight"], w["dim_pairwise_init_proj.0.bias"] = ln_params(gen, token_z + rel, perturbed)
+    w["dim_pairwise_init_proj.1.weight"] = kaiming_linear(gen, a_z, token_z + rel)
+    for i in range(num_transitions):
+        w.update(prefixed(f"transitions.{i}", transition_weights(gen, a_z, factor * a_z, True, perturbed)))
+    return w
+
+
+def msa_module_weights(gen, s_input_dim, blocks, msa_s=64, token_z=128, msa_feat=36, perturbed=True) -> dict:
+    """State dict of the reference's ``PairMixerMSAModule`` (``msa_feat`` = num_tokens + 2 + paired flag)."""
+    w = {"s_proj.weight": kaiming_linear(gen, msa_s, s_input_dim), "msa_proj.weight": kaiming_linear(gen, msa_s, msa_feat)}
+    for i in range(blocks):
+        w.update(prefixed(f"layers.{i}", msa_layer_weights(gen, msa_s, token_z, perturbed)))
+    return w
+
+
+def sequence_trunk_weights(gen, s_input_dim, msa_blocks, num_blocks, token_s=384, token_z=128, perturbed=True) -> dict:
+    """The reference ``PairMixerSequenceEmbedder``'s state dict without its feature encoders (rel_pos, token_bonds)."""
+    w = {"s_init.weight": kaiming_linear(gen, token_s, s_input_dim),
+         "z_init_1.weight": kaiming_linear(gen, token_z, s_input_dim),
+         "z_init_2.weight": kaiming_linear(gen, token_z, s_input_dim)}
+    w.update(prefixed("msa_module", msa_module_weights(gen, s_input_dim, msa_blocks, 64, token_z, 36, perturbed)))
+    for i in range(num_blocks):
+        w.update(prefixed(f"pairmixer_module.layers.{i}", pairmixer_layer_weights(gen, token_z, perturbed)))
+    w["s_recycle.weight"] = kaiming_linear(gen, token_s, token_s)
+    w["z_recycle.weight"] = kaiming_linear(gen, token_z, token_z)
+    w["s_norm.weight"], w["s_norm.bias"] = ln_params(gen, token_s, perturbed)
+    w["z_norm.weight"], w["z_norm.bias"] = ln_params(gen, token_z, perturbed)
+    w.update(prefixed("uncond_transition", transition_weights(gen, token_z, 4 * token_z, True, perturbed)))
+    return w
+
+
 def prefixed(prefix: str, w: dict) -> dict:
     return {f"{prefix}.{k}": v for k, v in w.items()}
 

@@ -41,7 +41,20 @@ def run_oracle(case: dict, dtype=torch.float32) -> torch.Tensor:
     if kind == "msa_layer":
         z, m = O.pairmixer_msa_layer(f(case["z"]), f(case["m"]), case["pair_mask"], case["msa_mask"], w)
         return torch.cat([z.flatten(), m.flatten()])
+    if kind == "pairwise_conditioning":
+        return O.pairwise_conditioning(f(case["z"]), f(case["rel"]), w)
+    if kind == "msa_module":
+        return O.pairmixer_msa_module(f(case["z"]), f(case["emb"]), _feats(case, dtype), w, case["blocks"])
+    if kind == "sequence_trunk":
+        s, z = O.sequence_trunk(f(case["s_inputs"]), f(case["pair_terms"]), _feats(case, dtype), w, recycles=case["recycles"],
+                                msa_blocks=case["msa_blocks"], num_blocks=case["num_blocks"],
+                                unconditional=case["unconditional"])
+        return torch.cat([z.flatten(), s.flatten()])
     raise KeyError(kind)
+
+
+def _feats(case: dict, dtype) -> dict:
+    return {k: (v if v.dtype == torch.bool else v.to(dtype)) for k, v in case["feats"].items()}
 
 
 @pytest.mark.parametrize("name", sorted(C.CASES))
