@@ -45,7 +45,7 @@ import torch  # noqa: E402
 METRIC = "pairformer_trunk_pair_cells_per_s"
 UNIT = "pair-cells/s"
 GRIDS = {1: (1, 1), 2: (1, 2), 4: (2, 2), 8: (2, 4)}
-PROBES = ("attention_core", "triatt", "trimul", "transition", "apb", "opm")
+PROBES = ("attention_core", "triatt", "trimul", "transition", "apb", "opm", "trunk_glue")
 
 
 def parse_args():
@@ -371,6 +371,8 @@ def run_probe(args) -> None:
             blk.to(dev)
             sd, zd, td = s.to(dev), z.to(dev), tok.to(dev)
             fn = lambda: blk.attention(sd, zd, td)  # noqa: E731
+        elif args.probe == "trunk_glue":
+            return run_trunk_glue_probe(args, dev)
         else:
             w, m, mask = opm_workload()
             mod = b.OuterProductMean(64, 32, 128).eval()
@@ -383,6 +385,44 @@ def run_probe(args) -> None:
         ms = event_time_ms(fn, args.steps)
         status = b._lib.device_status()
     print(json.dumps({"probe": args.probe, "tokens": N, "ms_per_call": ms, "device_status": status}), flush=True)
+
+
+def run_trunk_glue_probe(args, dev) -> None:
+    """The HBM-bound glue around the trunk blocks at --tokens: pair initialisation, the recycling update and pairwise
+    conditioning, each timed alone with its algorithmic bytes (fp32 pair tensor, 512 B per pair)."""
+    import bioemu2_b200 as b
+    from bioemu2_b200 import functional as F
+
+    N = args.tokens
+    g = torch.Generator().manual_seed(6)
+    pair_bytes = N * N * 128 * 4
+    emb = b.PairMixerSequenceEmbedder(384, 128, 456, msa_blocks=0, num_blocks=0, use_unconditional_branch=True).eval().to(dev)
+    cond = b.PairwiseConditioning(128, 128).eval().to(dev)
+    s_inputs = torch.randn(1, N, 456, generator=g).to(dev)
+    z = torch.randn(1, N, N, 128, generator=g).to(dev)
+    rel = torch.randn(1, N, N, 128, generator=g).to(dev)
+    feats = {"pair_init_terms": rel}
+    a, c = torch.randn(1, N, 128, generator=g).to(dev), torch.randn(1, N, 128, generator=g).to(dev)
+    z_init = emb.initial_embeddings(s_inputs, feats)[1]
+    legs = {
+        # min_bytes: the fp32 pair tensors (N*N*512 B each) a fully fused form would have to move - inputs read once,
+        # the result written once, no intermediate.  The legs that are several kernels move more than this.
+        "pair_outer_sum": (lambda: F.pair_outer_sum(a, c, rel), 2 * pair_bytes),                      # terms in, z_init out
+        "initial_embeddings": (lambda: emb.initial_embeddings(s_inputs, feats), 2 * pair_bytes),
+        "recycle_update_z": (lambda: emb._recycle(z, z_init, emb.z_norm, "z_recycle"), 3 * pair_bytes),  # z, z_init in
+        "unconditional_branch": (lambda: emb(s_inputs, feats, unconditional=True), 4 * pair_bytes),  # + z_init round trip
+        "pairwise_conditioning": (lambda: cond(z, rel), 3 * pair_bytes),                            # z, rel in; z out
+    }
+    peak = peaks()
+    out = {"probe": "trunk_glue", "tokens": N, "hbm_peak_gbs": peak["hbm_gbs"], "legs": {}}
+    for name, (fn, nbytes) in legs.items():
+        for _ in range(args.warmup):
+            fn()
+        ms = event_time_ms(fn, args.steps)
+        gbs = nbytes / (ms * 1e-3) / 1e9
+        out["legs"][name] = {"ms": ms, "min_bytes": nbytes, "gbs": gbs, "frac_of_hbm_peak": gbs / peak["hbm_gbs"]}
+    out["device_status"] = b._lib.device_status()
+    print(json.dumps(out), flush=True)
 
 
 def parity_stats(actual: torch.Tensor, expected: torch.Tensor) -> dict:

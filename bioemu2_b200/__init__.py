@@ -3,6 +3,7 @@
 from . import _lib  # noqa: F401  (fails loudly when the library is not built)
 from . import context_parallel, functional, ieee, precision
 from .attention_pair_bias import AttentionPairBias, PairBiasCache
+from .conditioning import PairwiseConditioning
 from .outer_product_mean import (
     OuterProductMean,
     OuterProductMeanTritonMemorySaving,
@@ -11,6 +12,7 @@ from .outer_product_mean import (
 from .pairformer import PairformerBlock, PairformerModule
 from .pair_weighted_averaging import PairWeightedAveraging
 from .pairmixer import PairMixerLayer, PairMixerModule, PairMixerMSALayer
+from .sequence_trunk import PairMixerMSAModule, PairMixerSequenceEmbedder
 from .swap import swap_into, to_b200
 from .transformer import AttentionLayer, ConditionedTransformerLayer
 from .transition import Transition
@@ -42,6 +44,9 @@ __all__ = [
     "PairMixerLayer",
     "PairMixerModule",
     "PairMixerMSALayer",
+    "PairMixerMSAModule",
+    "PairMixerSequenceEmbedder",
+    "PairwiseConditioning",
     "PairWeightedAveraging",
     "swap_into",
     "to_b200",

@@ -96,6 +96,63 @@ layernorm_rows_kernel(const void* __restrict__ x, __nv_bfloat16* __restrict__ y,
   }
 }
 
+// The same for narrow rows (cols <= 8 * L, L = 8 or 16 lanes per row): a warp normalises 32 / L rows at a time, one
+// 8-channel vector per lane, so that no lane idles on the 64- and 128-channel streams (MSA and pair widths).
+template <bool F32IN, int L>
+__global__ void __launch_bounds__(256)
+layernorm_rows_narrow_kernel(const void* __restrict__ x, __nv_bfloat16* __restrict__ y, const float* __restrict__ w,
+                             const float* __restrict__ b, long long rows, int cols, float eps, int normalize, int silu) {
+  constexpr int RPW = 32 / L;
+  const int lane = threadIdx.x & 31;
+  const int sub = lane / L, l = lane % L;
+  const int nvec = cols >> 3;
+  const bool has = l < nvec;
+  const long long warp_global = (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  const long long warp_stride = (long long)gridDim.x * (blockDim.x >> 5);
+  const float inv = 1.0f / float(cols);
+  float wv[8], bv[8];
+#pragma unroll
+  for (int e = 0; e < 8; ++e) {
+    wv[e] = (w && has) ? w[l * 8 + e] : 1.0f;
+    bv[e] = (b && has) ? b[l * 8 + e] : 0.0f;
+  }
+  // every lane runs the same number of iterations: the shuffles below are warp-wide
+  for (long long rb = warp_global * RPW; rb < rows; rb += warp_stride * RPW) {
+    const long long r = rb + sub;
+    const bool act = has && r < rows;
+    float f[8];
+#pragma unroll
+    for (int e = 0; e < 8; ++e) f[e] = 0.f;
+    if (act) load8<F32IN>(static_cast<const uint8_t*>(x) + r * cols * (long long)(F32IN ? 4 : 2), l * 8, f);
+    if (normalize) {
+      float s = 0.f;
+#pragma unroll
+      for (int e = 0; e < 8; ++e) s += f[e];
+#pragma unroll
+      for (int o = L / 2; o > 0; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
+      const float mean = s * inv;
+      float ss = 0.f;
+      if (has) {
+#pragma unroll
+        for (int e = 0; e < 8; ++e) {
+          f[e] -= mean;
+          ss = fmaf(f[e], f[e], ss);
+        }
+      }
+#pragma unroll
+      for (int o = L / 2; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+      const float rstd = rsqrtf(ss * inv + eps);
+#pragma unroll
+      for (int e = 0; e < 8; ++e) f[e] = fmaf(f[e] * rstd, wv[e], bv[e]);
+      if (silu) {
+#pragma unroll
+        for (int e = 0; e < 8; ++e) f[e] *= sigmoid_fast(f[e]);
+      }
+    }
+    if (act) store8<false>(y + r * cols, l * 8, f);
+  }
+}
+
 // Pair initialisation: z[i, j, :] = a[i, :] + c[j, :] (+ extra[i, j, :]) in fp32; one thread per 8 channels,
 // cols a multiple of 8.  a and c are tiny and stay in L1/L2: the kernel is the write (and the read of extra).
 __global__ void __launch_bounds__(256)

@@ -121,6 +121,18 @@ static int launch_rows_to_bf16(const void* x, bool f32, __nv_bfloat16* y, const 
   const int64_t cap = int64_t(sm_count()) * 16;
   if (blocks > cap) blocks = cap;
   if (blocks < 1) blocks = 1;
+  if (!x2 && cols <= 128) {  // narrow rows: several rows per warp
+    const int nn = normalize, ss = silu;
+    if (cols <= 64) {
+      if (f32) layernorm_rows_narrow_kernel<true, 8><<<int(blocks), warps * 32, 0, stream>>>(x, y, w, b, rows, cols, 1e-5f, nn, ss);
+      else layernorm_rows_narrow_kernel<false, 8><<<int(blocks), warps * 32, 0, stream>>>(x, y, w, b, rows, cols, 1e-5f, nn, ss);
+    } else {
+      if (f32) layernorm_rows_narrow_kernel<true, 16><<<int(blocks), warps * 32, 0, stream>>>(x, y, w, b, rows, cols, 1e-5f, nn, ss);
+      else layernorm_rows_narrow_kernel<false, 16><<<int(blocks), warps * 32, 0, stream>>>(x, y, w, b, rows, cols, 1e-5f, nn, ss);
+    }
+    B200_AFTER_LAUNCH();
+    return 0;
+  }
   if (f32)
     layernorm_rows_kernel<true><<<int(blocks), warps * 32, 0, stream>>>(x, y, w, b, rows, cols, 1e-5f, normalize, silu,
                                                                        x2, cols1);

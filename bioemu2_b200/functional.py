@@ -132,11 +132,18 @@ def trimul(x: Tensor, mask: Tensor, w: TriMulPacked, incoming: bool, add_residua
 
 
 class TransitionPacked:
-    """Weights of a 128 -> 512 -> 128 SwiGLU transition in the layout ``b200_transition_fwd`` expects."""
+    """Weights of a 128 -> 512 -> 128 SwiGLU transition in the layout ``b200_transition_fwd`` expects.  A narrower
+    hidden layer (the 128 -> 256 -> 128 transitions of the pairwise conditioning) is zero-padded to 512: the padded
+    units contribute ``silu(0) * 0 = 0`` exactly, and one fused pass still beats four un-fused ones."""
 
     def __init__(self, norm_w, norm_b, fc1, fc2, fc3):
-        if tuple(fc1.shape) != (512, 128) or tuple(fc3.shape) != (128, 512):
-            raise ValueError("the fused pair-transition kernel is built for dim=128, hidden=512")
+        hidden = fc1.shape[0]
+        if fc1.shape[1] != 128 or tuple(fc2.shape) != tuple(fc1.shape) or tuple(fc3.shape) != (128, hidden) or hidden > 512:
+            raise ValueError("the fused pair-transition kernel is built for dim=128, hidden<=512")
+        if hidden < 512:
+            pad = torch.zeros(512 - hidden, 128, dtype=fc1.dtype, device=fc1.device)
+            fc1, fc2 = torch.cat([fc1.detach(), pad]), torch.cat([fc2.detach(), pad])
+            fc3 = torch.cat([fc3.detach(), pad.t()], dim=1)
         bf = torch.bfloat16
         w13 = torch.cat([fc1.reshape(8, 64, 128), fc2.reshape(8, 64, 128)], dim=1)  # [8][128][128]
         self.w13 = w13.reshape(1024, 128).to(bf).contiguous()

@@ -11,6 +11,7 @@ import torch.nn as nn
 from torch import Tensor
 
 from . import _lib
+from . import functional as F
 from .outer_product_mean import OuterProductMean
 from .pair_weighted_averaging import PairWeightedAveraging
 from .transition import Transition
@@ -98,7 +99,8 @@ class PairMixerMSALayer(nn.Module):
             raise RuntimeError("bioemu2_b200 modules are inference-only: call .eval()")
         m = self.pair_weighted_averaging.forward_residual(m, z, token_mask)      # a new tensor
         self.msa_transition.forward_residual_(m)
-        z = z + self.outer_product_mean(m, msa_mask).to(z.dtype)
+        upd = self.outer_product_mean(m, msa_mask)
+        z = F.add_rows(z.contiguous(), upd) if z.dtype == torch.float32 else z + upd.to(z.dtype)  # a new tensor
         mask8 = token_mask.to(torch.uint8).contiguous()
         self.tri_mul_out.forward_residual_(z, mask8)
         self.tri_mul_in.forward_residual_(z, mask8)

@@ -11,6 +11,9 @@ Recognised classes (src/bioemu2/biomoa/ops/):
 ``Transition`` (transition.py:17-91), ``AttentionPairBias`` (attention_pair_bias.py:42-225),
 ``OuterProductMeanVanilla / TritonMemorySaving`` (outer_product_mean.py:32-152),
 ``PairWeightedAveraging`` (pair_weighted_averaging.py:6-153).
+Three of the reference's composite modules are swapped as a whole, glue included (src/bioemu2/biomoa/modules/):
+``PairwiseConditioning`` (diffusion.py:464-534), ``PairMixerMSAModule`` (pairmixer.py:459-612) and
+``PairMixerSequenceEmbedder`` (pairmixer.py:23-299; its feature encoders are moved across unchanged).
 A module whose sizes the kernels are not built for (for example a triangle multiplication of width 64) is left in
 place and reported, unless ``strict=True``.
 """
@@ -19,19 +22,34 @@ from __future__ import annotations
 import torch.nn as nn
 
 from .attention_pair_bias import AttentionPairBias
+from .conditioning import PairwiseConditioning
 from .outer_product_mean import OuterProductMean
 from .pair_weighted_averaging import PairWeightedAveraging
+from .sequence_trunk import PairMixerMSAModule, PairMixerSequenceEmbedder
 from .transition import Transition
 from .triangle_multiplication import TriangleMultiplication
 
 _TRIMUL = {"TriangleMultiplicationFull", "TriangleMultiplicationCueq", "TriangleMultiplicationCueqTiled",
            "TriangleMultiplicationOutgoing", "TriangleMultiplicationIncoming"}
 _OPM = {"OuterProductMeanVanilla", "OuterProductMeanTritonMemorySaving"}
-_OWN = (TriangleMultiplication, Transition, AttentionPairBias, OuterProductMean, PairWeightedAveraging)
+_COMPOSITE = {"PairwiseConditioning", "PairMixerMSAModule", "PairMixerSequenceEmbedder"}
+_ENCODERS = ("rel_pos", "token_bonds", "contact_conditioning", "method_conditioning")
+_OWN = (TriangleMultiplication, Transition, AttentionPairBias, OuterProductMean, PairWeightedAveraging,
+        PairwiseConditioning, PairMixerMSAModule, PairMixerSequenceEmbedder)
 
 
 def _is_reference_op(m: nn.Module) -> bool:
-    return type(m).__module__.startswith("bioemu2.biomoa.ops") and not isinstance(m, _OWN)
+    mod = type(m).__module__
+    if isinstance(m, _OWN):
+        return False
+    return mod.startswith("bioemu2.biomoa.ops") or (mod.startswith("bioemu2.biomoa.modules") and
+                                                     type(m).__name__ in _COMPOSITE)
+
+
+def _msa_module_args(ref: nn.Module) -> dict:
+    paired = bool(ref.use_paired_feature)
+    return dict(msa_s=ref.s_proj.out_features, s_input_dim=ref.s_proj.in_features, msa_blocks=len(ref.layers),
+                use_paired_feature=paired, num_tokens=ref.msa_proj.in_features - 2 - int(paired))
 
 
 def to_b200(ref: nn.Module) -> nn.Module:
@@ -55,6 +73,28 @@ def to_b200(ref: nn.Module) -> nn.Module:
     elif name in _OPM:
         new = OuterProductMean(ref.norm.normalized_shape[0], ref.c_hidden, ref.proj_o.out_features,
                                tile_size=getattr(ref, "tile_size", None))
+    elif name == "PairwiseConditioning":
+        ln, lin = ref.dim_pairwise_init_proj[0], ref.dim_pairwise_init_proj[1]
+        t0 = ref.transitions[0] if len(ref.transitions) else None
+        a_z = lin.out_features
+        token_z = getattr(ref, "token_z", a_z)
+        new = PairwiseConditioning(token_z, ln.normalized_shape[0] - token_z, a_z, num_transitions=len(ref.transitions),
+                                   transition_expansion_factor=(t0.fc1.out_features // a_z) if t0 is not None else 2)
+    elif name == "PairMixerMSAModule":
+        a = _msa_module_args(ref)
+        new = PairMixerMSAModule(token_s=getattr(ref, "token_s", 384), token_z=ref.layers[0].tri_mul_out.norm_in.normalized_shape[0],
+                                 **a)
+    elif name == "PairMixerSequenceEmbedder":
+        a = _msa_module_args(ref.msa_module)
+        new = PairMixerSequenceEmbedder(
+            token_s=ref.s_init.out_features, token_z=ref.z_init_1.out_features, s_input_dim=ref.s_init.in_features,
+            msa_s=a["msa_s"], msa_blocks=a["msa_blocks"], num_blocks=len(ref.pairmixer_module.layers),
+            use_contact_conditioning=ref.use_contact_conditioning, use_method_conditioning=ref.use_method_conditioning,
+            use_paired_feature=a["use_paired_feature"], use_unconditional_branch=ref.use_unconditional_branch,
+            num_tokens=a["num_tokens"])
+        for enc in _ENCODERS:  # input featurisation stays the reference's own modules
+            if isinstance(getattr(ref, enc, None), nn.Module):
+                setattr(new, enc, getattr(ref, enc))
     else:
         return ref
     new.load_state_dict(ref.state_dict(), strict=True)
@@ -72,7 +112,8 @@ def swap_into(model: nn.Module, strict: bool = False) -> dict[str, tuple[str, st
     def walk(parent: nn.Module, prefix: str) -> None:
         for name, child in list(parent.named_children()):
             path = f"{prefix}.{name}" if prefix else name
-            if _is_reference_op(child) and (type(child).__name__ in _TRIMUL | _OPM | {"Transition", "AttentionPairBias", "PairWeightedAveraging"}):
+            if _is_reference_op(child) and (type(child).__name__ in _TRIMUL | _OPM | _COMPOSITE | {
+                    "Transition", "AttentionPairBias", "PairWeightedAveraging"}):
                 try:
                     twin = to_b200(child)
                 except ValueError as exc:

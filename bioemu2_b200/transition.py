@@ -2,7 +2,7 @@
 
 ``fc3(silu(fc1(norm(x))) * fc2(norm(x)))``.  ``chunk_size`` exists in the reference to bound the
 memory of the hidden activations; the fused kernel never materialises them, so it is accepted and
-ignored.  The pair transition (dim 128, hidden 512) runs as one fused kernel; other widths (the single
+ignored.  The pair transition (dim 128, hidden up to 512) runs as one fused kernel; other widths (the single
 track: 384 -> 1536, 768 -> 4*768) run as LayerNorm, two tcgen05 GEMMs and a SwiGLU kernel.
 """
 from __future__ import annotations
@@ -28,7 +28,7 @@ class Transition(PackedWeightsMixin, nn.Module):
         self.fc2 = nn.Linear(dim, hidden, bias=False)
         self.fc3 = nn.Linear(hidden, out_dim, bias=False)
         self.hidden = hidden
-        self._fused = (dim, hidden, out_dim) == (128, 512, 128)
+        self._fused = (dim, out_dim) == (128, 128) and hidden <= 512 and hidden % 8 == 0
         if not self._fused and (dim % 8 or hidden % 8 or out_dim % 8 or dim > 1024):
             raise ValueError("bioemu2_b200.Transition needs widths that are multiples of 8 and dim <= 1024")
 

@@ -84,3 +84,43 @@ def test_context_parallel_wrappers_adopt_reference_layers():
     _same_state(ops.adopt_opm(ref_opm), ref_opm.state_dict())
     with pytest.raises(ValueError, match="Invalid direction"):
         ops._mode_of("sideways")
+
+
+def test_swap_takes_the_composite_modules_whole():
+    """``PairwiseConditioning`` and ``PairMixerSequenceEmbedder`` (with its MSA module) are replaced glue and all; the
+    embedder's feature encoders move across as the reference's own objects and the state dict is unchanged."""
+    import bioemu2_b200 as b
+
+    reference_shim.install()
+    from bioemu2.biomoa.modules.diffusion import PairwiseConditioning
+    from bioemu2.biomoa.modules.pairmixer import PairMixerSequenceEmbedder
+
+    torch.manual_seed(2)
+
+    class Model(nn.Module):
+        def __init__(self):
+            super().__init__()
+            self.embedder = PairMixerSequenceEmbedder(
+                token_s=384, token_z=128, s_input_dim=100, msa_s=64, msa_blocks=2, num_blocks=2, trimul_variant="full",
+                opm_variant="vanilla", use_contact_conditioning=False, use_method_conditioning=False,
+                use_paired_feature=True, use_unconditional_branch=True)
+            self.cond = PairwiseConditioning(token_z=128, dim_token_rel_pos_feats=128)
+
+    model = Model().eval()
+    before = {k: v.clone() for k, v in model.state_dict().items()}
+    rel_pos, token_bonds = model.embedder.rel_pos, model.embedder.token_bonds
+    report = b.swap_into(model)
+    assert report["embedder"] == ("PairMixerSequenceEmbedder", "PairMixerSequenceEmbedder")
+    assert report["cond"] == ("PairwiseConditioning", "PairwiseConditioning")
+    e, c = model.embedder, model.cond
+    assert isinstance(e, b.PairMixerSequenceEmbedder) and isinstance(e.msa_module, b.PairMixerMSAModule)
+    assert e.rel_pos is rel_pos and e.token_bonds is token_bonds
+    assert (e.token_s, e.token_z, e.s_input_dim, e.use_unconditional_branch) == (384, 128, 100, True)
+    assert len(e.msa_module.layers) == 2 and len(e.pairmixer_module.layers) == 2 and e.msa_module.use_paired_feature
+    assert isinstance(e.msa_module.layers[0].pair_weighted_averaging, b.PairWeightedAveraging)
+    assert isinstance(c, b.PairwiseConditioning) and (c.token_z, c.dim_token_rel_pos_feats, c.a_z) == (128, 128, 128)
+    assert len(c.transitions) == 2 and c.transitions[0].hidden == 256
+    sd = model.state_dict()
+    assert sorted(sd) == sorted(before)
+    for k in before:
+        assert torch.equal(sd[k], before[k]), k
