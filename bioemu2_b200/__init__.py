@@ -2,7 +2,7 @@
 ``nn.Module`` contracts.  Importing the package loads the CUDA library; without it the import fails."""
 from . import _lib  # noqa: F401  (fails loudly when the library is not built)
 from . import context_parallel, functional, ieee, precision
-from .attention_pair_bias import AttentionPairBias, PairBiasCache
+from .attention_pair_bias import AttentionPairBias, AttentionPairBiasSlidingWindow, PairBiasCache
 from .conditioning import PairwiseConditioning
 from .outer_product_mean import (
     OuterProductMean,
@@ -33,6 +33,7 @@ __all__ = [
     "ieee",
     "precision",
     "AttentionPairBias",
+    "AttentionPairBiasSlidingWindow",
     "PairBiasCache",
     "OuterProductMean",
     "OuterProductMeanTritonMemorySaving",

@@ -76,6 +76,39 @@ class AttentionPairBias(PackedWeightsMixin, nn.Module):
         return F.attention_pair_bias(s, z, mask, self.packed(), multiplicity)
 
 
+class AttentionPairBiasSlidingWindow(AttentionPairBias):
+    """Sliding-window attention with pair bias of the atom transformer, reference contract of
+    ``AttentionPairBiasSlidingWindow`` (src/bioemu2/biomoa/ops/attention_pair_bias.py:228-340): every window of
+    ``window_queries`` atoms attends to the ``window_keys`` atoms centred on it, the pair bias is
+    ``[B, heads, NW, W, H_keys]`` and shared by the ``multiplicity`` samples of a batch item.
+
+    ``forward(s[B*M*NW, W, c_s], z[B, NW, W, H_keys, c_z], mask[B*NW, W], multiplicity)``.  The projections run on the
+    tensor cores in bf16; scores, softmax and the weighted sum are fp32.
+    """
+
+    def __init__(self, c_s: int, c_z: int, num_heads: int, window_queries: int = 32, window_keys: int = 128,
+                 inf: float = 1e6, initial_norm: bool = True, tile_size: int | None = 512,
+                 zero_init_output: bool = False, use_bias_in_layer_norm: bool = False) -> None:
+        super().__init__(c_s, c_z, num_heads, inf=inf, initial_norm=initial_norm, tile_size=tile_size,
+                         zero_init_output=zero_init_output, use_bias_in_layer_norm=use_bias_in_layer_norm)
+        if (window_keys - window_queries) % 2 or window_keys % 8 or window_keys < window_queries:
+            raise ValueError("window_keys must be a multiple of 8, at least window_queries, with an even difference")
+        self.window_queries, self.window_keys = window_queries, window_keys
+
+    def _build_packed(self):
+        return F.WindowApbPacked(
+            self.c_s, self.c_z, self.num_heads, self.proj_qkv.weight, self.proj_q_bias, self.proj_g.weight,
+            self.norm_z.weight, self.norm_z.bias, self.proj_z.weight, self.proj_o.weight,
+            self.norm_s.weight if self.initial_norm else None, self.norm_s.bias if self.initial_norm else None)
+
+    def forward(self, s: Tensor, z: Tensor, mask: Tensor, multiplicity: int = 1) -> Tensor:
+        assert s.ndim == 3 and z.ndim == 5 and mask.ndim == 2, f"{s.shape}, {z.shape}, {mask.shape}"
+        if s.shape[1] != self.window_queries or z.shape[3] != self.window_keys:
+            raise ValueError(f"expected windows of {self.window_queries} queries and {self.window_keys} keys, got "
+                             f"s {tuple(s.shape)}, z {tuple(z.shape)}")
+        return F.window_attention_pair_bias(s, z, mask, self.packed(), multiplicity)
+
+
 class PairBiasCache:
     """The pair biases ``proj_z(norm_z(z))`` of a stack of ``AttentionPairBias`` modules, computed in ONE pass over a
     pair tensor that stays the same for many calls.

@@ -7,6 +7,7 @@ The reference wraps a loaded serial module for 2D context parallelism by passing
     AttentionPairBias(attention, dist_manager)                            src/bioemu2/context_parallel/ops/attention.py:45-72
     DistributedOuterProductMean(serial, device_mesh, comm)                src/bioemu2/context_parallel/ops/outer_product_mean.py:199-210
     DTensorAwareTransition(serial, device_mesh)                           src/bioemu2/context_parallel/ops/transition.py:19-27
+    LayerNormLinearParamsReplicatedTiled(serial, device_mesh)             src/bioemu2/context_parallel/ops/tiled_params_replicated.py:36-81
 
 The classes here take the same arguments, so the reference's wrapping code (``_distributed_trimul`` and the
 ``Distributed*`` module constructors) keeps working when it imports them from this package instead.  The serial
@@ -118,5 +119,75 @@ class DTensorAwareTransition(CPTransition):
         self.device_mesh = device_mesh
 
 
+def _rewrap(out, like, width: int):
+    """``out`` as a DTensor placed like ``like`` (global shape with ``width`` channels), or ``out`` itself."""
+    if not hasattr(like, "to_local"):
+        return out
+    import torch
+    from torch.distributed.tensor import DTensor
+
+    shape = torch.Size((*like.shape[:-1], width))
+    stride, acc = [], 1
+    for n in reversed(shape):
+        stride.append(acc)
+        acc *= n
+    return DTensor.from_local(out, like.device_mesh, like.placements, run_check=False, shape=shape,
+                              stride=tuple(reversed(stride)))
+
+
+class LayerNormLinearParamsReplicatedTiled(nn.Module):
+    """``Linear(LayerNorm(cat(*pairs, -1)))`` on the local blocks of one or two pair tensors, no communication and no
+    materialised concatenation (src/bioemu2/context_parallel/ops/tiled_params_replicated.py:36-81; the row tiling
+    there bounds the intermediates, which do not exist here).  ``serial`` is the ``nn.Sequential(LayerNorm, Linear)``
+    of the serial model; its parameters are shared, and sub-module keys ``0`` / ``1`` are kept."""
+
+    def __init__(self, serial: nn.Sequential, device_mesh=None) -> None:
+        super().__init__()
+        norm, linear = serial
+        if linear.bias is not None:
+            raise ValueError("the projection is expected to be bias-free (LinearNoBias)")
+        self.add_module("0", norm)
+        self.add_module("1", linear)
+        self.device_mesh = device_mesh
+        self._w = None
+        self._version = -1
+
+    def forward(self, *pairs):
+        import torch
+
+        from .. import functional as F
+
+        if torch.is_grad_enabled():
+            raise RuntimeError(f"{type(self).__name__} is forward-only; use torch.no_grad().")
+        if not 1 <= len(pairs) <= 2:
+            raise ValueError("one or two pair tensors are supported")
+        norm, linear = getattr(self, "0"), getattr(self, "1")
+        p = linear.weight
+        if self._w is None or self._version != p._version or self._w.device != p.device:
+            self._w, self._version = p.detach().to(torch.bfloat16).contiguous(), p._version
+        loc = [x.to_local() if hasattr(x, "to_local") else x for x in pairs]
+        zn = (F.rows_to_bf16(loc[0], norm.weight, norm.bias) if len(loc) == 1
+              else F.rows2_to_bf16(loc[0], loc[1].to(loc[0].dtype), norm.weight, norm.bias))
+        out = F.linear_bf16(zn, self._w, out_dtype=loc[0].dtype)
+        return _rewrap(out, pairs[0], p.shape[0])
+
+
+class DistributedPairwiseConditioning(nn.Module):
+    """``PairwiseConditioning`` on the local blocks of ``z_trunk`` and ``token_rel_pos_feats`` (every pair is
+    independent: no communication); DTensors in, a DTensor with the first input's placements out."""
+
+    def __init__(self, serial: nn.Module, device_mesh=None) -> None:
+        super().__init__()
+        from ..conditioning import PairwiseConditioning
+        from ..swap import to_b200
+
+        self.serial = serial if isinstance(serial, PairwiseConditioning) else to_b200(serial)
+        self.device_mesh = device_mesh
+
+    def forward(self, z_trunk, token_rel_pos_feats):
+        loc = [x.to_local() if hasattr(x, "to_local") else x for x in (z_trunk, token_rel_pos_feats)]
+        return _rewrap(self.serial(loc[0], loc[1]), z_trunk, self.serial.a_z)
+
+
 __all__ = ["grid_of", "TriangleMultiplicationAddRes", "AttentionPairBias", "DistributedOuterProductMean",
-           "DTensorAwareTransition"]
+           "DTensorAwareTransition", "LayerNormLinearParamsReplicatedTiled", "DistributedPairwiseConditioning"]

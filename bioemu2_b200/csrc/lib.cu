@@ -14,12 +14,22 @@
 #include "attention.cuh"
 #include "pair_bias.cuh"
 #include "triatt.cuh"
+#include "window_attention.cuh"
 
 namespace b200 {
 
 template <class Kernel>
 static int set_smem(Kernel k, uint32_t bytes) {
   return set_smem_once(reinterpret_cast<const void*>(k), bytes);
+}
+
+template <int DH>
+static int launch_window_attention(const WindowAttnParams& p, int BM, cudaStream_t st) {
+  const uint32_t smem = uint32_t(2u * p.Hk * p.heads * DH * 2u + p.Hk + 16);
+  if (int e = set_smem(window_attention_kernel<DH>, smem)) return e;
+  window_attention_kernel<DH><<<BM * p.NW, p.heads * p.W, smem, st>>>(p);
+  B200_AFTER_LAUNCH();
+  return B200_OK;
 }
 
 struct BmmLaunch {
@@ -1226,6 +1236,43 @@ int b200_rows2_to_bf16(const void* x1, int cols1, const void* x2, int cols2, voi
   if (rows == 0) return B200_OK;
   return launch_rows_to_bf16(x1, x_dtype == B200_DTYPE_F32, static_cast<__nv_bfloat16*>(y), w, b, rows, cols1 + cols2,
                              normalize != 0, static_cast<cudaStream_t>(stream), false, x2, cols1);
+}
+
+int b200_window_bias_fwd(const void* z, const float* ln_w, const float* ln_b, const float* w_z, float* bias,
+                         int64_t windows, int W, int Hk, int c_z, int heads, int z_dtype, b200_stream_t stream) {
+  if (int e = b200_check_device()) return e;
+  B200_CHECK_ARG(z && ln_w && w_z && bias, "z/ln_w/w_z/bias is NULL");
+  B200_CHECK_ARG(windows >= 0 && W > 0 && Hk > 0 && c_z > 0, "need windows >= 0 and W, Hk, c_z > 0");
+  B200_CHECK_ARG(heads > 0 && heads <= kWindowMaxHeads, "heads=%d must be in 1..%d", heads, kWindowMaxHeads);
+  B200_CHECK_ARG((z_dtype | 1) == 1, "unknown dtype");
+  if (windows == 0) return B200_OK;
+  WindowBiasParams p{z, ln_w, ln_b, w_z, bias, windows * W * Hk, W * Hk, c_z, heads, 1e-5f};
+  const int grid = grid_for(p.pairs, 256);
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  if (z_dtype == B200_DTYPE_F32) window_bias_kernel<true><<<grid, 256, 0, st>>>(p);
+  else window_bias_kernel<false><<<grid, 256, 0, st>>>(p);
+  B200_AFTER_LAUNCH();
+  return B200_OK;
+}
+
+int b200_window_attention_fwd(const void* qkv, const void* gate, const float* bias, const uint8_t* mask, void* out, int B,
+                              int M, int NW, int W, int Hk, int heads, int head_dim, b200_stream_t stream) {
+  if (int e = b200_check_device()) return e;
+  B200_CHECK_ARG(qkv && gate && bias && mask && out, "qkv/gate/bias/mask/out is NULL");
+  B200_CHECK_ARG(B > 0 && M > 0 && NW > 0 && W > 0 && Hk >= W && Hk % 8 == 0 && (Hk - W) % 2 == 0,
+                 "need B, M, NW, W > 0 and Hk >= W, a multiple of 8, with Hk - W even (W=%d, Hk=%d)", W, Hk);
+  B200_CHECK_ARG(heads > 0 && heads * W <= 256, "heads * W = %d exceeds the 256 threads of a window's CTA", heads * W);
+  B200_CHECK_ARG(head_dim == 16 || head_dim == 32 || head_dim == 64, "head_dim=%d must be 16, 32 or 64", head_dim);
+  B200_CHECK_ARG(2ll * Hk * heads * head_dim * 2 + Hk + 16 <= 227 * 1024, "the key window does not fit in shared memory");
+  B200_CHECK_ARG((int64_t)B * M * NW < (int64_t(1) << 31), "too many windows");
+  B200_CHECK_ARG(aligned(qkv, 16) && aligned(gate, 16) && aligned(out, 16) && aligned(bias, 16),
+                 "qkv/gate/out/bias must be 16-byte aligned");
+  WindowAttnParams p{static_cast<const __nv_bfloat16*>(qkv), static_cast<const __nv_bfloat16*>(gate), bias, mask,
+                     static_cast<__nv_bfloat16*>(out), NW, W, Hk, heads, M, 1.0f / sqrtf(float(head_dim))};
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  if (head_dim == 16) return launch_window_attention<16>(p, B * M, st);
+  if (head_dim == 32) return launch_window_attention<32>(p, B * M, st);
+  return launch_window_attention<64>(p, B * M, st);
 }
 
 int b200_pair_outer_sum(const float* a, const float* c, const float* extra, float* z, int n_i, int n_j, int cols,

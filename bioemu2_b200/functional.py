@@ -416,6 +416,52 @@ def add_rows(x: Tensor, y: Tensor, out: Tensor | None = None) -> Tensor:
     return out
 
 
+class WindowApbPacked:
+    """Weights of the sliding-window attention: ``proj_qkv`` with ``proj_q_bias`` folded into a GEMM bias on the q
+    columns, gate and output projections in bf16, the tiny pair-bias projection in fp32."""
+
+    def __init__(self, c_s, c_z, heads, proj_qkv, proj_q_bias, proj_g, norm_z_w, norm_z_b, proj_z, proj_o, norm_s_w, norm_s_b):
+        bf = torch.bfloat16
+        dh = c_s // heads
+        if dh not in (16, 32, 64) or heads > 16:
+            raise ValueError(f"the sliding-window kernel serves head dims 16, 32, 64 and up to 16 heads, got {dh} x {heads}")
+        self.c_s, self.c_z, self.H, self.dh = c_s, c_z, heads, dh
+        self.w_qkv = proj_qkv.detach().to(bf).contiguous()
+        b = torch.zeros(3 * c_s, dtype=torch.float32, device=proj_qkv.device)
+        b[:c_s] = proj_q_bias.detach().float()
+        self.b_qkv = b
+        self.w_g = proj_g.detach().to(bf).contiguous()
+        self.w_o = proj_o.detach().to(bf).contiguous()
+        self.w_z = proj_z.detach().float().contiguous()
+        self.ln_z_w = norm_z_w.detach().float().contiguous()
+        self.ln_z_b = norm_z_b.detach().float().contiguous() if norm_z_b is not None else None
+        self.ln_s_w = norm_s_w.detach().float().contiguous() if norm_s_w is not None else None
+        self.ln_s_b = norm_s_b.detach().float().contiguous() if norm_s_b is not None else None
+
+
+def window_attention_pair_bias(s: Tensor, z: Tensor, mask: Tensor, w: WindowApbPacked, multiplicity: int = 1) -> Tensor:
+    """Sliding-window attention with pair bias: ``s[B*M*NW, W, c_s]``, ``z[B, NW, W, Hk, c_z]``, ``mask[B*NW, W]``."""
+    _require_cuda(s, z, mask)
+    folded, W, c_s = s.shape
+    B, NW, Wz, Hk, c_z = z.shape
+    M = multiplicity
+    if Wz != W or folded != B * M * NW or tuple(mask.shape) != (B * NW, W) or c_s != w.c_s or c_z != w.c_z:
+        raise ValueError(f"inconsistent shapes: s {tuple(s.shape)}, z {tuple(z.shape)}, mask {tuple(mask.shape)}, "
+                         f"multiplicity {M}")
+    sn = rows_to_bf16(s, w.ln_s_w, w.ln_s_b, normalize=w.ln_s_w is not None)
+    qkv = linear_bf16(sn, w.w_qkv, bias_f32=w.b_qkv)
+    gate = linear_bf16(sn, w.w_g)
+    z = z.contiguous()
+    bias = torch.empty(B, NW, w.H, W, Hk, dtype=torch.float32, device=s.device)
+    _lib.check(lib.b200_window_bias_fwd(z.data_ptr(), w.ln_z_w.data_ptr(), _ptr(w.ln_z_b), w.w_z.data_ptr(), bias.data_ptr(),
+                                        B * NW, W, Hk, c_z, w.H, _zdtype(z), _stream()))
+    og = torch.empty(folded, W, c_s, dtype=torch.bfloat16, device=s.device)
+    m8 = mask_u8(mask).contiguous()
+    _lib.check(lib.b200_window_attention_fwd(qkv.data_ptr(), gate.data_ptr(), bias.data_ptr(), m8.data_ptr(), og.data_ptr(),
+                                             B, M, NW, W, Hk, w.H, w.dh, _stream()))
+    return linear_bf16(og, w.w_o, out_dtype=s.dtype)
+
+
 def swiglu(h12: Tensor) -> Tensor:
     """``silu(h12[..., :H]) * h12[..., H:]`` for bf16 ``h12[..., 2H]``."""
     H = h12.shape[-1] // 2

@@ -9,6 +9,7 @@ package is never imported here), builds the twin with the same constructor attri
 Recognised classes (src/bioemu2/biomoa/ops/):
 ``TriangleMultiplicationFull / Cueq / CueqTiled / Outgoing / Incoming`` (triangle_multiplication.py:86-395),
 ``Transition`` (transition.py:17-91), ``AttentionPairBias`` (attention_pair_bias.py:42-225),
+``AttentionPairBiasSlidingWindow`` (attention_pair_bias.py:228-340),
 ``OuterProductMeanVanilla / TritonMemorySaving`` (outer_product_mean.py:32-152),
 ``PairWeightedAveraging`` (pair_weighted_averaging.py:6-153).
 Three of the reference's composite modules are swapped as a whole, glue included (src/bioemu2/biomoa/modules/):
@@ -21,7 +22,7 @@ from __future__ import annotations
 
 import torch.nn as nn
 
-from .attention_pair_bias import AttentionPairBias
+from .attention_pair_bias import AttentionPairBias, AttentionPairBiasSlidingWindow
 from .conditioning import PairwiseConditioning
 from .outer_product_mean import OuterProductMean
 from .pair_weighted_averaging import PairWeightedAveraging
@@ -67,6 +68,11 @@ def to_b200(ref: nn.Module) -> nn.Module:
         new = AttentionPairBias(ref.proj_g.in_features, ref.proj_z.in_features, ref.num_heads, inf=ref.inf,
                                 initial_norm=ref.initial_norm, tile_size=getattr(ref, "tile_size", 512),
                                 use_bias_in_layer_norm=ref.norm_z.bias is not None)
+    elif name == "AttentionPairBiasSlidingWindow":
+        new = AttentionPairBiasSlidingWindow(ref.proj_g.in_features, ref.proj_z.in_features, ref.num_heads,
+                                             window_queries=ref.window_queries, window_keys=ref.window_keys, inf=ref.inf,
+                                             initial_norm=ref.initial_norm, tile_size=getattr(ref, "tile_size", 512),
+                                             use_bias_in_layer_norm=ref.norm_z.bias is not None)
     elif name == "PairWeightedAveraging":
         new = PairWeightedAveraging(ref.c_m, ref.c_z, ref.c_h, ref.num_heads, inf=ref.inf,
                                     use_bias_in_layer_norm=ref.norm_z.bias is not None)
@@ -113,7 +119,7 @@ def swap_into(model: nn.Module, strict: bool = False) -> dict[str, tuple[str, st
         for name, child in list(parent.named_children()):
             path = f"{prefix}.{name}" if prefix else name
             if _is_reference_op(child) and (type(child).__name__ in _TRIMUL | _OPM | _COMPOSITE | {
-                    "Transition", "AttentionPairBias", "PairWeightedAveraging"}):
+                    "Transition", "AttentionPairBias", "AttentionPairBiasSlidingWindow", "PairWeightedAveraging"}):
                 try:
                     twin = to_b200(child)
                 except ValueError as exc:

@@ -403,6 +403,24 @@ int b200_rows2_to_bf16(const void* x1, int cols1, const void* x2, int cols2, voi
                        int64_t rows, int x_dtype, int normalize, b200_stream_t stream);
 
 /* ---------------------------------------------------------------------------------------------------
+ * Sliding-window attention with pair bias for the atom transformer, AttentionPairBiasSlidingWindow.forward
+ * (src/bioemu2/biomoa/ops/attention_pair_bias.py:283-340): a query window of W atoms attends to the Hk keys centred
+ * on it; keys beyond the ends of the sequence are zero rows and masked.  The projections around the core are
+ * b200_rows_to_bf16 (norm_s) and b200_linear_bf16 (proj_qkv with proj_q_bias on the q columns, proj_g, proj_o).
+ *
+ * b200_window_bias_fwd       bias[win][h][i][j] = proj_z(norm_z(z[win][i][j][:]))[h] (:314), fp32; z fp32 or bf16
+ *                            [windows][W][Hk][c_z], w_z fp32 [heads][c_z], ln_b may be NULL.
+ * b200_window_attention_fwd  out = sigmoid(gate) * softmax_j(q.k_j / sqrt(d) + bias, masked keys REPLACED by -1e6) v
+ *                            (:320-337) in fp32 arithmetic.  qkv bf16 [B*M][NW*W][3*heads*d] (q | k | v), gate / out
+ *                            bf16 [B*M][NW*W][heads*d], bias fp32 [B][NW][heads][W][Hk] shared by the M samples of a
+ *                            batch item, mask one byte per atom [B][NW*W].  d is 16, 32 or 64.
+ * ------------------------------------------------------------------------------------------------- */
+int b200_window_bias_fwd(const void* z, const float* ln_w, const float* ln_b, const float* w_z, float* bias,
+                         int64_t windows, int W, int Hk, int c_z, int heads, int z_dtype, b200_stream_t stream);
+int b200_window_attention_fwd(const void* qkv, const void* gate, const float* bias, const uint8_t* mask, void* out, int B,
+                              int M, int NW, int W, int Hk, int heads, int head_dim, b200_stream_t stream);
+
+/* ---------------------------------------------------------------------------------------------------
  * Pair-weighted averaging, PairWeightedAveraging.forward (src/bioemu2/biomoa/ops/pair_weighted_averaging.py:121-153),
  * is assembled from b200_rows_to_bf16 (norm_m), b200_linear_bf16 (proj_g, proj_o), b200_pair_bias_fwd (proj_z(norm_z(z))),
  * b200_bmm_nt (proj_m written transposed per head; the weighted average itself) and the two kernels below.

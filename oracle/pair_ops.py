@@ -115,6 +115,35 @@ def attention_pair_bias(
     return linear(g * o, w["proj_o.weight"])
 
 
+def attention_pair_bias_sliding_window(s: Tensor, z: Tensor, mask: Tensor, w: dict, num_heads: int,
+                                       multiplicity: int = 1, inf: float = 1e6) -> Tensor:
+    """``AttentionPairBiasSlidingWindow.forward``: src/bioemu2/biomoa/ops/attention_pair_bias.py:283-340.
+
+    ``s[B*M*NW, W, c_s]`` (windows of W query atoms), ``z[B, NW, W, H, c_z]``, ``mask[B*NW, W]``.  Window ``n`` sees the
+    ``H`` keys ``n*W - (H-W)/2 ...`` of its own sample; keys beyond the sequence are zero rows (the projections are
+    bias-free) and count as masked (:303-318).  Masked logits are replaced by ``-inf`` after the bias is added (:331-332).
+    """
+    B, NW, W, H = z.shape[:4]
+    folded, _, c_s = s.shape
+    BM, M, dh, ctx = folded // NW, multiplicity, c_s // num_heads, (H - W) // 2
+    if "norm_s.weight" in w:
+        s = layer_norm(s, w["norm_s.weight"], w["norm_s.bias"])
+    qkv = linear(s, w["proj_qkv.weight"])
+    q = (qkv[..., :c_s] + w["proj_q_bias"]).view(folded, W, num_heads, dh)
+    g = torch.sigmoid(linear(s, w["proj_g.weight"]))
+    key_rows = torch.arange(NW)[:, None] * W + torch.arange(H)[None, :]          # rows of the padded sequence, [NW, H]
+    kv = torch.nn.functional.pad(qkv[..., c_s:].reshape(BM, NW * W, 2 * c_s), (0, 0, ctx, ctx))[:, key_rows]
+    k, v = kv.reshape(folded, H, 2, num_heads, dh).unbind(dim=2)
+    mask_keys = torch.nn.functional.pad(mask.bool().reshape(B, NW * W), (ctx, ctx))[:, key_rows]   # [B, NW, H]
+    zb = linear(layer_norm(z, w["norm_z.weight"], w.get("norm_z.bias")), w["proj_z.weight"]).permute(0, 1, 4, 2, 3)
+    attn = torch.einsum("bihd,bjhd->bhij", q, k) / math.sqrt(dh)               # [folded, heads, W, H]
+    attn = attn.view(B, M, NW, num_heads, W, H) + zb[:, None]
+    attn = attn.masked_fill(~mask_keys[:, None, :, None, None, :], -inf)
+    attn = attn.softmax(dim=-1).view(folded, num_heads, W, H)
+    o = torch.einsum("bhij,bjhd->bihd", attn, v).reshape(folded, W, c_s)
+    return linear(g * o, w["proj_o.weight"])
+
+
 def outer_product_mean(m: Tensor, mask: Tensor, w: dict, i_chunk: int | None = None) -> Tensor:
     """``OuterProductMeanVanilla.forward``.
 

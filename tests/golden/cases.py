@@ -170,6 +170,18 @@ def sequence_trunk_case(seed: int = 26, S: int = 8, N: int = 24, s_input_dim: in
                 recycles=1, msa_blocks=1, num_blocks=1, unconditional=unconditional)
 
 
+def window_apb_case(seed: int = 28, B: int = 1, M: int = 2, NW: int = 3, W: int = 32, Hk: int = 128, c_s: int = 128,
+                    c_z: int = 16, heads: int = 4, n_pad: int = 9):
+    g = _gen(seed)
+    w = H.apb_weights(g, c_s, c_z, heads, True)
+    s = torch.randn(B * M * NW, W, c_s, generator=g)
+    z = torch.randn(B, NW, W, Hk, c_z, generator=g)
+    mask = torch.ones(B, NW * W, dtype=torch.bool)
+    mask[:, NW * W - n_pad:] = False
+    mask[0, 40] = False
+    return dict(kind="window_apb", w=w, s=s, z=z, mask=mask.reshape(B * NW, W), heads=heads, M=M, W=W, Hk=Hk)
+
+
 CASES = {
     "trimul_outgoing": lambda: trimul_case("outgoing"),
     "trimul_incoming": lambda: trimul_case("incoming", seed=21),
@@ -188,6 +200,8 @@ CASES = {
     "msa_module": lambda: msa_module_case(),
     "sequence_trunk": lambda: sequence_trunk_case(),
     "sequence_trunk_unconditional": lambda: sequence_trunk_case(seed=27, unconditional=True),
+    "window_apb": lambda: window_apb_case(),
+    "window_apb_batch2": lambda: window_apb_case(seed=29, B=2, M=1, NW=2, n_pad=40),
 }
 
 

@@ -116,6 +116,13 @@ def run_reference(case: dict) -> torch.Tensor:
             feats = dict(case["feats"], asym_id=None, entity_id=None, residue_index=None, sym_id=None, token_bonds=None)
             s, z = mod(case["s_inputs"], feats, num_steps_recycle=case["recycles"], unconditional=case["unconditional"])
             return torch.cat([z.flatten(), s.flatten()])   # pair tensor first, then the single representation
+        if kind == "window_apb":
+            from bioemu2.biomoa.ops.attention_pair_bias import AttentionPairBiasSlidingWindow
+
+            mod = AttentionPairBiasSlidingWindow(case["s"].shape[-1], case["z"].shape[-1], case["heads"],
+                                                 window_queries=case["W"], window_keys=case["Hk"]).eval()
+            mod.load_state_dict(w, strict=True)
+            return mod(case["s"], case["z"], case["mask"], multiplicity=case["M"])
     raise KeyError(kind)
 
 

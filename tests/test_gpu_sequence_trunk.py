@@ -175,3 +175,31 @@ def test_sequence_trunk_argument_errors():
     mod.use_unconditional_branch = False
     with pytest.raises(ValueError, match="use_unconditional_branch"):
         mod(case["s_inputs"].cuda(), feats, unconditional=True)
+
+
+def test_context_parallel_wrappers_of_the_per_pair_glue():
+    """The per-pair ops need no exchange: the wrappers run the serial kernels on a rank's block, so a block of the
+    full result equals the result on the block."""
+    import bioemu2_b200 as b
+    from bioemu2_b200.context_parallel import ops
+
+    g = torch.Generator().manual_seed(920)
+    w = H.pairwise_conditioning_weights(g)
+    serial = _cond(w)
+    z = torch.randn(1, 96, 96, 128, generator=g).cuda()
+    rel = torch.randn(1, 96, 96, 128, generator=g).cuda()
+    with torch.no_grad():
+        full = serial(z, rel)
+        blk = ops.DistributedPairwiseConditioning(serial)(z[:, 48:, :40].contiguous(), rel[:, 48:, :40].contiguous())
+        assert torch.equal(blk, full[:, 48:, :40])
+        tiled = ops.LayerNormLinearParamsReplicatedTiled(serial.dim_pairwise_init_proj)
+        assert sorted(tiled.state_dict()) == ["0.bias", "0.weight", "1.weight"]
+        proj = tiled(z, rel)
+        ln = serial.dim_pairwise_init_proj[0]
+        want = torch.nn.functional.linear(
+            torch.nn.functional.layer_norm(torch.cat([z, rel], -1).double(), (256,), ln.weight.double(), ln.bias.double()),
+            serial.dim_pairwise_init_proj[1].weight.double())
+        assert_close("ln_linear_tiled", proj, want)
+    with pytest.raises(RuntimeError, match="forward-only"):
+        tiled(z, rel)
+    assert isinstance(serial, b.PairwiseConditioning)

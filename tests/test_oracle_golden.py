@@ -50,6 +50,8 @@ def run_oracle(case: dict, dtype=torch.float32) -> torch.Tensor:
                                 msa_blocks=case["msa_blocks"], num_blocks=case["num_blocks"],
                                 unconditional=case["unconditional"])
         return torch.cat([z.flatten(), s.flatten()])
+    if kind == "window_apb":
+        return O.attention_pair_bias_sliding_window(f(case["s"]), f(case["z"]), case["mask"], w, case["heads"], case["M"])
     raise KeyError(kind)
 
 
