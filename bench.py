@@ -45,7 +45,7 @@ import torch  # noqa: E402
 METRIC = "pairformer_trunk_pair_cells_per_s"
 UNIT = "pair-cells/s"
 GRIDS = {1: (1, 1), 2: (1, 2), 4: (2, 2), 8: (2, 4)}
-PROBES = ("attention_core", "triatt", "trimul", "transition", "apb", "opm", "trunk_glue")
+PROBES = ("attention_core", "triatt", "trimul", "transition", "apb", "opm", "trunk_glue", "window_attention")
 
 
 def parse_args():
@@ -373,6 +373,8 @@ def run_probe(args) -> None:
             fn = lambda: blk.attention(sd, zd, td)  # noqa: E731
         elif args.probe == "trunk_glue":
             return run_trunk_glue_probe(args, dev)
+        elif args.probe == "window_attention":
+            return run_window_attention_probe(args, dev)
         else:
             w, m, mask = opm_workload()
             mod = b.OuterProductMean(64, 32, 128).eval()
@@ -421,6 +423,52 @@ def run_trunk_glue_probe(args, dev) -> None:
         ms = event_time_ms(fn, args.steps)
         gbs = nbytes / (ms * 1e-3) / 1e9
         out["legs"][name] = {"ms": ms, "min_bytes": nbytes, "gbs": gbs, "frac_of_hbm_peak": gbs / peak["hbm_gbs"]}
+    out["device_status"] = b._lib.device_status()
+    print(json.dumps(out), flush=True)
+
+
+def run_window_attention_probe(args, dev) -> None:
+    """The atom transformer's sliding-window attention at 8 atoms per token of --tokens (windows of 32 queries, 128
+    keys, 4 heads of 32, pair width 16), 8 samples sharing one pair tensor: the whole module and its two kernels."""
+    import bioemu2_b200 as b
+    from bioemu2_b200 import functional as F
+
+    NW, W, Hk, c_s, c_z, heads, M = args.tokens * 8 // 32, 32, 128, 128, 16, 4, 8
+    g = torch.Generator().manual_seed(7)
+    mod = b.AttentionPairBiasSlidingWindow(c_s, c_z, heads).eval().to(dev)
+    s = torch.randn(M * NW, W, c_s, generator=g).to(dev)
+    z = torch.randn(1, NW, W, Hk, c_z, generator=g).to(dev)
+    mask = torch.ones(NW, W, dtype=torch.bool, device=dev)
+    w = mod.packed()
+    sn = F.rows_to_bf16(s, w.ln_s_w, w.ln_s_b)
+    qkv, gate = F.linear_bf16(sn, w.w_qkv, bias_f32=w.b_qkv), F.linear_bf16(sn, w.w_g)
+    bias = torch.empty(1, NW, heads, W, Hk, dtype=torch.float32, device=dev)
+    og = torch.empty(M * NW, W, c_s, dtype=torch.bfloat16, device=dev)
+    m8 = mask.to(torch.uint8)
+    lib = b._lib.lib
+    st = torch.cuda.current_stream().cuda_stream
+    legs = {
+        "module": lambda: mod(s, z, mask, multiplicity=M),
+        "window_bias_kernel": lambda: lib.b200_window_bias_fwd(z.data_ptr(), w.ln_z_w.data_ptr(), None, w.w_z.data_ptr(),
+                                                               bias.data_ptr(), NW, W, Hk, c_z, heads, 0, st),
+        "window_attention_kernel": lambda: lib.b200_window_attention_fwd(qkv.data_ptr(), gate.data_ptr(), bias.data_ptr(),
+                                                                         m8.data_ptr(), og.data_ptr(), 1, M, NW, W, Hk,
+                                                                         heads, c_s // heads, st),
+    }
+    peak = peaks()
+    z_bytes, bias_bytes = z.numel() * 4, bias.numel() * 4
+    flops = M * NW * heads * W * Hk * (c_s // heads) * 4
+    out = {"probe": "window_attention", "atoms": NW * W, "samples": M, "legs": {}}
+    for name, fn in legs.items():
+        for _ in range(args.warmup):
+            fn()
+        out["legs"][name] = {"ms": event_time_ms(fn, args.steps)}
+    kb = out["legs"]["window_bias_kernel"]
+    kb["bytes"] = z_bytes + bias_bytes
+    kb["frac_of_hbm_peak"] = kb["bytes"] / (kb["ms"] * 1e-3) / 1e9 / peak["hbm_gbs"]
+    ka = out["legs"]["window_attention_kernel"]
+    ka["fp32_tflops"] = flops / (ka["ms"] * 1e-3) / 1e12
+    ka["bytes"] = qkv.numel() * 2 + gate.numel() * 2 + og.numel() * 2 + M * bias_bytes
     out["device_status"] = b._lib.device_status()
     print(json.dumps(out), flush=True)
 

@@ -14,7 +14,7 @@ from .pair_weighted_averaging import PairWeightedAveraging
 from .pairmixer import PairMixerLayer, PairMixerModule, PairMixerMSALayer
 from .sequence_trunk import PairMixerMSAModule, PairMixerSequenceEmbedder
 from .swap import swap_into, to_b200
-from .transformer import AttentionLayer, ConditionedTransformerLayer
+from .transformer import AttentionLayer, ConditionedTransformerLayer, SlidingWindowAttentionLayer
 from .transition import Transition
 from .triangle_attention import (
     TriangleAttention,
@@ -40,6 +40,7 @@ __all__ = [
     "OuterProductMeanVanilla",
     "AttentionLayer",
     "ConditionedTransformerLayer",
+    "SlidingWindowAttentionLayer",
     "PairformerBlock",
     "PairformerModule",
     "PairMixerLayer",

@@ -370,10 +370,17 @@ def conditioned_transformer_layer(
     cc = layer_norm(c, w["cond.0.weight"], w["cond.0.bias"])
     cc = linear(F.silu(cc), w["cond.2.weight"], w["cond.2.bias"])
     a1, b1, g1, a2, b2, g2 = cc.chunk(6, dim=-1)
-    h = attention_pair_bias(
-        lns_scale * (layer_norm(x, None, None) * (1 + a1) + b1), pairs, mask,
-        _sub(w, "attention.pair_bias_attn"), num_heads, multiplicity,
-    )
+    t = lns_scale * (layer_norm(x, None, None) * (1 + a1) + b1)
+    if pairs.ndim == 5:
+        # windowed atom attention (SlidingWindowAttentionLayer.forward, transformer.py:198-229): atoms folded into
+        # query windows, ``pairs[B, NW, W, H, c]``, ``mask[B, N]``; keys ``attention.attention_layer.pair_bias_attn.*``
+        BM, N, D = x.shape
+        B, NW, W = pairs.shape[:3]
+        h = attention_pair_bias_sliding_window(
+            t.reshape(BM * NW, W, D), pairs, mask.reshape(B * NW, W),
+            _sub(w, "attention.attention_layer.pair_bias_attn"), num_heads, multiplicity).reshape(BM, N, D)
+    else:
+        h = attention_pair_bias(t, pairs, mask, _sub(w, "attention.pair_bias_attn"), num_heads, multiplicity)
     x = x + g1 * h
     h = transition(lns_scale * (layer_norm(x, None, None) * (1 + a2) + b2), _sub(w, "transition"))
     return x + g2 * h

@@ -107,6 +107,26 @@ def cond_layer_case(seed: int = 16, B: int = 1, M: int = 2, N: int = 24, dim: in
                 lns_scale=0.5)
 
 
+def cond_layer_window_case(seed: int = 30, B: int = 1, M: int = 2, NW: int = 3, W: int = 32, Hk: int = 128,
+                           dim: int = 128, dim_pair: int = 16, dim_cond: int = 128, heads: int = 4, hidden: int = 256):
+    """The atom transformer's block: ``ConditionedTransformerLayer(is_sliding_window=True)``."""
+    g = _gen(seed)
+    N = NW * W
+    w = {}
+    w["cond.0.weight"], w["cond.0.bias"] = H.ln_params(g, dim_cond)
+    w["cond.2.weight"] = H.kaiming_linear(g, 6 * dim, dim_cond)
+    w["cond.2.bias"] = 0.05 * torch.randn(6 * dim, generator=g)
+    w.update(H.prefixed("attention.attention_layer.pair_bias_attn", H.apb_weights(g, dim, dim_pair, heads, initial_norm=False)))
+    w.update(H.prefixed("transition", H.transition_weights(g, dim, hidden, use_norm=False)))
+    x = torch.randn(B * M, N, dim, generator=g)
+    c = torch.randn(B * M, N, dim_cond, generator=g)
+    z = torch.randn(B, NW, W, Hk, dim_pair, generator=g)
+    mask = torch.ones(B, N, dtype=torch.bool)
+    mask[0, N - 13:] = False
+    return dict(kind="cond_layer", w=w, x=x, c=c, z=z, mask=mask, heads=heads, M=M, hidden=hidden, lns_scale=0.5,
+                window=(W, Hk))
+
+
 def pwa_case(seed: int = 17, B: int = 2, S: int = 10, N: int = 24, c_m: int = 64, c_z: int = 128):
     g = _gen(seed)
     w = H.pwa_weights(g, c_m, c_z, 32, 8)
@@ -200,6 +220,7 @@ CASES = {
     "msa_module": lambda: msa_module_case(),
     "sequence_trunk": lambda: sequence_trunk_case(),
     "sequence_trunk_unconditional": lambda: sequence_trunk_case(seed=27, unconditional=True),
+    "cond_layer_window": lambda: cond_layer_window_case(),
     "window_apb": lambda: window_apb_case(),
     "window_apb_batch2": lambda: window_apb_case(seed=29, B=2, M=1, NW=2, n_pad=40),
 }

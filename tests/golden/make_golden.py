@@ -55,9 +55,12 @@ def run_reference(case: dict) -> torch.Tensor:
         if kind == "cond_layer":
             from bioemu2.biomoa.modules.transformer import ConditionedTransformerLayer
 
+            window = case.get("window")
             mod = ConditionedTransformerLayer(
                 dim=case["x"].shape[-1], dim_pairwise=case["z"].shape[-1], dim_cond=case["c"].shape[-1],
                 heads=case["heads"], transition_hidden=case["hidden"], lns_scale=case["lns_scale"],
+                is_sliding_window=window is not None, window_queries=window[0] if window else None,
+                window_keys=window[1] if window else None,
             ).eval()
             mod.load_state_dict(w, strict=True)
             return mod(case["x"], case["z"], case["c"], case["mask"], multiplicity=case["M"])

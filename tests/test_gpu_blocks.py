@@ -47,6 +47,29 @@ def test_conditioned_transformer_layer_golden():
     assert_close("cond_layer_golden", out, golden["cond_layer"]["output"])
 
 
+def test_conditioned_transformer_layer_sliding_window_golden():
+    """The atom transformer's block: windowed attention inside the same conditioned layer, mask given and omitted."""
+    import bioemu2_b200 as b
+
+    golden = torch.load(C.GOLDEN_PATH)
+    case = C.CASES["cond_layer_window"]()
+    W, Hk = case["window"]
+    m = b.ConditionedTransformerLayer(dim=128, dim_pairwise=16, dim_cond=128, heads=case["heads"],
+                                      transition_hidden=case["hidden"], lns_scale=case["lns_scale"],
+                                      is_sliding_window=True, window_queries=W, window_keys=Hk).eval()
+    m.load_state_dict(case["w"], strict=True)
+    m.cuda()
+    assert isinstance(m.attention, b.SlidingWindowAttentionLayer)
+    x, z, c = case["x"].cuda(), case["z"].cuda(), case["c"].cuda()
+    with torch.no_grad():
+        out = m(x, z, c, case["mask"].cuda(), multiplicity=case["M"])
+        flat = m(x, z.reshape(1, -1, Hk, 16), c, case["mask"].cuda(), multiplicity=case["M"])   # flat [B, N, H, c] pairs
+        full = m(x, z, c, None, multiplicity=case["M"])
+        ones = m(x, z, c, torch.ones_like(case["mask"]).cuda(), multiplicity=case["M"])
+    assert_close("cond_layer_window_golden", out, golden["cond_layer_window"]["output"])
+    assert torch.equal(out, flat) and torch.equal(full, ones)
+
+
 def _pairformer_weights(g):
     w = {}
     w.update(H.prefixed("tri_mul_out", H.trimul_weights(g)))

@@ -124,3 +124,20 @@ def test_swap_takes_the_composite_modules_whole():
     assert sorted(sd) == sorted(before)
     for k in before:
         assert torch.equal(sd[k], before[k]), k
+
+
+def test_swap_recognises_the_sliding_window_attention():
+    import bioemu2_b200 as b
+
+    reference_shim.install()
+    from bioemu2.biomoa.ops.attention_pair_bias import AttentionPairBiasSlidingWindow
+
+    torch.manual_seed(3)
+    model = nn.Sequential(AttentionPairBiasSlidingWindow(128, 16, 4, window_queries=32, window_keys=128)).eval()
+    before = {k: v.clone() for k, v in model.state_dict().items()}
+    report = b.swap_into(model)
+    twin = model[0]
+    assert report["0"] == ("AttentionPairBiasSlidingWindow", "AttentionPairBiasSlidingWindow")
+    assert isinstance(twin, b.AttentionPairBiasSlidingWindow)
+    assert (twin.c_s, twin.c_z, twin.num_heads, twin.window_queries, twin.window_keys) == (128, 16, 4, 32, 128)
+    _same_state(model, before)
