@@ -113,7 +113,10 @@ bmm_nt_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ C
       }
     }
   } else if (warp == 1) {
-    if (lane == 0) {
+    // The whole warp walks the tile and K loops and waits on the barriers; one elected lane issues the products and
+    // the commits (a converged warp issues a tcgen05.mma several times faster than a lone thread of a diverged one).
+    {
+      const bool leader = elect_one();
       constexpr uint32_t idesc = make_idesc_bf16(128, BN);
       int stage = 0;
       uint32_t phase = 0;
@@ -129,16 +132,20 @@ bmm_nt_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ C
           const uint32_t sa = smem_u32(smem + stage * Cfg::STAGE_BYTES);
           const uint32_t sb = sa + Cfg::A_BYTES;
           const uint32_t a_lo = desc_lo(sa), b_lo = desc_lo(sb);
+          if (leader) {
 #pragma unroll
-          for (int k = 0; k < 4; ++k)
-            umma_bf16_ss2(d_tmem, a_lo + 2 * k, kDescHiSw128, b_lo + 2 * k, kDescHiSw128, idesc, (kb | k) != 0);
-          umma_commit(&empty[stage]);
+            for (int k = 0; k < 4; ++k)
+              umma_bf16_ss2(d_tmem, a_lo + 2 * k, kDescHiSw128, b_lo + 2 * k, kDescHiSw128, idesc, (kb | k) != 0);
+            umma_commit(&empty[stage]);
+          }
+          __syncwarp();
           if (++stage == Cfg::STAGES) {
             stage = 0;
             phase ^= 1;
           }
         }
-        umma_commit(&acc_full[acc]);
+        if (leader) umma_commit(&acc_full[acc]);
+        __syncwarp();
       }
     }
   } else {

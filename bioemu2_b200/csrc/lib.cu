@@ -1242,15 +1242,19 @@ int b200_window_bias_fwd(const void* z, const float* ln_w, const float* ln_b, co
                          int64_t windows, int W, int Hk, int c_z, int heads, int z_dtype, b200_stream_t stream) {
   if (int e = b200_check_device()) return e;
   B200_CHECK_ARG(z && ln_w && w_z && bias, "z/ln_w/w_z/bias is NULL");
-  B200_CHECK_ARG(windows >= 0 && W > 0 && Hk > 0 && c_z > 0, "need windows >= 0 and W, Hk, c_z > 0");
+  B200_CHECK_ARG(windows >= 0 && W > 0 && Hk > 0, "need windows >= 0 and W, Hk > 0");
+  B200_CHECK_ARG(c_z > 0 && c_z % 4 == 0 && c_z <= 128, "c_z=%d must be a multiple of 4, at most 128", c_z);
+  B200_CHECK_ARG(aligned(z, 16) && aligned(bias, 4), "z must be 16-byte aligned");
   B200_CHECK_ARG(heads > 0 && heads <= kWindowMaxHeads, "heads=%d must be in 1..%d", heads, kWindowMaxHeads);
   B200_CHECK_ARG((z_dtype | 1) == 1, "unknown dtype");
   if (windows == 0) return B200_OK;
   WindowBiasParams p{z, ln_w, ln_b, w_z, bias, windows * W * Hk, W * Hk, c_z, heads, 1e-5f};
-  const int grid = grid_for(p.pairs, 256);
+  int lpr = 1;
+  while (lpr * 4 < c_z) lpr *= 2;  // lanes per pair: four channels each
+  const int grid = grid_for(p.pairs * lpr, 256);
   cudaStream_t st = static_cast<cudaStream_t>(stream);
-  if (z_dtype == B200_DTYPE_F32) window_bias_kernel<true><<<grid, 256, 0, st>>>(p);
-  else window_bias_kernel<false><<<grid, 256, 0, st>>>(p);
+  if (z_dtype == B200_DTYPE_F32) window_bias_kernel<true><<<grid, 256, 0, st>>>(p, lpr);
+  else window_bias_kernel<false><<<grid, 256, 0, st>>>(p, lpr);
   B200_AFTER_LAUNCH();
   return B200_OK;
 }

@@ -75,26 +75,32 @@ opm_proj_kernel(const __grid_constant__ CUtensorMap tmW, OpmProjParams p) {
   const uint32_t tmem_base = *tmem_slot;
 
   if (warp == 8) {
-    if (lane == 0) {
+    // the whole warp waits on the barriers, one elected lane issues
+    const bool leader = elect_one();
+    if (leader) {
       mbar_arrive_expect_tx(w_full, 8192);
       tma_load_2d(smem + W_OFF, &tmW, w_full, 0, 0);
-      mbar_wait(w_full, 0, 50);
-      constexpr uint32_t idesc = make_idesc_bf16(128, 64);
-      const uint32_t w_s = smem_u32(smem + W_OFF);
-      int it = 0;
-      for (int tile = blockIdx.x; tile < p.num_tiles; tile += gridDim.x, ++it) {
-        const int s = it & 1;
-        mbar_wait(&x_full[s], (it >> 1) & 1, 51);
-        mbar_wait(&acc_empty[s], ((it >> 1) & 1) ^ 1, 52);
-        tc_fence_after_sync();
-        const uint32_t x_s = smem_u32(smem + X_OFF + s * kOperandHalf);
-        const uint32_t x_lo = desc_lo(x_s), w_lo = desc_lo(w_s);
+    }
+    __syncwarp();
+    mbar_wait(w_full, 0, 50);
+    constexpr uint32_t idesc = make_idesc_bf16(128, 64);
+    const uint32_t w_s = smem_u32(smem + W_OFF);
+    int it = 0;
+    for (int tile = blockIdx.x; tile < p.num_tiles; tile += gridDim.x, ++it) {
+      const int s = it & 1;
+      mbar_wait(&x_full[s], (it >> 1) & 1, 51);
+      mbar_wait(&acc_empty[s], ((it >> 1) & 1) ^ 1, 52);
+      tc_fence_after_sync();
+      const uint32_t x_s = smem_u32(smem + X_OFF + s * kOperandHalf);
+      const uint32_t x_lo = desc_lo(x_s), w_lo = desc_lo(w_s);
+      if (leader) {
 #pragma unroll
         for (int k = 0; k < 4; ++k)
           umma_bf16_ss2(tmem_base + s * 64, x_lo + 2 * k, kDescHiSw128, w_lo + 2 * k, kDescHiSw128, idesc, k > 0);
         umma_commit(&x_empty[s]);
         umma_commit(&acc_full[s]);
       }
+      __syncwarp();
     }
   } else if (warp >= 4) {
     // producers: 8 threads per row (8 channels each), 16 rows per pass, 8 passes

@@ -65,21 +65,27 @@ pair_bias_kernel(const __grid_constant__ CUtensorMap tmW, PairBiasParams p) {
   const uint32_t tmem_base = *tmem_slot;
 
   if (warp == 12) {
-    if (lane == 0) {
+    // The whole warp walks the tile loop and waits on the barriers; one elected lane issues the products and the
+    // commits (a converged warp issues a tcgen05.mma several times faster than a lone thread of a diverged one).
+    const bool leader = elect_one();
+    if (leader) {
       mbar_arrive_expect_tx(w_full, 4096);
       tma_load_2d(smem + W_OFF, &tmW, w_full, 0, 0);
       tma_load_2d(smem + W_OFF + 2048, &tmW, w_full, 64, 0);
-      mbar_wait(w_full, 0, 80);
-      constexpr uint32_t idesc = make_idesc_bf16(128, 16);
-      const uint32_t w_s = smem_u32(smem + W_OFF);
-      int it = 0;
-      for (int tile = blockIdx.x; tile < p.num_tiles; tile += gridDim.x, ++it) {
-        const int s = it & 1;
-        mbar_wait(&x_full[s], (it >> 1) & 1, 81);
-        mbar_wait(&acc_empty[s], ((it >> 1) & 1) ^ 1, 82);
-        tc_fence_after_sync();
-        const uint32_t x_s = smem_u32(smem + X_OFF + s * kOperandTile);
-        const uint32_t x_lo = desc_lo(x_s), w_lo = desc_lo(w_s);
+    }
+    __syncwarp();
+    mbar_wait(w_full, 0, 80);
+    constexpr uint32_t idesc = make_idesc_bf16(128, 16);
+    const uint32_t w_s = smem_u32(smem + W_OFF);
+    int it = 0;
+    for (int tile = blockIdx.x; tile < p.num_tiles; tile += gridDim.x, ++it) {
+      const int s = it & 1;
+      mbar_wait(&x_full[s], (it >> 1) & 1, 81);
+      mbar_wait(&acc_empty[s], ((it >> 1) & 1) ^ 1, 82);
+      tc_fence_after_sync();
+      const uint32_t x_s = smem_u32(smem + X_OFF + s * kOperandTile);
+      const uint32_t x_lo = desc_lo(x_s), w_lo = desc_lo(w_s);
+      if (leader) {
 #pragma unroll
         for (int k = 0; k < 8; ++k)
           umma_bf16_ss2(tmem_base + s * 16, x_lo + (k >> 2) * (kOperandHalf >> 4) + (k & 3) * 2, kDescHiSw128,
@@ -87,6 +93,7 @@ pair_bias_kernel(const __grid_constant__ CUtensorMap tmW, PairBiasParams p) {
         umma_commit(&x_empty[s]);
         umma_commit(&acc_full[s]);
       }
+      __syncwarp();
     }
   } else if (warp >= 4) {
     const int pt = threadIdx.x - 128;

@@ -133,7 +133,9 @@ transition_kernel(const __grid_constant__ CUtensorMap tmW1, const __grid_constan
     }
   } else if (warp == 16) {
     // ------------------------------------------------------------------ GEMM1 issuer
-    if (lane == 0) {
+    // (both issuers: the whole warp walks the chunk loop and waits on the barriers, one elected lane issues)
+    {
+      const bool leader = elect_one();
       constexpr uint32_t idesc = make_idesc_bf16(128, 128);
       for (int g = 0; g < total_chunks; ++g) {
         const int c = g & 7, b = g & 1, it = g >> 3, ws = g % WS;
@@ -141,15 +143,19 @@ transition_kernel(const __grid_constant__ CUtensorMap tmW1, const __grid_constan
         mbar_wait(&w1_full[ws], (g / WS) & 1, 36);
         mbar_wait(&d1_empty[b], ((g >> 1) & 1) ^ 1, 37);
         tc_fence_after_sync();
-        umma_k128(tmem_base + b * 128, smem_u32(smem + X_OFF), smem_u32(smem + W1_OFF + ws * kOperandTile), idesc, false);
-        umma_commit(&w1_empty[ws]);
-        umma_commit(&d1_full[b]);
-        if (c == 7) umma_commit(x_empty);
+        if (leader) {
+          umma_k128(tmem_base + b * 128, smem_u32(smem + X_OFF), smem_u32(smem + W1_OFF + ws * kOperandTile), idesc, false);
+          umma_commit(&w1_empty[ws]);
+          umma_commit(&d1_full[b]);
+          if (c == 7) umma_commit(x_empty);
+        }
+        __syncwarp();
       }
     }
   } else if (warp == 18) {
     // ------------------------------------------------------------------ GEMM2 issuer
-    if (lane == 0) {
+    {
+      const bool leader = elect_one();
       constexpr uint32_t idesc = make_idesc_bf16(128, 128);
       for (int g = 0; g < total_chunks; ++g) {  // consumes H[g&1] and the fc3 slice of chunk g
         const int c = g & 7, b = g & 1, o = (g >> 3) & 1, ws = g % WS;
@@ -160,12 +166,15 @@ transition_kernel(const __grid_constant__ CUtensorMap tmW1, const __grid_constan
         const uint32_t h_s = smem_u32(smem + H_OFF + b * kOperandHalf);
         const uint32_t w3_s = smem_u32(smem + W3_OFF + ws * kOperandHalf);
         const uint32_t h_lo = desc_lo(h_s), w3_lo = desc_lo(w3_s);
+        if (leader) {
 #pragma unroll
-        for (int k = 0; k < 4; ++k)
-          umma_bf16_ss2(tmem_base + 256 + o * 128, h_lo + 2 * k, kDescHiSw128, w3_lo + 2 * k, kDescHiSw128, idesc, (c | k) != 0);
-        umma_commit(&h_empty[b]);
-        umma_commit(&w3_empty[ws]);
-        if (c == 7) umma_commit(&out_full[o]);
+          for (int k = 0; k < 4; ++k)
+            umma_bf16_ss2(tmem_base + 256 + o * 128, h_lo + 2 * k, kDescHiSw128, w3_lo + 2 * k, kDescHiSw128, idesc, (c | k) != 0);
+          umma_commit(&h_empty[b]);
+          umma_commit(&w3_empty[ws]);
+          if (c == 7) umma_commit(&out_full[o]);
+        }
+        __syncwarp();
       }
     }
   } else if (warp >= 8) {

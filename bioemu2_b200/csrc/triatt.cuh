@@ -76,31 +76,41 @@ triatt_proj_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constan
   const uint32_t tmem_base = *tmem_slot;
 
   if (warp == 12) {
-    if (lane == 0) {
+    // The whole warp walks the tile loop and waits on the barriers; one elected lane issues the products and the
+    // commits (a converged warp issues a tcgen05.mma several times faster than a lone thread of a diverged one).
+    const bool leader = elect_one();
+    if (leader) {
       mbar_arrive_expect_tx(w_full, 4 * kOperandTile);
       for (int mt = 0; mt < 4; ++mt)
         for (int h = 0; h < 2; ++h)
           tma_load_2d(smem + W_OFF + mt * kOperandTile + h * kOperandHalf, &tmW, w_full, h * 64, mt * 128);
-      mbar_wait(w_full, 0, 90);
-      constexpr uint32_t idesc = make_idesc_bf16(128, 128);
-      const uint32_t w_s = smem_u32(smem + W_OFF);
-      int it = 0;
-      for (int tile = blockIdx.x; tile < p.num_tiles; tile += gridDim.x, ++it) {
-        const int s = it & 1;
-        mbar_wait(&x_full[s], (it >> 1) & 1, 91);
-        const uint32_t x_s = smem_u32(smem + X_OFF + s * kOperandTile);
-        mbar_wait(&acc_empty[0], (it & 1) ^ 1, 92);
-        tc_fence_after_sync();
+    }
+    __syncwarp();
+    mbar_wait(w_full, 0, 90);
+    constexpr uint32_t idesc = make_idesc_bf16(128, 128);
+    const uint32_t w_s = smem_u32(smem + W_OFF);
+    int it = 0;
+    for (int tile = blockIdx.x; tile < p.num_tiles; tile += gridDim.x, ++it) {
+      const int s = it & 1;
+      mbar_wait(&x_full[s], (it >> 1) & 1, 91);
+      const uint32_t x_s = smem_u32(smem + X_OFF + s * kOperandTile);
+      mbar_wait(&acc_empty[0], (it & 1) ^ 1, 92);
+      tc_fence_after_sync();
+      if (leader) {
         umma_k128(tmem_base + 0, x_s, w_s + 0 * kOperandTile, idesc, false);    // q  [pair][ch]
         umma_k128(tmem_base + 128, x_s, w_s + 1 * kOperandTile, idesc, false);  // k
         umma_commit(&acc_full[0]);
-        mbar_wait(&acc_empty[1], (it & 1) ^ 1, 93);
-        tc_fence_after_sync();
+      }
+      __syncwarp();
+      mbar_wait(&acc_empty[1], (it & 1) ^ 1, 93);
+      tc_fence_after_sync();
+      if (leader) {
         umma_k128(tmem_base + 256, x_s, w_s + 2 * kOperandTile, idesc, false);  // g  [pair][ch]
         umma_k128(tmem_base + 384, w_s + 3 * kOperandTile, x_s, idesc, false);  // V^T [ch][pair]
         umma_commit(&acc_full[1]);
         umma_commit(&x_empty[s]);
       }
+      __syncwarp();
     }
   } else if (warp >= 4) {
     const int pt = threadIdx.x - 128;

@@ -145,16 +145,20 @@ trimul_in_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant_
     const CUtensorMap* tmOut = half ? &tmB : &tmA;
     const uint32_t p_addr = tmem_addr(tmem_base, (warp & 3) * 32, (half * 2) * 128);
     const uint32_t g_addr = p_addr + 128;
-    const bool issuer = (threadIdx.x & 127) == 0;  // first thread of the group
+    // The first WARP of the group issues the group's products: all its lanes wait on the barriers and one elected
+    // lane issues (a converged warp issues a tcgen05.mma several times faster than a lone thread of a diverged one).
+    const bool issue_warp = (warp & 3) == 0;
+    const bool leader = issue_warp && elect_one();
     constexpr uint32_t idesc = make_idesc_bf16(128, 128);
     const uint32_t w_s = smem_u32(smem + W_OFF);
-    if (issuer) {
-      if (half == 0) {
+    if (issue_warp) {
+      if (half == 0 && leader) {
         mbar_arrive_expect_tx(w_full, 4 * kOperandTile);
         for (int mt = 0; mt < 4; ++mt)
           for (int h = 0; h < 2; ++h)
             tma_load_2d(smem + W_OFF + mt * kOperandTile + h * kOperandHalf, &tmW, w_full, h * 64, mt * 128);
       }
+      __syncwarp();
       mbar_wait(w_full, 0, 10);
     }
     int it = 0;
@@ -162,18 +166,18 @@ trimul_in_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant_
       const int line = tile / tiles_per_line;
       const int pos0 = (tile - line * tiles_per_line) << 7;
       const uint32_t* msk = reinterpret_cast<const uint32_t*>(mask_s + (it & 3) * 128);
-      if (issuer) {  // this half's products for the tile: p and g projections against operand stage it & 1
+      if (issue_warp) {  // this half's products for the tile: p and g projections against operand stage it & 1
         const int s = it & 1;
         mbar_wait(&x_full[s], (it >> 1) & 1, 11);
         mbar_wait(&acc_empty[half], (it & 1) ^ 1, 12);  // the whole group has drained the previous tile
         tc_fence_after_sync();
         const uint32_t x_s = smem_u32(smem + X_OFF + s * kOperandTile);
-        for (int m2 = 0; m2 < 2; ++m2) {
-          const int mt = half * 2 + m2;
-          umma_k128(tmem_base + mt * 128, w_s + mt * kOperandTile, x_s, idesc, false);
+        if (leader) {
+          umma_k128(tmem_base + (half * 2) * 128, w_s + (half * 2) * kOperandTile, x_s, idesc, false);
+          umma_k128(tmem_base + (half * 2 + 1) * 128, w_s + (half * 2 + 1) * kOperandTile, x_s, idesc, false);
+          umma_commit(&acc_full[half]);
+          umma_commit(&x_empty[s]);
         }
-        umma_commit(&acc_full[half]);
-        umma_commit(&x_empty[s]);
       }
       __syncwarp();
       mbar_wait(&acc_full[half], it & 1, 14);
@@ -185,10 +189,6 @@ trimul_in_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant_
       tmem_ld_32x16(g_addr, ga);
 #pragma unroll
       for (int c = 0; c < 8; ++c) {
-        if ((c & 3) == 0) {  // the previous store has finished reading the staging tile
-          if (d == 0) tma_store_wait_read0();
-          named_bar_sync(1 + half, 128);
-        }
         uint32_t(&pv)[16] = (c & 1) ? pb : pa;
         uint32_t(&gv)[16] = (c & 1) ? gb : ga;
         tmem_ld_wait();
@@ -211,6 +211,10 @@ trimul_in_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant_
             v1 = ((m4 >> (((j + 1) & 3) * 8)) & 0xff) ? v1 : 0.f;
           }
           packed[j >> 1] = pack_bf16x2(v0, v1);
+        }
+        if ((c & 3) == 0) {  // the previous store has finished reading the staging tile (its wait hides behind the
+          if (d == 0) tma_store_wait_read0();  // chunk's arithmetic above)
+          named_bar_sync(1 + half, 128);
         }
         *reinterpret_cast<uint4*>(stage + sw128_offset(d, (c & 3) * 2)) = make_uint4(packed[0], packed[1], packed[2], packed[3]);
         *reinterpret_cast<uint4*>(stage + sw128_offset(d, (c & 3) * 2 + 1)) =
@@ -405,30 +409,39 @@ trimul_out_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant
     };
     int my_tiles = 0;
     for (int tile = blockIdx.x; tile < p.num_tiles; tile += gridDim.x) ++my_tiles;
-    if (threadIdx.x == 0) {
-      mbar_arrive_expect_tx(w_full, 2 * kOperandTile);
-      for (int mt = 0; mt < 2; ++mt)
-        for (int h = 0; h < 2; ++h)
-          tma_load_2d(smem + W_OFF + mt * kOperandTile + h * kOperandHalf, &tmW, w_full, h * 64, mt * 128);
-      if (my_tiles > 0) issue_t(blockIdx.x, 0);          // first two t tiles in flight
-      if (my_tiles > 1) issue_t(blockIdx.x + gridDim.x, 1);
+    // Warp 0 as a whole waits on the barriers; one elected lane issues the loads and the products (a converged warp
+    // issues a tcgen05.mma several times faster than a lone thread of a diverged one).
+    const bool leader = warp == 0 && elect_one();
+    if (warp == 0) {
+      if (leader) {
+        mbar_arrive_expect_tx(w_full, 2 * kOperandTile);
+        for (int mt = 0; mt < 2; ++mt)
+          for (int h = 0; h < 2; ++h)
+            tma_load_2d(smem + W_OFF + mt * kOperandTile + h * kOperandHalf, &tmW, w_full, h * 64, mt * 128);
+        if (my_tiles > 0) issue_t(blockIdx.x, 0);          // first two t tiles in flight
+        if (my_tiles > 1) issue_t(blockIdx.x + gridDim.x, 1);
+      }
+      __syncwarp();
       mbar_wait(w_full, 0, 20);
     }
     __syncwarp();
     for (int step = 0; step <= my_tiles; ++step) {
-      if (threadIdx.x == 0 && step < my_tiles) {
+      if (warp == 0 && step < my_tiles) {
         const int acc = step & 1;
         mbar_wait(&acc_empty[acc], ((step >> 1) & 1) ^ 1, 21);
         mbar_wait(a1_full, step & 1, 22);
         mbar_wait(a2_full, step & 1, 23);
         tc_fence_after_sync();
-        umma_k128(tmem_base + acc * 256, a1_s, w_s, idesc, false);                       // p_out(LN_out(t))
-        umma_k128(tmem_base + acc * 256 + 128, a2_s, w_s + kOperandTile, idesc, false);  // g_out(LN_in(z))
-        umma_commit(a_empty);
-        umma_commit(&acc_full[acc]);
+        if (leader) {
+          umma_k128(tmem_base + acc * 256, a1_s, w_s, idesc, false);                       // p_out(LN_out(t))
+          umma_k128(tmem_base + acc * 256 + 128, a2_s, w_s + kOperandTile, idesc, false);  // g_out(LN_in(z))
+          umma_commit(a_empty);
+          umma_commit(&acc_full[acc]);
+        }
+        __syncwarp();
         if (step + 2 < my_tiles) {  // refill the raw-t stage this tile used, once the transformers have released it
           mbar_wait(&t_empty[step & 1], (step >> 1) & 1, 24);
-          issue_t(blockIdx.x + (step + 2) * gridDim.x, step & 1);
+          if (leader) issue_t(blockIdx.x + (step + 2) * gridDim.x, step & 1);
         }
       }
       __syncwarp();

@@ -6,7 +6,7 @@
 // So the two kernels here are plain fp32 CUDA-core kernels and the arithmetic of the core - scores, softmax and the
 // weighted sum - is exact fp32, as in the reference's autocast-free block.
 //
-//   window_bias_kernel       bias[b][w][h][i][j] = proj_z(LayerNorm(z[b][w][i][j][:]))[h], one thread per pair
+//   window_bias_kernel       bias[b][w][h][i][j] = proj_z(LayerNorm(z[b][w][i][j][:]))[h], c_z / 4 lanes per pair
 //   window_attention_kernel  one CTA per (sample, window): K and V rows of the window staged in shared memory as bf16,
 //                            one thread per (head, query), online softmax over the keys in chunks of 8
 #pragma once
@@ -28,39 +28,70 @@ struct WindowBiasParams {
 
 constexpr int kWindowMaxHeads = 16;
 
+// A group of LPR lanes (a power of two >= c_z / 4) shares one pair: each lane holds four channels, the LayerNorm
+// statistics and the per-head dot products are reduced across the group with shuffles, so a warp's loads cover
+// 32 / LPR consecutive rows (contiguous memory) instead of 32 rows a stride apart.
 template <bool F32>
 __global__ void __launch_bounds__(256)
-window_bias_kernel(WindowBiasParams p) {
-  for (long long t = (long long)blockIdx.x * blockDim.x + threadIdx.x; t < p.pairs; t += (long long)gridDim.x * blockDim.x) {
-    const uint8_t* row = static_cast<const uint8_t*>(p.z) + t * p.c_z * (long long)(F32 ? 4 : 2);
-    auto ld = [&](int c) -> float {
-      return F32 ? reinterpret_cast<const float*>(row)[c]
-                 : __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(row)[c]);
-    };
-    float s = 0.f;
-    for (int c = 0; c < p.c_z; ++c) s += ld(c);
-    const float mean = s / float(p.c_z);
+window_bias_kernel(WindowBiasParams p, int lpr) {
+  const int lane = threadIdx.x & 31;
+  const int sub = lane / lpr, l = lane % lpr;
+  const int rpw = 32 / lpr;
+  const bool has = l * 4 < p.c_z;
+  const long long warp_global = (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  const long long warp_stride = (long long)gridDim.x * (blockDim.x >> 5);
+  float g[4] = {0.f, 0.f, 0.f, 0.f}, bt[4] = {0.f, 0.f, 0.f, 0.f};
+  if (has) {
+#pragma unroll
+    for (int e = 0; e < 4; ++e) {
+      g[e] = p.ln_w[l * 4 + e];
+      bt[e] = p.ln_b ? p.ln_b[l * 4 + e] : 0.f;
+    }
+  }
+  const float inv = 1.0f / float(p.c_z);
+  // every lane runs the same number of iterations: the shuffles are warp-wide
+  for (long long rb = warp_global * rpw; rb < p.pairs; rb += warp_stride * rpw) {
+    const long long t = rb + sub;
+    const bool act = has && t < p.pairs;
+    float x[4] = {0.f, 0.f, 0.f, 0.f};
+    if (act) {
+      if (F32) {
+        const float4 v = *reinterpret_cast<const float4*>(static_cast<const float*>(p.z) + t * p.c_z + l * 4);
+        x[0] = v.x; x[1] = v.y; x[2] = v.z; x[3] = v.w;
+      } else {
+        const uint2 v = *reinterpret_cast<const uint2*>(static_cast<const __nv_bfloat16*>(p.z) + t * p.c_z + l * 4);
+        x[0] = bf16lo(v.x); x[1] = bf16hi(v.x); x[2] = bf16lo(v.y); x[3] = bf16hi(v.y);
+      }
+    }
+    float s = (x[0] + x[1]) + (x[2] + x[3]);
+    for (int o = lpr >> 1; o > 0; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
+    const float mean = s * inv;
     float ss = 0.f;
-    for (int c = 0; c < p.c_z; ++c) {
-      const float d = ld(c) - mean;
-      ss = fmaf(d, d, ss);
-    }
-    const float rstd = rsqrtf(ss / float(p.c_z) + p.eps);
-    float acc[kWindowMaxHeads];
+    if (has) {
 #pragma unroll
-    for (int h = 0; h < kWindowMaxHeads; ++h) acc[h] = 0.f;
-    for (int c = 0; c < p.c_z; ++c) {
-      const float y = fmaf((ld(c) - mean) * rstd, __ldg(p.ln_w + c), p.ln_b ? __ldg(p.ln_b + c) : 0.f);
-#pragma unroll
-      for (int h = 0; h < kWindowMaxHeads; ++h)
-        if (h < p.heads) acc[h] = fmaf(y, __ldg(p.w_z + h * p.c_z + c), acc[h]);
+      for (int e = 0; e < 4; ++e) {
+        x[e] -= mean;
+        ss = fmaf(x[e], x[e], ss);
+      }
     }
+    for (int o = lpr >> 1; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+    const float rstd = rsqrtf(ss * inv + p.eps);
+    float y[4];
+#pragma unroll
+    for (int e = 0; e < 4; ++e) y[e] = has ? fmaf(x[e] * rstd, g[e], bt[e]) : 0.f;
     const long long win = t / p.window_pairs;
     const int ij = int(t - win * p.window_pairs);
     float* dst = p.bias + win * p.heads * p.window_pairs + ij;
+    for (int h = 0; h < p.heads; ++h) {
+      float acc = 0.f;
+      if (has) {
+        const float* wr = p.w_z + h * p.c_z + l * 4;
 #pragma unroll
-    for (int h = 0; h < kWindowMaxHeads; ++h)
-      if (h < p.heads) dst[(long long)h * p.window_pairs] = acc[h];
+        for (int e = 0; e < 4; ++e) acc = fmaf(y[e], __ldg(wr + e), acc);
+      }
+      for (int o = lpr >> 1; o > 0; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
+      if (l == (h % lpr) && t < p.pairs) dst[(long long)h * p.window_pairs] = acc;
+    }
   }
 }
 
