@@ -16,6 +16,12 @@ Exchange used here (all NCCL collectives over the whole grid or its row / column
                         the slab kernel runs on complete attention rows and each rank keeps its own block of the
                         update.  The ranks of a group compute the same slab: this first form scales with one grid
                         axis per direction (rows for the starting node, columns for the ending node).
+* pair-weighted averaging  the MSA's token axis lies along the grid's COLUMNS while the weights' row axis lies along
+                        its rows, so a rank needs weight rows it does not hold.  The 8-head logits of every block (and
+                        the pair mask, one byte per pair) are all-gathered over the grid - they are 1/16 of z -, each
+                        rank soft-maxes the rows of ITS tokens, all-gathers the normalised MSA (bf16) over the row
+                        group for the values, and averages its own (depth slice, token block) with the single-GPU
+                        kernels.  Reference: a 2D ring, src/bioemu2/context_parallel/ops/pair_averaging.py:44-290.
 * outer product mean    the MSA is sharded (depth over grid rows, tokens over grid columns); tokens are all-gathered
                         over the row group, every rank forms the partial result of ITS depth slice for its column
                         block with proj_o already applied (proj_o is linear, so partial sums commute with it), and a
@@ -56,6 +62,22 @@ class CudaAttentionLocal:
         from .. import functional as F
 
         return F.outer_product_mean_cols(m_rows, mask_rows, opm_packed, j0, nj, inv_count, add_bias)
+
+    def pwa_logits(self, z_slab: Tensor, pwa_packed) -> Tensor:
+        from .. import functional as F
+
+        return F.pair_bias_slab(z_slab, pwa_packed.ln_z_w, pwa_packed.ln_z_b, pwa_packed.w_z, pwa_packed.H)
+
+    def pwa_norm(self, m_loc: Tensor, pwa_packed) -> Tensor:
+        from .. import functional as F
+
+        return F.pwa_norm(m_loc, pwa_packed)
+
+    def pwa_apply(self, mn_all, mn_own, logits, mask_rows, pwa_packed, residual):
+        from .. import functional as F
+
+        out = torch.empty(mn_own.shape, dtype=residual.dtype if residual is not None else torch.float32, device=mn_own.device)
+        return F.pwa_apply(mn_all, mn_own, logits.contiguous(), F.mask_u8(mask_rows), pwa_packed, residual, out)
 
     def to_exchange(self, x: Tensor) -> Tensor:
         """The pair block as it travels to the ranks that attend over its lines: bf16, half the bytes on NVLink.  The
@@ -165,6 +187,35 @@ def cp_triangle_attention_(z_loc: Tensor, mask_loc: Tensor, tri_packed, grid: CP
         r0, r1 = grid.coords.my_rows(n)
         z_loc += upd[r0:r1]
     return z_loc
+
+
+def _assemble_blocks(blocks: list[Tensor], grid: CPGrid, n: int) -> Tensor:
+    """World all-gathered pair blocks ``[n_r, n_c]`` -> the full ``[n, n]`` tensor."""
+    co = grid.coords
+    full = blocks[0].new_zeros((n, n))
+    for rank, blk in enumerate(blocks):
+        (r0, r1), (c0, c1) = co.row_ranges(n)[rank // co.cols], co.col_ranges(n)[rank % co.cols]
+        full[r0:r1, c0:c1] = blk
+    return full
+
+
+def cp_pair_weighted_averaging(m_loc: Tensor, z_loc: Tensor, mask_loc: Tensor, pwa_packed, grid: CPGrid,
+                               add_residual: bool = False, local=None) -> Tensor:
+    """``m_loc[S_r, n_c, c_m]`` (MSA depth over grid rows, tokens over grid columns), ``z_loc[n_r, n_c, 128]``,
+    ``mask_loc[n_r, n_c]`` (pair mask block) -> the update of this rank's MSA block ``[S_r, n_c, c_m]`` (plus ``m_loc``
+    when ``add_residual``)."""
+    local = local or CudaAttentionLocal()
+    n_r, n_c = z_loc.shape[0], z_loc.shape[1]
+    n = n_r * grid.rows
+    if n_c * grid.cols != n or m_loc.shape[1] != n_c:
+        raise ValueError("blocks must tile a square pair tensor and the MSA's token block must match its columns")
+    logits_full = _assemble_bias(grid.all_gather(local.pwa_logits(z_loc, pwa_packed), grid.group), grid, n, False)
+    mask_full = _assemble_blocks(grid.all_gather(mask_loc.to(torch.uint8), grid.group), grid, n)
+    c0, c1 = grid.coords.my_cols(n)
+    mn_own = local.pwa_norm(m_loc, pwa_packed)
+    mn_all = torch.cat(grid.all_gather(mn_own, grid.row_group), dim=1)           # [S_r, N, c_m]: values of every token
+    return local.pwa_apply(mn_all, mn_own, logits_full[:, c0:c1], mask_full[c0:c1], pwa_packed,
+                           m_loc if add_residual else None)
 
 
 def cp_outer_product_mean(m_loc: Tensor, mask_loc: Tensor, row_count: Tensor, opm_packed, grid: CPGrid, local=None) -> Tensor:

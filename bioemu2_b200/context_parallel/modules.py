@@ -20,7 +20,8 @@ from ..outer_product_mean import OuterProductMean
 from ..transition import Transition
 from ..triangle_attention import TriangleAttention
 from ..triangle_multiplication import TriangleMultiplication
-from .attention import cp_attention_pair_bias, cp_outer_product_mean, cp_triangle_attention_
+from .attention import (cp_attention_pair_bias, cp_outer_product_mean, cp_pair_weighted_averaging,
+                        cp_triangle_attention_)
 from .mesh import CPGrid
 from .trimul import cp_triangle_multiplication_
 
@@ -199,6 +200,70 @@ class CPOuterProductMean(nn.Module):
 
             return DTensor.from_local(out, m.device_mesh, m.placements, run_check=False)
         return out
+
+
+class CPPairWeightedAveraging(nn.Module):
+    """``forward(m, z, mask)`` with ``m[B, S_r, n_c, c_m]`` (depth over grid rows, tokens over grid columns), the pair
+    block ``z[B, n_r, n_c, 128]`` and its pair mask; returns the update of this rank's MSA block
+    (reference: ``DistributedPairWeightedAveraging``, src/bioemu2/context_parallel/ops/pair_weighted_averaging.py:16-84)."""
+
+    def __init__(self, serial, grid, local=None) -> None:
+        super().__init__()
+        self.serial = serial
+        self.grid = _grid(grid)
+        self.local = local
+
+    def forward(self, m, z, mask, chunk_heads: bool = False, add_residual: bool = False):
+        ml, zl, kl = _local(m), _local(z), _local(mask)
+        packed = self.serial.packed()
+        out = torch.stack([cp_pair_weighted_averaging(ml[b], zl[b], kl[b], packed, self.grid, add_residual, self.local)
+                           for b in range(ml.shape[0])])
+        if hasattr(m, "to_local"):
+            from torch.distributed.tensor import DTensor
+
+            return DTensor.from_local(out, m.device_mesh, m.placements, run_check=False)
+        return out
+
+
+class CPPairMixerMSALayer(nn.Module):
+    """The MSA block on sharded tensors (reference: ``DistributedPairMixerMSALayer``,
+    src/bioemu2/context_parallel/modules/pairmixer.py:118-174): ``forward(z, m, token_mask, msa_mask, msa_row_count)
+    -> (z, m)``.  ``z[B, n_r, n_c, 128]`` is updated in place; ``m[B, S_r, n_c, c_m]`` has its depth over the grid's
+    rows and its tokens over the grid's columns; ``token_mask`` is the pair-mask block, ``msa_mask[B, S_r, n_c]``,
+    ``msa_row_count[B]`` the global number of valid MSA rows."""
+
+    def __init__(self, serial, grid, backend=None, local=None) -> None:
+        super().__init__()
+        grid = _grid(grid)
+        self.grid = grid
+        self.msa_transition = serial.msa_transition                      # per (row, token): no communication
+        self.pair_weighted_averaging = CPPairWeightedAveraging(serial.pair_weighted_averaging, grid, local)
+        self.outer_product_mean = CPOuterProductMean(serial.outer_product_mean, grid, local)
+        self.tri_mul_out = CPTriangleMultiplication(serial.tri_mul_out, grid, backend)
+        self.tri_mul_in = CPTriangleMultiplication(serial.tri_mul_in, grid, backend)
+        self.z_transition = CPTransition(serial.z_transition, grid)
+
+    def forward(self, z, m, token_mask, msa_mask, msa_row_count):
+        ml = self.pair_weighted_averaging(_local(m), z, token_mask, add_residual=True)       # a new tensor
+        ml = self._msa_transition_(ml)
+        zl = _local(z)
+        zl += self.outer_product_mean(ml, _local(msa_mask), msa_row_count).to(zl.dtype)
+        self.tri_mul_out(z, token_mask)
+        self.tri_mul_in(z, token_mask)
+        self.z_transition.forward_residual_(z)
+        if hasattr(m, "to_local"):
+            from torch.distributed.tensor import DTensor
+
+            ml = DTensor.from_local(ml, m.device_mesh, m.placements, run_check=False)
+        return z, ml
+
+    def _msa_transition_(self, ml):
+        fn = getattr(self.msa_transition, "forward_residual_", None)
+        return fn(ml) if fn is not None else ml + self.msa_transition(ml)
+
+
+DistributedPairWeightedAveraging = CPPairWeightedAveraging
+DistributedPairMixerMSALayer = CPPairMixerMSALayer
 
 
 class CPPairformerBlock(nn.Module):

@@ -288,20 +288,21 @@ gated_residual_rows_kernel(void* __restrict__ x, const void* __restrict__ h, con
 }
 
 // Row softmax of pair-bias logits with the reference's masking convention, one warp per row:
-//   w[h][i][j] = softmax_j( mask[i][j] ? logit[h][i][j] : -1e6 )      for j < n; columns n .. pitch-1 are written as 0.
+//   w[h][i][j] = softmax_j( mask[i][j] ? logit[h][i][j] : -1e6 )      for i < n_rows, j < n; columns n .. pitch-1 are
+//   written as 0.  (n_rows < n when a rank of a context-parallel grid holds only some rows of the weights.)
 // The logits arrive in base-2 units (pre-multiplied by log2(e), as the pair-bias projection kernel writes them), bf16;
 // the weights leave as bf16.  The row is read three times (maximum, sum, store): it is a few KB and stays in L1/L2.
 __global__ void __launch_bounds__(256)
 masked_softmax_rows_kernel(const __nv_bfloat16* __restrict__ logits, const uint8_t* __restrict__ mask,
-                           __nv_bfloat16* __restrict__ out, int H, int n, int pitch) {
+                           __nv_bfloat16* __restrict__ out, int H, int n_rows, int n, int pitch) {
   constexpr float kNegMasked = -1.0e6f * 1.4426950408889634f;
   const int lane = threadIdx.x & 31;
-  const long long rows = (long long)H * n;
+  const long long rows = (long long)H * n_rows;
   const long long warp_global = (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
   const long long warp_stride = (long long)gridDim.x * (blockDim.x >> 5);
   const int nvec = pitch >> 3;
   for (long long r = warp_global; r < rows; r += warp_stride) {
-    const int i = int(r % n);
+    const int i = int(r % n_rows);
     const __nv_bfloat16* src = logits + r * pitch;
     const uint8_t* mrow = mask + (long long)i * n;
     auto load_masked = [&](int v, float (&x)[8]) {

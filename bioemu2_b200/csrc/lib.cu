@@ -1380,14 +1380,15 @@ int b200_gated_residual_fwd(void* x, const void* h, const float* cond, int cond_
   return B200_OK;
 }
 
-int b200_masked_softmax_rows(const void* logits, const uint8_t* mask, void* out, int H, int n, int pitch,
+int b200_masked_softmax_rows(const void* logits, const uint8_t* mask, void* out, int H, int n_rows, int n, int pitch,
                              b200_stream_t stream) {
   if (int e = b200_check_device()) return e;
   B200_CHECK_ARG(logits && mask && out, "logits/mask/out is NULL");
-  B200_CHECK_ARG(H > 0 && n > 0 && pitch >= n && pitch % 8 == 0, "need H, n > 0 and a pitch >= n that is a multiple of 8");
+  B200_CHECK_ARG(H > 0 && n > 0 && n_rows > 0 && pitch >= n && pitch % 8 == 0,
+                 "need H, n_rows, n > 0 and a pitch >= n that is a multiple of 8");
   B200_CHECK_ARG(aligned(logits, 16) && aligned(out, 16), "logits/out must be 16-byte aligned");
-  masked_softmax_rows_kernel<<<grid_for((int64_t)H * n, 8), 256, 0, static_cast<cudaStream_t>(stream)>>>(
-      static_cast<const __nv_bfloat16*>(logits), mask, static_cast<__nv_bfloat16*>(out), H, n, pitch);
+  masked_softmax_rows_kernel<<<grid_for((int64_t)H * n_rows, 8), 256, 0, static_cast<cudaStream_t>(stream)>>>(
+      static_cast<const __nv_bfloat16*>(logits), mask, static_cast<__nv_bfloat16*>(out), H, n_rows, n, pitch);
   B200_AFTER_LAUNCH();
   return B200_OK;
 }

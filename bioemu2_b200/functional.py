@@ -711,28 +711,48 @@ def pair_weighted_averaging(m: Tensor, z: Tensor, mask: Tensor, w: PwaPacked, ad
     B, S, N, c_m = m.shape
     if c_m != w.c_m:
         raise ValueError(f"m has {c_m} channels, the module was built for {w.c_m}")
-    H, Nk = w.H, pad8(N)
     m = m.contiguous()
     m8 = mask_u8(mask)
     out = torch.empty_like(m)
-    bf = torch.bfloat16
     for b in range(B):
-        mn = rows_to_bf16(m[b].view(S * N, c_m), w.ln_m[0], w.ln_m[1], normalize=True)            # [S*N, c_m]
-        g = linear_bf16(mn, w.w_g)                                                                 # [S*N, H*32]
-        mn_p = mn.view(S, N, c_m)
-        if N != Nk:   # the token axis is the GEMM's column count, which the kernel wants in multiples of 8
-            mn_p = torch.zeros(S, Nk, c_m, dtype=bf, device=m.device)
-            mn_p[:, :N] = mn.view(S, N, c_m)
-        vT = torch.empty(H, S * 32, Nk, dtype=bf, device=m.device)                                 # [h][(s, d)][j]
-        for h in range(H):   # v_h^T[s] = W_m[h] . mn[s]^T : one A for all S batch items
-            bmm_nt_into(w.w_m[h * 32:(h + 1) * 32].unsqueeze(0).expand(S, 32, c_m), mn_p, vT[h].view(S, 32, Nk))
-        logits = pair_bias_slab(z[b], w.ln_z_w, w.ln_z_b, w.w_z, H)                                # [H, N, Nk], base 2
-        wts = torch.empty_like(logits)
-        _lib.check(lib.b200_masked_softmax_rows(logits.data_ptr(), m8[b].data_ptr(), wts.data_ptr(), H, N, Nk, _stream()))
-        o = torch.empty(H, N, S * 32, dtype=bf, device=m.device)
-        bmm_nt_into(wts, vT, o)                                                                    # o[h][i][(s, d)]
-        og = torch.empty(S * N, H * 32, dtype=bf, device=m.device)
-        _lib.check(lib.b200_pwa_gate(o.data_ptr(), g.data_ptr(), og.data_ptr(), S, N, H, _stream()))
-        linear_bf16(og, w.w_o, residual=m[b].view(S * N, c_m) if add_residual else None, out_dtype=m.dtype,
-                    out=out[b].view(S * N, c_m))
+        mn = pwa_norm(m[b], w)
+        logits = pair_bias_slab(z[b], w.ln_z_w, w.ln_z_b, w.w_z, w.H)                               # [H, N, Nk], base 2
+        pwa_apply(mn, mn, logits, m8[b], w, m[b] if add_residual else None, out[b])
+    return out
+
+
+def pwa_norm(m: Tensor, w: PwaPacked) -> Tensor:
+    """``norm_m`` of MSA rows ``m[S, n, c_m]`` as bf16."""
+    return rows_to_bf16(m.contiguous(), w.ln_m[0], w.ln_m[1], normalize=True)
+
+
+def pwa_apply(mn_all: Tensor, mn_own: Tensor, logits: Tensor, mask8: Tensor, w: PwaPacked, residual: Tensor | None,
+              out: Tensor) -> Tensor:
+    """The averaging itself for the token rows ``i`` a caller owns: ``mn_all[S, N, c_m]`` (normalised MSA, every token:
+    the values), ``mn_own[S, n_i, c_m]`` (the same for the owned tokens: the gate), ``logits[H, n_i, pad8(N)]`` (base-2
+    pair-bias logits of the owned rows), ``mask8[n_i, N]`` -> ``out[S, n_i, c_m]`` (plus ``residual``).  Single GPU:
+    ``n_i = N`` and the two MSA tensors are the same object; a rank of a context-parallel grid owns a block of tokens."""
+    S, N, c_m = mn_all.shape
+    n_i = mn_own.shape[1]
+    H, Nk = w.H, pad8(N)
+    bf = torch.bfloat16
+    if tuple(logits.shape) != (H, n_i, Nk) or tuple(mask8.shape) != (n_i, N) or tuple(out.shape) != (S, n_i, c_m):
+        raise ValueError(f"inconsistent shapes: logits {tuple(logits.shape)}, mask {tuple(mask8.shape)}, out {tuple(out.shape)}")
+    mn_p = mn_all
+    if N != Nk:   # the token axis is the GEMM's column count, which the kernel wants in multiples of 8
+        mn_p = torch.zeros(S, Nk, c_m, dtype=bf, device=mn_all.device)
+        mn_p[:, :N] = mn_all
+    vT = torch.empty(H, S * 32, Nk, dtype=bf, device=mn_all.device)                                # [h][(s, d)][j]
+    for h in range(H):   # v_h^T[s] = W_m[h] . mn[s]^T : one A for all S batch items
+        bmm_nt_into(w.w_m[h * 32:(h + 1) * 32].unsqueeze(0).expand(S, 32, c_m), mn_p, vT[h].view(S, 32, Nk))
+    wts = torch.empty_like(logits)
+    _lib.check(lib.b200_masked_softmax_rows(logits.data_ptr(), mask8.contiguous().data_ptr(), wts.data_ptr(), H, n_i, N, Nk,
+                                            _stream()))
+    o = torch.empty(H, n_i, S * 32, dtype=bf, device=mn_all.device)
+    bmm_nt_into(wts, vT, o)                                                                        # o[h][i][(s, d)]
+    g = linear_bf16(mn_own.contiguous().view(S * n_i, c_m), w.w_g)                                 # [S*n_i, H*32]
+    og = torch.empty(S * n_i, H * 32, dtype=bf, device=mn_all.device)
+    _lib.check(lib.b200_pwa_gate(o.data_ptr(), g.data_ptr(), og.data_ptr(), S, n_i, H, _stream()))
+    linear_bf16(og, w.w_o, residual=residual.view(S * n_i, c_m) if residual is not None else None, out_dtype=out.dtype,
+                out=out.view(S * n_i, c_m))
     return out

@@ -426,12 +426,13 @@ int b200_window_attention_fwd(const void* qkv, const void* gate, const float* bi
  * b200_bmm_nt (proj_m written transposed per head; the weighted average itself) and the two kernels below.
  *
  * b200_masked_softmax_rows  w[h][i][j] = softmax_j(mask[i][j] ? logits[h][i][j] : -1e6) (:141-142); logits bf16 in base-2
- *                           units [H][n][pitch] as b200_pair_bias_fwd writes them, mask one byte per pair [n][n],
- *                           w bf16 [H][n][pitch] with zeros in columns n .. pitch-1.
+ *                           units [H][n_rows][pitch] as b200_pair_bias_fwd writes them, mask one byte per pair
+ *                           [n_rows][n], w bf16 [H][n_rows][pitch] with zeros in columns n .. pitch-1.  n_rows == n
+ *                           for the whole weight matrix; a rank of a context-parallel grid passes the rows it owns.
  * b200_pwa_gate             og[(s,i)][h*32+d] = sigmoid(g[(s,i)][h*32+d]) * o[h][i][s*32+d] (:145-151): gating and the
  *                           re-layout from per-head products to MSA rows; heads of 32 channels.
  * ------------------------------------------------------------------------------------------------- */
-int b200_masked_softmax_rows(const void* logits, const uint8_t* mask, void* out, int H, int n, int pitch,
+int b200_masked_softmax_rows(const void* logits, const uint8_t* mask, void* out, int H, int n_rows, int n, int pitch,
                              b200_stream_t stream);
 int b200_pwa_gate(const void* o, const void* g, void* og, int S, int n, int H, b200_stream_t stream);
 

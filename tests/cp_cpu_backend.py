@@ -111,3 +111,23 @@ class CpuAttentionLocal:
         a, b = mp.chunk(2, dim=-1)
         z = torch.einsum("sic,sjd->ijcd", a, b[:, j0:j0 + nj]).reshape(a.shape[1], nj, -1) * inv_count.to(m_rows.dtype)
         return O.linear(z, w["proj_o.weight"], w["proj_o.bias"] if add_bias else None)
+
+    # ---- pair-weighted averaging (logits in natural-log units here; the GPU path carries them in base-2 units)
+    def pwa_logits(self, z_slab, packed):
+        w = packed.w
+        zb = O.linear(O.layer_norm(z_slab, w["norm_z.weight"], w.get("norm_z.bias")), w["proj_z.weight"])
+        return _pad_last(zb.permute(2, 0, 1))
+
+    def pwa_norm(self, m_loc, packed):
+        return O.layer_norm(m_loc, packed.w["norm_m.weight"], packed.w["norm_m.bias"])
+
+    def pwa_apply(self, mn_all, mn_own, logits, mask_rows, packed, residual):
+        w, H = packed.w, packed.H
+        S, n, _ = mn_all.shape
+        n_i = mn_own.shape[1]
+        v = O.linear(mn_all, w["proj_m.weight"]).view(S, n, H, -1)
+        b = torch.where(mask_rows.bool()[None], logits[:, :, :n], torch.full_like(logits[:, :, :n], -1e6))
+        o = torch.einsum("hij,sjhd->sihd", b.softmax(dim=-1), v).reshape(S, n_i, -1)
+        out = O.linear(torch.sigmoid(O.linear(mn_own, w["proj_g.weight"])) * o, w["proj_o.weight"])
+        return out + residual if residual is not None else out
+

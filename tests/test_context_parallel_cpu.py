@@ -106,7 +106,7 @@ def _attn_worker(rank, world, rows, cols, port, n, q):
     dist.init_process_group("gloo", rank=rank, world_size=world)
     try:
         from bioemu2_b200.context_parallel import (CPGrid, cp_attention_pair_bias, cp_outer_product_mean,
-                                                   cp_triangle_attention_, shard_range)
+                                                   cp_pair_weighted_averaging, cp_triangle_attention_, shard_range)
         from cp_cpu_backend import CpuAttentionLocal, Packed
 
         grid = CPGrid(rows, cols)
@@ -146,6 +146,12 @@ def _attn_worker(rank, world, rows, cols, port, n, q):
         out = cp_outer_product_mean(m[0, s0:s1, c0:c1].contiguous(), mm[0, s0:s1, c0:c1].contiguous(), row_count,
                                     Packed(wo), grid, local=loc)
         errs["opm"] = float((out - grid.shard_pair(ref)[0]).abs().max())
+        # ---- pair-weighted averaging: same MSA sharding, weights from the pair block, a random pair mask
+        wp = dbl(H.pwa_weights(g))
+        ref = m + O.pair_weighted_averaging(m, z, pm, wp)
+        out = cp_pair_weighted_averaging(m[0, s0:s1, c0:c1].contiguous(), grid.shard_pair(z)[0], grid.shard_pair(pm)[0],
+                                         Packed(wp, 8), grid, add_residual=True, local=loc)
+        errs["pwa"] = float((out - ref[0, s0:s1, c0:c1]).abs().max())
         q.put((rank, errs))
     finally:
         dist.destroy_process_group()
@@ -153,7 +159,8 @@ def _attn_worker(rank, world, rows, cols, port, n, q):
 
 @pytest.mark.parametrize("rows,cols,n", [(1, 2, 12), (2, 2, 12), (2, 1, 12)])
 def test_cp_attention_ops_match_serial_on_gloo(rows, cols, n):
-    """Sharded pair-bias attention, triangle attention (both nodes) and outer product mean against the serial oracle
+    """Sharded pair-bias attention, triangle attention (both nodes), outer product mean and pair-weighted averaging
+    against the serial oracle
     (reference's analogous tests: tests/context_parallel/ops/test_attention.py atol 5e-7, test_outer_product_mean.py)."""
     world = rows * cols
     ctx = mp.get_context("spawn")

@@ -97,11 +97,12 @@ def _run_block_rank(rank, world, rows, cols, port, n, q):
     try:
         import bioemu2_b200 as b
         from bioemu2_b200.context_parallel import (CPConditionedTransformerLayer, CPGrid, CPOuterProductMean,
-                                                   CPPairformerBlock, shard_range)
+                                                   CPPairformerBlock, CPPairMixerMSALayer, shard_range)
 
         torch.manual_seed(21)  # same seed on every rank: replicated weights
         blk = b.PairformerBlock().eval().to(dev)
         opm = b.OuterProductMean(64, 32, 128).eval().to(dev)
+        msa = b.PairMixerMSALayer(token_s=384, msa_s=64, token_z=128).eval().to(dev)
         tokblk = b.ConditionedTransformerLayer(dim=768, dim_pairwise=128, dim_cond=768, heads=16, transition_hidden=3072,
                                                lns_scale=0.5).eval().to(dev)
         with torch.no_grad():
@@ -138,6 +139,14 @@ def _run_block_rank(rank, world, rows, cols, port, n, q):
             a_out = cpt(a_loc, z_blk, c_loc, t_loc, 2)
             cpt.attention.prepare_static(z_blk)
             a_out_static = cpt(a_loc, z_blk, c_loc, t_loc, 2)
+            # the MSA block: pair-weighted averaging, MSA transition, outer product mean, triangle multiplications
+            pm = tok[:, :, None] & tok[:, None, :]
+            z2_ref, m2_ref = msa(None, z.to(dev), m.to(dev), pm.to(dev), mm.to(dev))[1:]
+            z2_loc = grid.shard_pair(z).to(dev)
+            z2_out, m2_out = CPPairMixerMSALayer(msa, grid)(
+                z2_loc, m[:, s0:s1, c0:c1].contiguous().to(dev), grid.shard_pair(pm).to(dev),
+                mm[:, s0:s1, c0:c1].contiguous().to(dev), mm.any(-1).sum(1).to(dev))
+            assert z2_out.data_ptr() == z2_loc.data_ptr()
         torch.cuda.synchronize()
         rel = lambda x, e: float((x - e).abs().max() / e.abs().max())  # noqa: E731  (every cell, masked ones included)
         errs = {
@@ -146,6 +155,8 @@ def _run_block_rank(rank, world, rows, cols, port, n, q):
             "opm": rel(o_out[0], o_ref[0, r0:r1, c0:c1]),
             "token_block": rel(a_out, a_ref[:, r0:r1]),
             "token_block_static_bias": rel(a_out_static, a_ref[:, r0:r1]),
+            "msa_layer_z": rel(z2_out[0], z2_ref[0, r0:r1, c0:c1]),
+            "msa_layer_m": rel(m2_out[0], m2_ref[0, s0:s1, c0:c1]),
         }
         q.put((rank, errs, b._lib.device_status()))
     finally:
