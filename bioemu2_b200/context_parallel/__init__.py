@@ -12,6 +12,10 @@ from .modules import (
     DistributedPairMixerModule,
     CPOuterProductMean,
     CPPairMixerMSALayer,
+    CPPairMixerMSAModule,
+    CPPairMixerSequenceEmbedder,
+    DistributedPairMixerMSAModule,
+    PairMixerSequenceEmbedderDistributed,
     CPPairWeightedAveraging,
     DistributedPairMixerMSALayer,
     DistributedPairWeightedAveraging,
@@ -31,5 +35,6 @@ __all__ = [
     "DistributedPairMixerModule", "CPAttentionPairBias", "CPOuterProductMean", "CPPairformerBlock", "CPPairformerModule", "CPPairMixerLayer", "CPPairMixerModule", "CPTransition",
     "CPTriangleAttention", "CPTriangleMultiplication", "cp_attention_pair_bias", "cp_outer_product_mean",
     "cp_triangle_attention_", "cp_triangle_multiplication_", "cp_pair_weighted_averaging", "CPPairMixerMSALayer",
+    "CPPairMixerMSAModule", "CPPairMixerSequenceEmbedder", "DistributedPairMixerMSAModule", "PairMixerSequenceEmbedderDistributed",
     "CPPairWeightedAveraging", "DistributedPairMixerMSALayer", "DistributedPairWeightedAveraging",
 ]

@@ -262,8 +262,86 @@ class CPPairMixerMSALayer(nn.Module):
         return fn(ml) if fn is not None else ml + self.msa_transition(ml)
 
 
+class CPPairMixerMSAModule(nn.Module):
+    """The MSA module on sharded tensors (reference: ``DistributedPairMixerMSAModule``,
+    src/bioemu2/context_parallel/modules/pairmixer.py:177-263).  ``forward(z, emb, msa, msa_mask, has_deletion,
+    deletion_value, msa_paired, token_pad_mask) -> z``: ``z[B, n_r, n_c, 128]`` is this rank's pair block (updated in
+    place), the MSA tensors are this rank's ``[B, S_r, n_c, ...]`` block (depth over grid rows, tokens over grid
+    columns), ``emb[B, T, .]`` and ``token_pad_mask[B, T]`` are replicated."""
+
+    def __init__(self, serial, grid, backend=None, local=None) -> None:
+        super().__init__()
+        self.grid = _grid(grid)
+        self.serial = serial
+        self.layers = nn.ModuleList(CPPairMixerMSALayer(layer, self.grid, backend, local) for layer in serial.layers)
+
+    def forward(self, z, emb, msa, msa_mask, has_deletion, deletion_value, msa_paired, token_pad_mask):
+        import torch.distributed as dist
+
+        n = token_pad_mask.shape[1]
+        (r0, r1), (c0, c1) = self.grid.coords.my_rows(n), self.grid.coords.my_cols(n)
+        m = self.serial.embed_msa(emb, _local(msa), _local(has_deletion), _local(deletion_value),
+                                  _local(msa_paired) if msa_paired is not None else None, tokens=slice(c0, c1))
+        tok = token_pad_mask.bool()
+        token_mask = (tok[:, r0:r1, None] & tok[:, None, c0:c1]).contiguous()
+        mk = _local(msa_mask)
+        # global number of MSA rows with at least one valid token: the per-row flags are combined over the row group
+        # (token blocks), then counted over the column group (depth slices)
+        has_any = mk.bool().any(dim=-1).to(torch.int32)                     # [B, S_r]
+        if self.grid.cols > 1:
+            dist.all_reduce(has_any, op=dist.ReduceOp.MAX, group=self.grid.row_group)
+        count = has_any.sum(dim=1)
+        if self.grid.rows > 1:
+            dist.all_reduce(count, group=self.grid.col_group)
+        for layer in self.layers:
+            z, m = layer(z, m, token_mask, mk, count)
+        return z
+
+
+class CPPairMixerSequenceEmbedder(nn.Module):
+    """The recycling trunk on an R x C grid (reference: ``PairMixerSequenceEmbedderDistributed``,
+    src/bioemu2/context_parallel/modules/pairmixer.py:266-...).  ``forward(s_inputs, feats, num_steps_recycle)`` with
+    ``s_inputs`` and ``feats["token_pad_mask"]`` replicated, the MSA features as this rank's ``[B, S_r, n_c, ...]`` block,
+    and ``feats["pair_init_terms"]`` (the feature encoders' pair terms) as this rank's ``[B, n_r, n_c, 128]`` block.
+    Returns the replicated single representation and this rank's block of the pair representation."""
+
+    def __init__(self, serial, grid, backend=None, local=None) -> None:
+        super().__init__()
+        self.grid = _grid(grid)
+        self.serial = serial
+        self.msa_module = CPPairMixerMSAModule(serial.msa_module, self.grid, backend, local)
+        self.pairmixer_module = CPPairMixerModule(serial.pairmixer_module, self.grid, backend)
+
+    def forward(self, s_inputs, feats: dict, num_steps_recycle: int = 0):
+        from .. import functional as F
+
+        e = self.serial
+        if num_steps_recycle < 0:
+            raise ValueError("num_steps_recycle must be non-negative")
+        n = s_inputs.shape[1]
+        (r0, r1), (c0, c1) = self.grid.coords.my_rows(n), self.grid.coords.my_cols(n)
+        xb = e._lin["s_init"].operand(s_inputs)
+        s_init = e._lin["s_init"](xb)
+        a, c = e._lin["z_init_1"](xb), e._lin["z_init_2"](xb)
+        terms = feats.get("pair_init_terms")
+        z_init = F.pair_outer_sum(a[:, r0:r1].contiguous(), c[:, c0:c1].contiguous(),
+                                  _local(terms).float().contiguous() if terms is not None else None)
+        tok = feats["token_pad_mask"].bool()
+        pair_mask = (tok[:, r0:r1, None] & tok[:, None, c0:c1]).to(torch.uint8).contiguous()
+        s, z = torch.zeros_like(s_init), torch.zeros_like(z_init)
+        for _ in range(num_steps_recycle + 1):
+            s = e._recycle(s, s_init, e.s_norm, "s_recycle")          # replicated: every rank computes the whole track
+            z = e._recycle(z, z_init, e.z_norm, "z_recycle")          # per pair: the local block
+            z = self.msa_module(z, s_inputs, feats["msa"], feats["msa_mask"], feats["has_deletion"],
+                                feats["deletion_value"], feats.get("msa_paired"), feats["token_pad_mask"])
+            z = self.pairmixer_module(z, pair_mask)
+        return s, z
+
+
 DistributedPairWeightedAveraging = CPPairWeightedAveraging
 DistributedPairMixerMSALayer = CPPairMixerMSALayer
+DistributedPairMixerMSAModule = CPPairMixerMSAModule
+PairMixerSequenceEmbedderDistributed = CPPairMixerSequenceEmbedder
 
 
 class CPPairformerBlock(nn.Module):

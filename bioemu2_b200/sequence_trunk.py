@@ -81,6 +81,18 @@ class PairMixerMSAModule(nn.Module):
                 deletion_value: Tensor, msa_paired: Tensor, token_pad_mask: Tensor) -> tuple[Tensor | None, Tensor]:
         if self.training:
             raise RuntimeError("bioemu2_b200 modules are inference-only: call .eval()")
+        m = self.embed_msa(emb, msa, has_deletion, deletion_value, msa_paired)
+        tok = token_pad_mask.bool()
+        token_mask = tok.unsqueeze(-1) & tok.unsqueeze(-2)
+        for layer in self.layers:
+            s, z, m = layer(s, z, m, token_mask, msa_mask, False)
+        return s, z
+
+    def embed_msa(self, emb: Tensor, msa: Tensor, has_deletion: Tensor, deletion_value: Tensor, msa_paired: Tensor,
+                  tokens: slice | None = None) -> Tensor:
+        """``msa_proj(cat(msa, has_deletion, deletion_value[, msa_paired])) + s_proj(emb)[:, None]`` as fp32
+        ``[B, R, T, msa_s]`` (pairmixer.py:590-599).  ``tokens`` selects the token block a context-parallel rank holds:
+        the MSA tensors then cover that block only, ``emb`` stays whole."""
         B, R, T = msa.shape[:3]
         width = self.msa_proj.in_features
         # the MSA features as one zero-padded bf16 operand (one-hot rows and 0/1 flags are exact in bf16)
@@ -94,14 +106,12 @@ class PairMixerMSAModule(nn.Module):
         if nt + 2 + int(self.use_paired_feature) != width:
             raise ValueError(f"msa has {nt} feature columns, msa_proj expects {width - 2 - int(self.use_paired_feature)}")
         m = self._msa_proj(feat)                                    # fp32 [B, R, T, msa_s]
-        e = self._s_proj(self._s_proj.operand(emb))                 # fp32 [B, T, msa_s]
+        e = self._s_proj(self._s_proj.operand(emb))                 # fp32 [B, tokens, msa_s]
+        if tokens is not None:
+            e = e[:, tokens].contiguous()
         for b in range(B):
             F.add_rows(m[b], e[b], out=m[b])                        # broadcast over the MSA rows
-        tok = token_pad_mask.bool()
-        token_mask = tok.unsqueeze(-1) & tok.unsqueeze(-2)
-        for layer in self.layers:
-            s, z, m = layer(s, z, m, token_mask, msa_mask, False)
-        return s, z
+        return m
 
 
 class PairMixerSequenceEmbedder(nn.Module):

@@ -190,3 +190,75 @@ def test_cp_pairformer_block_and_opm_grid(rows, cols, n):
     if torch.cuda.device_count() < rows * cols:
         pytest.skip(f"needs {rows * cols} GPUs")
     _launch_block(rows, cols, n)
+
+
+# --------------------------------------------------------------------------------------------------------------
+# The recycling trunk (pair initialisation, recycling update, MSA module, PairMixer blocks) on a grid
+def _run_embedder_rank(rank, world, rows, cols, port, n, q):
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    os.environ.setdefault("NCCL_NVLS_ENABLE", "0")
+    torch.cuda.set_device(rank)
+    dev = torch.device("cuda", rank)
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=dev)
+    try:
+        import bioemu2_b200 as b
+        from bioemu2_b200.context_parallel import CPGrid, CPPairMixerSequenceEmbedder, shard_range
+
+        torch.manual_seed(31)  # same seed on every rank: replicated weights
+        emb = b.PairMixerSequenceEmbedder(384, 128, 100, msa_s=64, msa_blocks=2, num_blocks=2).eval().to(dev)
+        g = torch.Generator().manual_seed(32)
+        S = 8 * rows
+        s_inputs = torch.randn(1, n, 100, generator=g)
+        terms = torch.randn(1, n, n, 128, generator=g)
+        tok = torch.ones(1, n, dtype=torch.bool)
+        tok[0, n - 7:] = False
+        msa = torch.nn.functional.one_hot(torch.randint(0, 33, (1, S, n), generator=g), 33).float()
+        msa_mask = tok[:, None, :].expand(1, S, n).clone()
+        msa_mask[0, 2] = False
+        feats = dict(msa=msa, msa_mask=msa_mask, has_deletion=(torch.rand(1, S, n, generator=g) < 0.2).float(),
+                     deletion_value=torch.rand(1, S, n, generator=g), msa_paired=(torch.rand(1, S, n, generator=g) < 0.5).float(),
+                     token_pad_mask=tok, pair_init_terms=terms)
+        with torch.no_grad():
+            s_ref, z_ref = emb(s_inputs.to(dev), {k: v.to(dev) for k, v in feats.items()}, num_steps_recycle=1)
+        grid = CPGrid(rows, cols)
+        (r0, r1), (c0, c1) = grid.coords.my_rows(n), grid.coords.my_cols(n)
+        s0, s1 = shard_range(S, rows, grid.coords.r)
+        local = {k: v[:, s0:s1, c0:c1].contiguous().to(dev) for k, v in feats.items() if k not in ("token_pad_mask", "pair_init_terms")}
+        local["token_pad_mask"] = tok.to(dev)
+        local["pair_init_terms"] = terms[:, r0:r1, c0:c1].contiguous().to(dev)
+        with torch.no_grad():
+            s_out, z_out = CPPairMixerSequenceEmbedder(emb, grid)(s_inputs.to(dev), local, num_steps_recycle=1)
+        torch.cuda.synchronize()
+        rel = lambda x, e: float((x - e).abs().max() / e.abs().max())  # noqa: E731
+        q.put((rank, {"s": rel(s_out, s_ref), "z": rel(z_out[0], z_ref[0, r0:r1, c0:c1])}, b._lib.device_status()))
+    finally:
+        dist.destroy_process_group()
+
+
+def _launch_embedder(rows, cols, n):
+    world = rows * cols
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    port = 31900 + (os.getpid() + rows * 31 + cols * 17 + n) % 1500
+    procs = [ctx.Process(target=_run_embedder_rank, args=(r, world, rows, cols, port, n, q)) for r in range(world)]
+    for p in procs:
+        p.start()
+    for p in procs:
+        p.join(300)
+        assert p.exitcode == 0
+    for _ in range(world):
+        rank, errs, status = q.get(timeout=5)
+        assert status == 0, f"rank {rank}: device status {status:#x}"
+        assert max(errs.values()) < 1e-2, (rank, errs)
+
+
+def test_cp_sequence_embedder_1x1():
+    _launch_embedder(1, 1, 136)
+
+
+@pytest.mark.parametrize("rows,cols,n", [(1, 2, 144), (2, 2, 272)])
+def test_cp_sequence_embedder_grid(rows, cols, n):
+    if torch.cuda.device_count() < rows * cols:
+        pytest.skip(f"needs {rows * cols} GPUs")
+    _launch_embedder(rows, cols, n)
