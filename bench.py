@@ -389,7 +389,7 @@ def run_probe(args) -> None:
     print(json.dumps({"probe": args.probe, "tokens": N, "ms_per_call": ms, "device_status": status}), flush=True)
 
 
-def run_trunk_glue_probe(args, dev) -> None:
+def run_trunk_glue_probe(args, dev, emit: bool = True) -> dict:
     """The HBM-bound glue around the trunk blocks at --tokens: pair initialisation, the recycling update and pairwise
     conditioning, each timed alone with its algorithmic bytes (fp32 pair tensor, 512 B per pair)."""
     import bioemu2_b200 as b
@@ -424,10 +424,12 @@ def run_trunk_glue_probe(args, dev) -> None:
         gbs = nbytes / (ms * 1e-3) / 1e9
         out["legs"][name] = {"ms": ms, "min_bytes": nbytes, "gbs": gbs, "frac_of_hbm_peak": gbs / peak["hbm_gbs"]}
     out["device_status"] = b._lib.device_status()
-    print(json.dumps(out), flush=True)
+    if emit:
+        print(json.dumps(out), flush=True)
+    return out
 
 
-def run_window_attention_probe(args, dev) -> None:
+def run_window_attention_probe(args, dev, emit: bool = True) -> dict:
     """The atom transformer's sliding-window attention at 8 atoms per token of --tokens (windows of 32 queries, 128
     keys, 4 heads of 32, pair width 16), 8 samples sharing one pair tensor: the whole module and its two kernels."""
     import bioemu2_b200 as b
@@ -470,7 +472,9 @@ def run_window_attention_probe(args, dev) -> None:
     ka["fp32_tflops"] = flops / (ka["ms"] * 1e-3) / 1e12
     ka["bytes"] = qkv.numel() * 2 + gate.numel() * 2 + og.numel() * 2 + M * bias_bytes
     out["device_status"] = b._lib.device_status()
-    print(json.dumps(out), flush=True)
+    if emit:
+        print(json.dumps(out), flush=True)
+    return out
 
 
 def parity_stats(actual: torch.Tensor, expected: torch.Tensor) -> dict:
@@ -674,7 +678,7 @@ def run_b200(args) -> None:
             "gpu_launches_per_step": int(launches_per_step),
             "roofline": roofline, "ops": ops, "device_status": status,
         }
-        for k in ("torch_gpu_baseline", "larger_sizes"):
+        for k in ("torch_gpu_baseline", "larger_sizes", "trunk_glue", "atom_window_attention"):
             if k in extras:
                 line[k] = extras[k]
         if not args.no_cpu_baseline and world == 1:
@@ -764,6 +768,18 @@ def extra_ops(args, dev, b) -> dict:
         b.functional.release_workspaces()
         torch.cuda.empty_cache()
     out["larger_sizes"] = larger
+    # the glue around the trunk blocks and the atom transformer's window attention (the rows after the trunk itself)
+    try:
+        import types
+
+        pa = types.SimpleNamespace(tokens=args.tokens, steps=10, warmup=3)
+        out["trunk_glue"] = run_trunk_glue_probe(pa, dev, emit=False)["legs"]
+        torch.cuda.empty_cache()
+        wa = run_window_attention_probe(pa, dev, emit=False)
+        out["atom_window_attention"] = {"atoms": wa["atoms"], "samples": wa["samples"], **wa["legs"]}
+    except Exception as exc:  # must not cost the headline
+        out["trunk_glue"] = {"unavailable": f"{type(exc).__name__}: {exc}"[:200]}
+    torch.cuda.empty_cache()
     # the oracle's plain torch code on this GPU under bf16 autocast (cuBLAS / eager kernels)
     try:
         fn = oracle_block_fn(args.tokens, args.block, device=str(dev))
