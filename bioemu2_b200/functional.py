@@ -121,6 +121,8 @@ def trimul(x: Tensor, mask: Tensor, w: TriMulPacked, incoming: bool, add_residua
         out = torch.empty_like(x)
     elif out.dtype != x.dtype or out.shape != x.shape or not out.is_contiguous():
         raise ValueError("out must match x in shape and dtype and be contiguous")
+    if x.numel() == 0:  # empty batch or no tokens: nothing to launch (with a residual, out = x = empty)
+        return out
     m8 = mask_u8(mask)
     B, N = x.shape[0], x.shape[1]
     nbytes = lib.b200_trimul_workspace_bytes(N)
@@ -166,6 +168,8 @@ def transition(x: Tensor, w: TransitionPacked, add_residual: bool = False, out: 
     elif out.dtype != x.dtype or out.shape != x.shape or not out.is_contiguous():
         raise ValueError("out must match x in shape and dtype and be contiguous")
     rows = x.numel() // 128
+    if rows == 0:
+        return out
     use_norm = w.norm_w is not None
     _lib.check(lib.b200_transition_fwd(x.data_ptr(), out.data_ptr(), w.w13.data_ptr(), w.w3.data_ptr(),
                                        w.norm_w.data_ptr() if use_norm else None,
@@ -205,6 +209,10 @@ def outer_product_mean(m: Tensor, mask: Tensor, w: OpmPacked) -> Tensor:
     zd = _zdtype(m)
     m = m.contiguous()
     out = torch.empty(B, N, N, 128, dtype=m.dtype, device=m.device)
+    if out.numel() == 0:
+        return out
+    if S == 0:  # no MSA rows: the mean of nothing is zero, so every pair gets proj_o's bias
+        return out.copy_(w.f32[2].to(out.dtype).expand_as(out))
     m8 = mask_u8(mask)
     nbytes = lib.b200_opm_workspace_bytes(S, N)
     ws = workspace(nbytes, m.device)
@@ -271,6 +279,8 @@ def attention_pair_bias(s: Tensor, z: Tensor, mask: Tensor, w: ApbPacked, multip
     sd, zd = _zdtype(s), _zdtype(z)
     s, z = s.contiguous(), z.contiguous()
     out = torch.empty_like(s)
+    if out.numel() == 0:
+        return out
     m8 = mask_u8(mask)
     nbytes = lib.b200_apb_workspace_bytes(B, multiplicity, N, w.c_s, w.H)
     ws = workspace(nbytes, s.device)
@@ -315,6 +325,8 @@ def triangle_attention(x: Tensor, mask: Tensor, w: TriAttPacked, ending: bool, a
         out = torch.empty_like(x)
     elif out.dtype != x.dtype or out.shape != x.shape or not out.is_contiguous():
         raise ValueError("out must match x in shape and dtype and be contiguous")
+    if x.numel() == 0:
+        return out
     m8 = mask_u8(mask)
     B, N = x.shape[0], x.shape[1]
     nbytes = lib.b200_triatt_workspace_bytes(N)
@@ -337,6 +349,8 @@ def rows_to_bf16(x: Tensor, weight: Tensor | None = None, bias: Tensor | None = 
     x = x.contiguous()
     cols = x.shape[-1]
     y = torch.empty(x.shape, dtype=torch.bfloat16, device=x.device)
+    if y.numel() == 0:
+        return y
     w = weight.detach().float().contiguous() if weight is not None else None
     b = bias.detach().float().contiguous() if bias is not None else None
     _lib.check(lib.b200_rows_to_bf16(x.data_ptr(), y.data_ptr(), _ptr(w), _ptr(b), x.numel() // cols, cols, xd,
@@ -358,6 +372,8 @@ def linear_bf16(x: Tensor, w_bf16: Tensor, bias_f32: Tensor | None = None, resid
     if out is None:
         out = torch.empty(x.shape[:-1] + (fout,), dtype=out_dtype, device=x.device)
     od = _zdtype(out)
+    if rows == 0:
+        return out
     if residual is not None and (residual.dtype != out.dtype or residual.shape != out.shape or not residual.is_contiguous()):
         raise ValueError("residual must match the output in shape and dtype and be contiguous")
     _lib.check(lib.b200_linear_bf16(x.data_ptr(), w_bf16.data_ptr(), _ptr(bias_f32), _ptr(residual), out.data_ptr(),
@@ -374,6 +390,8 @@ def rows2_to_bf16(x1: Tensor, x2: Tensor, weight: Tensor | None = None, bias: Te
     x1, x2 = x1.contiguous(), x2.contiguous()
     c1, c2 = x1.shape[-1], x2.shape[-1]
     y = torch.empty(x1.shape[:-1] + (c1 + c2,), dtype=torch.bfloat16, device=x1.device)
+    if y.numel() == 0:
+        return y
     w = weight.detach().float().contiguous() if weight is not None else None
     b = bias.detach().float().contiguous() if bias is not None else None
     _lib.check(lib.b200_rows2_to_bf16(x1.data_ptr(), c1, x2.data_ptr(), c2, y.data_ptr(), _ptr(w), _ptr(b),
@@ -393,6 +411,8 @@ def pair_outer_sum(a: Tensor, c: Tensor, extra: Tensor | None = None) -> Tensor:
     a, c = a.contiguous(), c.contiguous()
     extra = extra.contiguous() if extra is not None else None
     z = torch.empty(B, ni, nj, D, dtype=torch.float32, device=a.device)
+    if z.numel() == 0:
+        return z
     for b in range(B):
         _lib.check(lib.b200_pair_outer_sum(a[b].data_ptr(), c[b].data_ptr(), extra[b].data_ptr() if extra is not None else None,
                                            z[b].data_ptr(), ni, nj, D, _stream()))
@@ -411,6 +431,8 @@ def add_rows(x: Tensor, y: Tensor, out: Tensor | None = None) -> Tensor:
     cols = x.shape[-1]
     if out is None:
         out = torch.empty_like(x)
+    if x.numel() == 0:
+        return out
     _lib.check(lib.b200_add_rows(x.data_ptr(), y.data_ptr(), out.data_ptr(), x.numel() // cols, y.numel() // cols, cols,
                                  _zdtype(y), _stream()))
     return out
@@ -448,6 +470,8 @@ def window_attention_pair_bias(s: Tensor, z: Tensor, mask: Tensor, w: WindowApbP
     if Wz != W or folded != B * M * NW or tuple(mask.shape) != (B * NW, W) or c_s != w.c_s or c_z != w.c_z:
         raise ValueError(f"inconsistent shapes: s {tuple(s.shape)}, z {tuple(z.shape)}, mask {tuple(mask.shape)}, "
                          f"multiplicity {M}")
+    if s.numel() == 0:
+        return torch.empty_like(s)
     sn = rows_to_bf16(s, w.ln_s_w, w.ln_s_b, normalize=w.ln_s_w is not None)
     qkv = linear_bf16(sn, w.w_qkv, bias_f32=w.b_qkv)
     gate = linear_bf16(sn, w.w_g)
@@ -467,6 +491,8 @@ def swiglu(h12: Tensor) -> Tensor:
     H = h12.shape[-1] // 2
     h12 = h12.contiguous()
     out = torch.empty(h12.shape[:-1] + (H,), dtype=torch.bfloat16, device=h12.device)
+    if out.numel() == 0:
+        return out
     _lib.check(lib.b200_swiglu_fwd(h12.data_ptr(), out.data_ptr(), h12.numel() // (2 * H), H, _stream()))
     return out
 
@@ -477,6 +503,8 @@ def adaln(x: Tensor, cond: Tensor, alpha_col: int, beta_col: int, lns: float) ->
     x = x.contiguous()
     cols = x.shape[-1]
     y = torch.empty(x.shape, dtype=torch.bfloat16, device=x.device)
+    if y.numel() == 0:
+        return y
     _lib.check(lib.b200_adaln_fwd(x.data_ptr(), cond.data_ptr(), cond.shape[-1], alpha_col, beta_col, float(lns),
                                   y.data_ptr(), x.numel() // cols, cols, xd, _stream()))
     return y
@@ -487,6 +515,8 @@ def gated_residual_(x: Tensor, h: Tensor, cond: Tensor, gamma_col: int) -> Tenso
     if not x.is_contiguous() or not h.is_contiguous():
         raise ValueError("gated_residual_ needs contiguous tensors")
     cols = x.shape[-1]
+    if x.numel() == 0:
+        return x
     _lib.check(lib.b200_gated_residual_fwd(x.data_ptr(), h.data_ptr(), cond.data_ptr(), cond.shape[-1], gamma_col,
                                            x.numel() // cols, cols, _zdtype(x), _zdtype(h), _stream()))
     return x
@@ -714,6 +744,8 @@ def pair_weighted_averaging(m: Tensor, z: Tensor, mask: Tensor, w: PwaPacked, ad
     m = m.contiguous()
     m8 = mask_u8(mask)
     out = torch.empty_like(m)
+    if out.numel() == 0:
+        return out
     for b in range(B):
         mn = pwa_norm(m[b], w)
         logits = pair_bias_slab(z[b], w.ln_z_w, w.ln_z_b, w.w_z, w.H)                               # [H, N, Nk], base 2
