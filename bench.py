@@ -150,7 +150,8 @@ def config_dict(args, impl_note: str, parallelism: str) -> dict:
     if "context parallel" in parallelism:
         launch = "eager launches (NCCL collectives between the kernels)"
     else:
-        launch = "eager" if args.no_graph else "CUDA graph replay of the step (value); eager launches (e2e)"
+        launch = "eager" if args.no_graph else ("CUDA graph replay of the step (value); trunk.graphed(...) - the public "
+                                                "graph-captured call - around pinned-memory copies (e2e)")
     return {
         "workload": f"Pairformer trunk forward, {args.blocks} blocks ({what}), N={args.tokens}, c_z=128, c_s=384, "
                     f"batch 1, last {pad_tokens(args.tokens)} tokens padded, seed 2",
@@ -571,14 +572,42 @@ def run_b200(args) -> None:
         ms = event_time_ms(timed_step, args.steps)
         barrier()
 
-        step_e2e()
+        e2e_step, e2e_graphed = step_e2e, False
+        if not args.no_graph:
+            # the public form of the same idea: trunk.graphed(...) captures the block loop once; a call copies the
+            # inputs in (here from pinned host memory), replays, and returns static output buffers
+            try:
+                g_trunk = trunk.graphed(s_dev, z_dev, tok_dev if composite else pair_mask.to(dev))
+                mask_pin = tok_pinned if composite else pm_pinned
+
+                def step_e2e_graphed():
+                    s_out, z_out = g_trunk(s_pinned, z_pinned, mask_pin)
+                    z_out_pinned.copy_(z_out, non_blocking=True)
+                    s_out_pinned.copy_(s_out, non_blocking=True)
+                    torch.cuda.current_stream().synchronize()
+
+                e2e_step, e2e_graphed = step_e2e_graphed, True
+            except Exception as exc:
+                print(f"trunk.graphed failed ({exc}); end-to-end step stays eager", file=sys.stderr)
+                torch.cuda.synchronize()
+        e2e_step()
         barrier()
         t0 = time.perf_counter()
         for _ in range(args.steps):
-            step_e2e()
+            e2e_step()
         torch.cuda.synchronize()
         e2e_ms = (time.perf_counter() - t0) * 1e3 / args.steps
         barrier()
+        e2e_eager_ms = None
+        if e2e_graphed:
+            step_e2e()
+            torch.cuda.synchronize()
+            t0 = time.perf_counter()
+            for _ in range(max(args.steps // 2, 2)):
+                step_e2e()
+            torch.cuda.synchronize()
+            e2e_eager_ms = (time.perf_counter() - t0) * 1e3 / max(args.steps // 2, 2)
+            del g_trunk
         clocks = sampler.stop() if rank == 0 else None
 
         # per-op timings on the same data (inputs > L2), for the rooflines
@@ -673,7 +702,10 @@ def run_b200(args) -> None:
             "config": config_dict(args, "hand-written sm_100a kernels through the C ABI (libb200pair.so)", par),
             "clocks": clocks,
             "e2e": {"value": world * cells / (e2e_ms * 1e-3), "unit": UNIT, "ms_per_step": e2e_ms,
-                    "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": z_host.numel() * 4 + s_host.numel() * 4},
+                    "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": z_host.numel() * 4 + s_host.numel() * 4,
+                    "call": "trunk.graphed(s, z, mask)(s_pinned, z_pinned, mask_pinned)" if e2e_graphed
+                            else "trunk(s, z, mask) (eager launches)",
+                    "ms_per_step_eager_forward": e2e_eager_ms},
             "gpu_launches": int(args.steps * launches_per_step),
             "gpu_launches_per_step": int(launches_per_step),
             "roofline": roofline, "ops": ops, "device_status": status,

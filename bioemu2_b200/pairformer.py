@@ -68,3 +68,10 @@ class PairformerModule(nn.Module):
             layer.forward_(s, z, token_mask, pm)
         _lib.raise_if_device_wait()  # a kernel whose bounded wait ran out earlier in the stack invalidates the result
         return s, z
+
+    def graphed(self, s: Tensor, z: Tensor, token_mask: Tensor):
+        """The block loop captured in a CUDA graph for inputs of these shapes: ``g = trunk.graphed(s, z, mask)`` once,
+        then ``s_out, z_out = g(s, z[, mask])`` per forward (see ``bioemu2_b200.graph``)."""
+        from .graph import GraphedTrunk
+
+        return GraphedTrunk(self, s, z, token_mask)

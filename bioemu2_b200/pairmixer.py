@@ -65,6 +65,13 @@ class PairMixerModule(nn.Module):
         _lib.raise_if_device_wait()  # a kernel whose bounded wait ran out earlier in the stack invalidates the result
         return s, z
 
+    def graphed(self, s: Tensor, z: Tensor, pair_mask: Tensor):
+        """The block loop captured in a CUDA graph for inputs of these shapes: ``g = trunk.graphed(s, z, pair_mask)``
+        once, then ``s_out, z_out = g(s, z[, pair_mask])`` per forward (see ``bioemu2_b200.graph``)."""
+        from .graph import GraphedTrunk
+
+        return GraphedTrunk(self, s, z, pair_mask)
+
 
 class PairMixerMSALayer(nn.Module):
     """The MSA block of the PairMixer trunk (src/bioemu2/biomoa/modules/pairmixer.py:614-757):
