@@ -161,10 +161,6 @@ triatt_proj_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constan
       for (int c = 0; c < 16; ++c) {
         uint32_t(&v)[32] = (c & 1) ? vb : va;
         uint8_t* stage = smem + STAGE_OFF + ((c >> 1) & 1) * kOperandHalf;
-        if ((c & 1) == 0) {  // the store that last used this staging tile has finished reading it
-          if (leader) tma_store_wait_read1();
-          named_bar_sync(1, 128);
-        }
         tmem_ld_wait();
         if (c == 7) {  // q, k read: the next tile's group A products may start; g, V^T must have landed
           tc_fence_before_sync();
@@ -178,6 +174,7 @@ triatt_proj_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constan
           tc_fence_before_sync();
           mbar_arrive(&acc_empty[1]);
         }
+        uint4 packed[4];
 #pragma unroll
         for (int g = 0; g < 4; ++g) {
           float y[8];
@@ -187,9 +184,15 @@ triatt_proj_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constan
 #pragma unroll
             for (int e = 0; e < 8; ++e) y[e] = sigmoid_fast(y[e] + gb_s[(c - 8) * 32 + g * 8 + e]);  // the gate leaves activated
           }
-          *reinterpret_cast<uint4*>(stage + sw128_offset(r, (c & 1) * 4 + g)) = make_uint4(
-              pack_bf16x2(y[0], y[1]), pack_bf16x2(y[2], y[3]), pack_bf16x2(y[4], y[5]), pack_bf16x2(y[6], y[7]));
+          packed[g] = make_uint4(pack_bf16x2(y[0], y[1]), pack_bf16x2(y[2], y[3]), pack_bf16x2(y[4], y[5]),
+                                 pack_bf16x2(y[6], y[7]));
         }
+        if ((c & 1) == 0) {  // the store that last used this staging tile has finished reading it (the wait hides
+          if (leader) tma_store_wait_read1();  // behind the conversion above)
+          named_bar_sync(1, 128);
+        }
+#pragma unroll
+        for (int g = 0; g < 4; ++g) *reinterpret_cast<uint4*>(stage + sw128_offset(r, (c & 1) * 4 + g)) = packed[g];
         if (c & 1) {
           fence_proxy_async_smem();
           named_bar_sync(1, 128);
