@@ -80,7 +80,7 @@ def _worker(rank, world, rows, cols, port, n_tokens, q):
         dist.destroy_process_group()
 
 
-@pytest.mark.parametrize("rows,cols,n_tokens", [(1, 2, 12), (2, 1, 12), (2, 2, 12), (1, 4, 8), (4, 1, 8)])
+@pytest.mark.parametrize("rows,cols,n_tokens", [(1, 2, 12), (2, 1, 12), (2, 2, 12), (1, 4, 8), (4, 1, 8), (2, 4, 16)])
 def test_cp_trimul_matches_serial_on_gloo(rows, cols, n_tokens):
     """Outgoing then incoming triangle multiplication, sharded, against the serial oracle (reference's analogous
     test: tests/context_parallel/ops/test_trimul_serial_vs_cp.py, fp32 atol 2e-6; fp64 here)."""
@@ -157,7 +157,7 @@ def _attn_worker(rank, world, rows, cols, port, n, q):
         dist.destroy_process_group()
 
 
-@pytest.mark.parametrize("rows,cols,n", [(1, 2, 12), (2, 2, 12), (2, 1, 12)])
+@pytest.mark.parametrize("rows,cols,n", [(1, 2, 12), (2, 2, 12), (2, 1, 12), (2, 4, 16)])
 def test_cp_attention_ops_match_serial_on_gloo(rows, cols, n):
     """Sharded pair-bias attention, triangle attention (both nodes), outer product mean and pair-weighted averaging
     against the serial oracle
