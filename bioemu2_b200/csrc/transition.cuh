@@ -193,73 +193,6 @@ transition_kernel(const __grid_constant__ CUtensorMap tmW1, const __grid_constan
       else
         regs.template load<F32, false>(pt, rp, gamma, beta, p.eps, 0.5f);
     };
-    // Output of tile number `ot` of this CTA (global tile index `otile`): CPS columns (64 B) at a time, the next
-    // TMEM load in flight, through this half-group's staging tile and TMA.
-    constexpr int CPS = F32 ? 16 : 32;
-    const int half = (warp - 8) >> 2;          // which 64 channels
-    const int quarter = warp & 3;
-    const int r = quarter * 32 + lane;         // pair row of the tile == TMEM lane
-    const bool leader = (pt & 127) == 0;
-    const bool reduce = p.add_residual && p.out == p.x;
-    const bool read_res = p.add_residual && !reduce;
-    const uint32_t row_off = r * 64, row_xor = (r >> 1) & 3;
-    auto store_out = [&](int ot, int otile) {
-      const int o = ot & 1;
-      mbar_wait(&out_full[o], (ot >> 1) & 1, 41);
-      tc_fence_after_sync();
-      const long long row = (long long)otile * 128 + r;
-      const bool valid = row < p.rows;
-      const uint8_t* xrow = static_cast<const uint8_t*>(p.x) + row * kD * zbytes<F32>();
-      const uint32_t o_addr = tmem_addr(tmem_base, quarter * 32, 256 + o * 128 + half * 64);
-      uint32_t va[CPS], vb[CPS];
-      if (F32) tmem_ld_32x16(o_addr, reinterpret_cast<uint32_t(&)[16]>(va));
-      else tmem_ld_32x32(o_addr, reinterpret_cast<uint32_t(&)[32]>(va));
-#pragma unroll
-      for (int k = 0; k < 64 / CPS; ++k) {
-        uint32_t(&v)[CPS] = (k & 1) ? vb : va;
-        uint8_t* stage = smem + STAGE_OFF + half * 8192;
-        if (leader) tma_store_wait_read0();  // the previous store has read the staging tile
-        named_bar_sync(1 + half, 128);
-        tmem_ld_wait();
-        if (k + 1 < 64 / CPS) {
-          if (F32) tmem_ld_32x16(o_addr + (k + 1) * CPS, reinterpret_cast<uint32_t(&)[16]>((k & 1) ? va : vb));
-          else tmem_ld_32x32(o_addr + (k + 1) * CPS, reinterpret_cast<uint32_t(&)[32]>((k & 1) ? va : vb));
-        } else {
-          tc_fence_before_sync();
-          mbar_arrive(&out_empty[o]);
-        }
-        const int ch0 = half * 64 + k * CPS;
-#pragma unroll
-        for (int q = 0; q < CPS / 8; ++q) {
-          float zr[8];
-          if (read_res && valid) {
-            load8<F32>(xrow, ch0 + q * 8, zr);
-          } else {
-#pragma unroll
-            for (int e = 0; e < 8; ++e) zr[e] = 0.f;
-          }
-#pragma unroll
-          for (int e = 0; e < 8; ++e) zr[e] = fmaf(2.0f, __uint_as_float(v[q * 8 + e]), zr[e]);
-          if (F32) {
-            *reinterpret_cast<float4*>(stage + row_off + (((q * 2) ^ row_xor) << 4)) = make_float4(zr[0], zr[1], zr[2], zr[3]);
-            *reinterpret_cast<float4*>(stage + row_off + (((q * 2 + 1) ^ row_xor) << 4)) =
-                make_float4(zr[4], zr[5], zr[6], zr[7]);
-          } else {
-            *reinterpret_cast<uint4*>(stage + row_off + ((q ^ row_xor) << 4)) = make_uint4(
-                pack_bf16x2(zr[0], zr[1]), pack_bf16x2(zr[2], zr[3]), pack_bf16x2(zr[4], zr[5]), pack_bf16x2(zr[6], zr[7]));
-          }
-        }
-        fence_proxy_async_smem();
-        named_bar_sync(1 + half, 128);
-        if (leader) {
-          if (reduce)
-            tma_reduce_add_2d(&tmO, stage, ch0, otile * 128);
-          else
-            tma_store_2d(&tmO, stage, ch0, otile * 128);
-          tma_store_commit();
-        }
-      }
-    };
     int it = 0;
     int tile = blockIdx.x;
     if (tile < p.num_tiles) load_tile(tile);
@@ -270,17 +203,84 @@ transition_kernel(const __grid_constant__ CUtensorMap tmW1, const __grid_constan
       mbar_arrive(x_full);
       const int next = tile + gridDim.x;
       if (next < p.num_tiles) load_tile(next);
-      if (it > 0) store_out(it - 1, tile - gridDim.x);
     }
-    if (it > 0) store_out(it - 1, tile - gridDim.x);
-    if (leader) tma_store_wait0();
   } else {
     // ------------------------------------------------------------------ SwiGLU epilogues
-    const int grp = warp >> 2;             // 0: even chunks / even tiles, 1: odd
+    // These warps also drain the finished output accumulators: group `grp` owns output channels 64*grp .. +63 and
+    // stores them in 64 / CPS parts (CPS columns = 64 B at a time through the group's staging tile and TMA), one
+    // part after each of its SwiGLU chunks of the NEXT tile, so the drain of tile i - 1 is spread over tile i
+    // and neither the chunk pipeline nor the LayerNorm producers wait for it.
+    const int grp = warp >> 2;             // 0: even chunks, 1: odd chunks
     const int quarter = warp & 3;
     const int r = quarter * 32 + lane;     // pair row of the tile == TMEM lane
+    constexpr int CPS = F32 ? 16 : 32;
+    constexpr int PARTS = 64 / CPS;
+    const int half = grp;
+    const bool leader = (threadIdx.x & 127) == 0;
+    const bool reduce = p.add_residual && p.out == p.x;
+    const bool read_res = p.add_residual && !reduce;
+    const uint32_t row_off = r * 64, row_xor = (r >> 1) & 3;
+    uint8_t* stage = smem + STAGE_OFF + half * 8192;
+    auto drain_part = [&](int ot, int otile, int k) {  // part k of output tile number `ot` (global tile `otile`)
+      const int o = ot & 1;
+      const uint32_t o_addr = tmem_addr(tmem_base, quarter * 32, 256 + o * 128 + half * 64);
+      if (k == 0) {
+        mbar_wait(&out_full[o], (ot >> 1) & 1, 41);
+        tc_fence_after_sync();
+      }
+      const long long row = (long long)otile * 128 + r;
+      const bool valid = row < p.rows;
+      const uint8_t* xrow = static_cast<const uint8_t*>(p.x) + row * kD * zbytes<F32>();
+      uint32_t v[CPS];
+      if (F32) tmem_ld_32x16(o_addr + k * CPS, reinterpret_cast<uint32_t(&)[16]>(v));
+      else tmem_ld_32x32(o_addr + k * CPS, reinterpret_cast<uint32_t(&)[32]>(v));
+      tmem_ld_wait();
+      if (k == PARTS - 1) {
+        tc_fence_before_sync();
+        mbar_arrive(&out_empty[o]);
+      }
+      const int ch0 = half * 64 + k * CPS;
+      float zr[CPS / 8][8];
+#pragma unroll
+      for (int q = 0; q < CPS / 8; ++q) {
+        if (read_res && valid) {
+          load8<F32>(xrow, ch0 + q * 8, zr[q]);
+        } else {
+#pragma unroll
+          for (int e = 0; e < 8; ++e) zr[q][e] = 0.f;
+        }
+#pragma unroll
+        for (int e = 0; e < 8; ++e) zr[q][e] = fmaf(2.0f, __uint_as_float(v[q * 8 + e]), zr[q][e]);
+      }
+      if (leader) tma_store_wait_read0();  // the previous store has read the staging tile
+      named_bar_sync(1 + half, 128);
+#pragma unroll
+      for (int q = 0; q < CPS / 8; ++q) {
+        if (F32) {
+          *reinterpret_cast<float4*>(stage + row_off + (((q * 2) ^ row_xor) << 4)) =
+              make_float4(zr[q][0], zr[q][1], zr[q][2], zr[q][3]);
+          *reinterpret_cast<float4*>(stage + row_off + (((q * 2 + 1) ^ row_xor) << 4)) =
+              make_float4(zr[q][4], zr[q][5], zr[q][6], zr[q][7]);
+        } else {
+          *reinterpret_cast<uint4*>(stage + row_off + ((q ^ row_xor) << 4)) =
+              make_uint4(pack_bf16x2(zr[q][0], zr[q][1]), pack_bf16x2(zr[q][2], zr[q][3]), pack_bf16x2(zr[q][4], zr[q][5]),
+                         pack_bf16x2(zr[q][6], zr[q][7]));
+        }
+      }
+      fence_proxy_async_smem();
+      named_bar_sync(1 + half, 128);
+      if (leader) {
+        if (reduce)
+          tma_reduce_add_2d(&tmO, stage, ch0, otile * 128);
+        else
+          tma_store_2d(&tmO, stage, ch0, otile * 128);
+        tma_store_commit();
+      }
+    };
     int it = 0;
-    for (int tile = blockIdx.x; tile < p.num_tiles; tile += gridDim.x, ++it) {
+    int tile = blockIdx.x;
+    for (; tile < p.num_tiles; tile += gridDim.x, ++it) {
+      int part = 0;
       for (int c = grp; c < CHUNKS; c += 2) {
         const int g = it * CHUNKS + c;
         const int b = g & 1;  // == grp
@@ -311,8 +311,18 @@ transition_kernel(const __grid_constant__ CUtensorMap tmW1, const __grid_constan
         fence_proxy_async_smem();
         mbar_arrive(&d1_empty[b]);
         mbar_arrive(&h_full[b]);
+        // one part of the previous tile's output (4 chunks per group and tile: every part finds its turn)
+        if (it > 0 && part < PARTS && (PARTS == 4 || (c >> 1) & 1)) {
+          drain_part(it - 1, tile - (int)gridDim.x, part);
+          ++part;
+        }
       }
     }
+    if (it > 0) {  // the last tile's output
+#pragma unroll 1
+      for (int k = 0; k < PARTS; ++k) drain_part(it - 1, tile - (int)gridDim.x, k);
+    }
+    if (leader) tma_store_wait0();
   }
 
   tc_fence_before_sync();
