@@ -1077,6 +1077,13 @@ static int triatt_slab(const void* z, const uint8_t* mask, const void* ext_bias,
     const uint32_t box[3] = {64, 128, 1};
     if (int e = make_tmap_bf16(&tmVT, vT, 3, dims, str, box, CU_TENSOR_MAP_SWIZZLE_128B)) return e;
   }
+  CUtensorMap tmWB;  // the 8 rows of the bias weights that hold the 4 heads, as two 64-channel halves
+  {
+    const uint64_t dims[2] = {128, 16};
+    const uint64_t str[1] = {256};
+    const uint32_t box[2] = {64, 8};
+    if (int e = make_tmap_bf16(&tmWB, w->w_b, 2, dims, str, box, CU_TENSOR_MAP_SWIZZLE_128B)) return e;
+  }
   if (int e = set_smem(triatt_proj_kernel<true>, triatt_proj::SMEM_BYTES)) return e;
   if (int e = set_smem(triatt_proj_kernel<false>, triatt_proj::SMEM_BYTES)) return e;
   TriAttProjParams pp;
@@ -1093,17 +1100,17 @@ static int triatt_slab(const void* z, const uint8_t* mask, const void* ext_bias,
   pp.z_pos_stride = pos_b;
   pp.num_tiles = lines * ((pos + 127) / 128);
   pp.eps = 1e-5f;
+  // Without a bias from the caller the projection kernel writes the triangle bias of the same rows itself.
+  pp.tri_bias = ext_bias ? nullptr : tb;
+  pp.bias_plane = (long long)pos * pl.Nk;
+  pp.bias_pitch = pl.Nk;
+  pp.bias_scale = 1.4426950408889634f;
   const int grid = pp.num_tiles < sm_count() ? pp.num_tiles : sm_count();
   if (f32)
-    triatt_proj_kernel<true><<<grid, triatt_proj::THREADS, triatt_proj::SMEM_BYTES, stream>>>(tmW, tmQKG, tmVT, pp);
+    triatt_proj_kernel<true><<<grid, triatt_proj::THREADS, triatt_proj::SMEM_BYTES, stream>>>(tmW, tmQKG, tmVT, tmWB, pp);
   else
-    triatt_proj_kernel<false><<<grid, triatt_proj::THREADS, triatt_proj::SMEM_BYTES, stream>>>(tmW, tmQKG, tmVT, pp);
+    triatt_proj_kernel<false><<<grid, triatt_proj::THREADS, triatt_proj::SMEM_BYTES, stream>>>(tmW, tmQKG, tmVT, tmWB, pp);
   B200_AFTER_LAUNCH();
-  if (!ext_bias) {
-    if (int e = launch_pair_bias(z, f32, w->ln_w, w->ln_b, w->w_b, tb, lines, pos, line_b, pos_b, (long long)pos * pl.Nk,
-                                 pl.Nk, 4, stream))
-      return e;
-  }
   {
     FlashLaunch a;
     a.qk = qkg;
