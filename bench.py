@@ -520,8 +520,7 @@ def run_b200(args) -> None:
         z_work.copy_(z_dev)
         s_work.copy_(s_dev)
         if composite:
-            for layer in trunk.layers:
-                layer.forward_(s_work, z_work, tok_dev, mask8)
+            trunk.forward_(s_work, z_work, tok_dev, mask8)
         else:
             for layer in trunk.layers:
                 layer.forward_(z_work, mask8)

@@ -634,15 +634,19 @@ def pad8(n: int) -> int:
 
 
 def pair_bias_slab(z_slab: Tensor, ln_w: Tensor, ln_b: Tensor | None, w_z_bf16: Tensor, H: int,
-                   transposed: bool = False) -> Tensor:
+                   transposed: bool = False, out: Tensor | None = None) -> Tensor:
     """``log2(e) * proj(LN(z))`` on a slab ``z[n_rows, n_cols, 128]`` -> bf16 ``[H, lines, pad8(pos)]`` with
-    (line, pos) = (row, col), or (col, row) when ``transposed``."""
+    (line, pos) = (row, col), or (col, row) when ``transposed``.  ``out``: a buffer of that shape to write into (its
+    padding columns must already be zero)."""
     _require_cuda(z_slab)
     zd = _zdtype(z_slab)
     z_slab = z_slab.contiguous()
     n_rows, n_cols = z_slab.shape[0], z_slab.shape[1]
     lines, pos = (n_cols, n_rows) if transposed else (n_rows, n_cols)
-    out = torch.zeros(H, lines, pad8(pos), dtype=torch.bfloat16, device=z_slab.device)
+    if out is None:
+        out = torch.zeros(H, lines, pad8(pos), dtype=torch.bfloat16, device=z_slab.device)
+    elif tuple(out.shape) != (H, lines, pad8(pos)) or out.dtype != torch.bfloat16 or not out.is_contiguous():
+        raise ValueError("out must be a contiguous bf16 [H, lines, pad8(pos)] buffer")
     _lib.check(lib.b200_pair_bias_fwd(z_slab.data_ptr(), ln_w.data_ptr(), _ptr(ln_b), w_z_bf16.data_ptr(), out.data_ptr(),
                                       n_rows, n_cols, n_cols * 128, lines * pad8(pos), pad8(pos), H,
                                       1 if transposed else 0, zd, _stream()))

@@ -53,8 +53,7 @@ class GraphedTrunk:
         self.z_out.copy_(self.z_in)
         if self.composite:
             pm = (self.mask_in[:, :, None] & self.mask_in[:, None, :]).to(torch.uint8)
-            for layer in self.trunk.layers:
-                layer.forward_(self.s_out, self.z_out, self.mask_in, pm)
+            self.trunk.forward_(self.s_out, self.z_out, self.mask_in, pm)
         else:
             pm = self.mask_in.to(torch.uint8)
             for layer in self.trunk.layers:
