@@ -59,3 +59,23 @@ def test_graphed_pairmixer_trunk_matches_eager():
         _, z_ref = trunk(s, z, pm)
         _, z_out = trunk.graphed(s, z, pm)(s, z)
     assert torch.equal(z_out, z_ref)
+
+
+def test_two_stream_trunk_loop_equals_the_serial_loop():
+    """``PairformerModule.forward_`` runs each block's single track on a side stream under the next block's pair
+    track; the kernels and their inputs are those of the serial loop, so the results are identical."""
+    import bioemu2_b200 as b
+
+    torch.manual_seed(44)
+    trunk = b.PairformerModule(384, 128, 4).eval().cuda()
+    g = torch.Generator().manual_seed(45)
+    N = 136
+    s, z = torch.randn(2, N, 384, generator=g).cuda(), torch.randn(2, N, N, 128, generator=g).cuda()
+    tok = torch.ones(2, N, dtype=torch.bool, device="cuda")
+    tok[0, N - 9:] = False
+    pm = (tok[:, :, None] & tok[:, None, :]).to(torch.uint8)
+    with torch.no_grad():
+        s1, z1 = trunk.forward_(s.clone(), z.clone(), tok, pm, overlap=True)
+        s2, z2 = trunk.forward_(s.clone(), z.clone(), tok, pm, overlap=False)
+        torch.cuda.synchronize()
+    assert torch.equal(z1, z2) and torch.equal(s1, s2)
