@@ -321,38 +321,56 @@ trimul_out_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant
 
   if (warp >= 4 && warp < 8) {
     // ------------------------------------------------------------------ t transformers
-    // thread j owns pair column j of the raw tile [d][j]; LayerNorm over d, written as row j of A1.
-    const int j = threadIdx.x - 128;
+    // The raw tile is [d][j] (channel-major, as the contraction writes it); LayerNorm runs over d and the result is row
+    // j of A1.  A thread owns TWO adjacent pair columns and HALF of the channels (lanes l and l ^ 16 share a column
+    // pair): one 32-bit shared-memory load brings both columns of a channel (two passes of 64 loads where one column
+    // per thread took two passes of 128 16-bit loads), and the two half sums meet in one shuffle.
+    const int tt = threadIdx.x - 128;
+    const int j0 = (tt >> 5) * 32 + (lane & 15) * 2;  // columns j0, j0 + 1
+    const int dh = lane >> 4;                         // channels 64*dh .. 64*dh + 63
     int it = 0;
     for (int tile = blockIdx.x; tile < p.num_tiles; tile += gridDim.x, ++it) {
       const int s = it & 1;
       mbar_wait(&t_full[s], (it >> 1) & 1, 25);
-      const __nv_bfloat16* traw = reinterpret_cast<const __nv_bfloat16*>(smem + T_OFF + s * kOperandTile) + j;
-      const float shift = __bfloat162float(traw[0]);
-      float sum = 0.f, sq = 0.f;
-#pragma unroll 8
-      for (int d = 0; d < kD; ++d) {
-        const float x = __bfloat162float(traw[d * 128]) - shift;
-        sum += x;
-        sq = fmaf(x, x, sq);
+      const uint32_t* traw = reinterpret_cast<const uint32_t*>(smem + T_OFF + s * kOperandTile) + (j0 >> 1);
+      const uint32_t* tcol = traw + dh * 64 * 64;
+      const uint32_t first = traw[0];
+      const float shift0 = bf16lo(first), shift1 = bf16hi(first);
+      float s0 = 0.f, q0 = 0.f, s1 = 0.f, q1 = 0.f;
+#pragma unroll 16
+      for (int k = 0; k < 64; ++k) {
+        const uint32_t vk = tcol[k * 64];
+        const float x0 = bf16lo(vk) - shift0, x1 = bf16hi(vk) - shift1;
+        s0 += x0;
+        q0 = fmaf(x0, x0, q0);
+        s1 += x1;
+        q1 = fmaf(x1, x1, q1);
       }
-      const float mean_s = sum * (1.0f / kD);
-      const float var = fmaxf(sq * (1.0f / kD) - mean_s * mean_s, 0.f);
-      const float rstd = rsqrtf(var + p.eps);
-      const float mean = mean_s + shift;
+      s0 += __shfl_xor_sync(0xffffffffu, s0, 16);
+      q0 += __shfl_xor_sync(0xffffffffu, q0, 16);
+      s1 += __shfl_xor_sync(0xffffffffu, s1, 16);
+      q1 += __shfl_xor_sync(0xffffffffu, q1, 16);
+      const float ms0 = s0 * (1.0f / kD), ms1 = s1 * (1.0f / kD);
+      const float rstd0 = rsqrtf(fmaxf(q0 * (1.0f / kD) - ms0 * ms0, 0.f) + p.eps);
+      const float rstd1 = rsqrtf(fmaxf(q1 * (1.0f / kD) - ms1 * ms1, 0.f) + p.eps);
+      const float mean0 = ms0 + shift0, mean1 = ms1 + shift1;
       mbar_wait(a_empty, (it & 1) ^ 1, 26);
-      uint8_t* a1 = smem + A1_OFF;
+      uint8_t* a1 = smem + A1_OFF + dh * kOperandHalf;  // this thread's channels are one 64-channel half of the operand
 #pragma unroll 2
-      for (int c = 0; c < 16; ++c) {
-        float y[8];
+      for (int cc = 0; cc < 8; ++cc) {
+        float y0[8], y1[8];
 #pragma unroll
         for (int i = 0; i < 8; ++i) {
-          const int d = c * 8 + i;
-          y[i] = fmaf((__bfloat162float(traw[d * 128]) - mean) * rstd, ln_s[d], ln_s[128 + d]);
+          const int k = cc * 8 + i, d = dh * 64 + k;
+          const uint32_t vk = tcol[k * 64];
+          const float g = ln_s[d], bb = ln_s[128 + d];
+          y0[i] = fmaf((bf16lo(vk) - mean0) * rstd0, g, bb);
+          y1[i] = fmaf((bf16hi(vk) - mean1) * rstd1, g, bb);
         }
-        uint4 o = make_uint4(pack_bf16x2(y[0], y[1]), pack_bf16x2(y[2], y[3]), pack_bf16x2(y[4], y[5]),
-                             pack_bf16x2(y[6], y[7]));
-        *reinterpret_cast<uint4*>(a1 + (c >> 3) * kOperandHalf + sw128_offset(j, c & 7)) = o;
+        *reinterpret_cast<uint4*>(a1 + sw128_offset(j0, cc)) = make_uint4(
+            pack_bf16x2(y0[0], y0[1]), pack_bf16x2(y0[2], y0[3]), pack_bf16x2(y0[4], y0[5]), pack_bf16x2(y0[6], y0[7]));
+        *reinterpret_cast<uint4*>(a1 + sw128_offset(j0 + 1, cc)) = make_uint4(
+            pack_bf16x2(y1[0], y1[1]), pack_bf16x2(y1[2], y1[3]), pack_bf16x2(y1[4], y1[5]), pack_bf16x2(y1[6], y1[7]));
       }
       fence_proxy_async_smem();
       mbar_arrive(a1_full);
